@@ -1,0 +1,183 @@
+/* libpgb200 - B200 (sm_100a) runtime library for the dense contractions that
+ * appear as C loop nests in Polygeist's PolyBench workloads.
+ *
+ * Calling convention.  The entry points take exactly what Polygeist's C-style
+ * memref lowering hands to an external callee: one bare pointer to element
+ * (0,0) of each row-major array (lib/polygeist/Passes/ConvertPolygeistToLLVM.cpp
+ * :2802-2810, pinned by test/polygeist-opt/cconv-func.mlir:3-18), sizes and
+ * leading dimensions as explicit integers, floating scalars by value, and an
+ * opaque `void*` stream whose null value means the default stream
+ * (lib/polygeist/Passes/RuntimeWrapperUtils.h:124,139;
+ * ConvertPolygeistToLLVM.cpp:2315-2318).  Like the reference runtime's `*Err`
+ * wrappers (lib/polygeist/ExecutionEngine/CudaRuntimeWrappers.cpp:29-50,90-97)
+ * every function returns an int32_t status (0 = success), prints
+ * "'<expr>' failed with '<msg>'" to stderr on a CUDA error and returns: no
+ * abort, no exception.
+ *
+ * Pointers.  Each array pointer may be device, managed or host memory.  Device
+ * and managed arrays are used in place and the call is asynchronous on
+ * `stream`.  Host arrays (what the PolyBench nests operate on,
+ * tools/cgeist/Test/polybench/utilities/polybench.h:233-235) are staged to the
+ * GPU and back inside the call, which then synchronises `stream` before
+ * returning because the C caller reads the result immediately.
+ *
+ * There is no CPU fallback: without a usable sm_100 GPU every compute entry
+ * point fails with PGB200_ERR_CUDA / PGB200_ERR_UNSUPPORTED.
+ */
+#ifndef PGB200_H
+#define PGB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  PGB200_OK = 0,
+  PGB200_ERR_INVALID = 1,     /* bad size, leading dimension or null pointer */
+  PGB200_ERR_CUDA = 2,        /* a CUDA runtime/driver call failed           */
+  PGB200_ERR_NCCL = 3,        /* reserved for the multi-GPU entry points     */
+  PGB200_ERR_TIMEOUT = 4,     /* a bounded device-side wait expired          */
+  PGB200_ERR_UNSUPPORTED = 5  /* no sm_100 device / feature unavailable      */
+};
+
+/* Optional tuning knobs; pgb200Init(NULL) and lazy initialisation use the
+ * defaults.  A zero field means "default". */
+typedef struct pgb200Config {
+  int32_t log_level;          /* 0 quiet (errors only), 1 info, 2 per call   */
+  int32_t sgemm_chunk_kblocks;/* 3xTF32: K-blocks (of 32) accumulated in the
+                                 tensor-core accumulator before it is drained
+                                 into fp32 registers; bounds the truncation
+                                 bias of tensor-core accumulation             */
+  int32_t force_generic;      /* 1: always take the plain SIMT kernels        */
+  int32_t reserved[5];
+} pgb200Config;
+
+/* Runtime life cycle.  Replaces nothing in the reference one-to-one; plays the
+ * role of the lazily created primary context of
+ * lib/polygeist/ExecutionEngine/CudaRuntimeWrappers.cpp:52-76.  Initialisation
+ * is also done lazily by the first compute call. */
+int32_t pgb200Init(const pgb200Config *cfg);
+int32_t pgb200Shutdown(void);
+const char *pgb200GetLastErrorString(void);
+int32_t pgb200Version(void);
+
+/* C[MxN] = alpha * A[MxK] * B[KxN] + beta * C, all row-major.
+ * Replaces the loop nest kernel_gemm,
+ * tools/cgeist/Test/polybench/linear-algebra/blas/gemm/gemm.c:104-113, and each
+ * of the two nests of kernel_2mm,
+ * tools/cgeist/Test/polybench/linear-algebra/kernels/2mm/2mm.c:103-119
+ * (beta == 0 never reads C, like `tmp[i][j] = 0` at 2mm.c:108).
+ * fp64 runs on the DMMA tensor path. */
+int32_t pgb200Dgemm(void *stream, int64_t M, int64_t N, int64_t K, double alpha,
+                    const double *A, int64_t lda, const double *B, int64_t ldb,
+                    double beta, double *C, int64_t ldc);
+
+/* fp32 version of the same nest (gemm.c built with -DDATA_TYPE_IS_FLOAT,
+ * gemm.h:70-77) on the tcgen05 tensor path with an error-compensated 3xTF32
+ * split. */
+int32_t pgb200Sgemm(void *stream, int64_t M, int64_t N, int64_t K, float alpha,
+                    const float *A, int64_t lda, const float *B, int64_t ldb,
+                    float beta, float *C, int64_t ldc);
+
+/* Lower triangle of C[NxN] = alpha * A[NxK] * A^T + beta * C; the strict upper
+ * triangle of C is neither read nor written.  Replaces kernel_syrk,
+ * tools/cgeist/Test/polybench/linear-algebra/blas/syrk/syrk.c:97-106. */
+int32_t pgb200Dsyrk(void *stream, int64_t N, int64_t K, double alpha,
+                    const double *A, int64_t lda, double beta, double *C,
+                    int64_t ldc);
+int32_t pgb200Ssyrk(void *stream, int64_t N, int64_t K, float alpha,
+                    const float *A, int64_t lda, float beta, float *C,
+                    int64_t ldc);
+
+/* Rows [row0,row1) of the same lower-triangular update: the unit one GPU owns
+ * when the rows of C are partitioned across devices.  A must hold rows
+ * [0,row1).  No counterpart loop in the reference (it has no multi-GPU path);
+ * the statements are those of syrk.c:97-106 with the outer i restricted. */
+int32_t pgb200SsyrkRows(void *stream, int64_t N, int64_t K, int64_t row0,
+                        int64_t row1, float alpha, const float *A, int64_t lda,
+                        float beta, float *C, int64_t ldc);
+
+/* y[.] = alpha * op(A) * x + beta * y with A[MxN] row-major;
+ * transA == 0: op(A) = A (y has M entries), transA != 0: op(A) = A^T (y has N).
+ * Replaces either nest of kernel_mvt taken alone,
+ * tools/cgeist/Test/polybench/linear-algebra/kernels/mvt/mvt.c:102-105 and
+ * :106-109, and the same-shaped nests of atax/bicg/gesummv. */
+int32_t pgb200Dgemv(void *stream, int32_t transA, int64_t M, int64_t N,
+                    double alpha, const double *A, int64_t lda, const double *x,
+                    double beta, double *y);
+
+/* x1 += A * y1 and x2 += A^T * y2 with A[NxN] read ONCE for both results.
+ * Replaces the whole scop of kernel_mvt, mvt.c:102-109. */
+int32_t pgb200Dmvt(void *stream, int64_t N, const double *A, int64_t lda,
+                   const double *y1, const double *y2, double *x1, double *x2);
+
+/* Counter-based uniform generator used by the test and benchmark harness
+ * (device pointer only).  Element (r,c) of the logical rows x cols array, for
+ * r in [row0,row0+rows), written at dst[(r-row0)*ld + c]:
+ *   h = splitmix64(seed ^ (array_id << 56)); x = splitmix64(h + r*cols + c);
+ *   fp64: u = (x >> 11) * 2^-53; fp32: u = (x >> 40) * 2^-24;
+ *   value = lo + (hi - lo) * u.
+ * No counterpart in the reference (PolyBench's init_array is a modular
+ * formula, e.g. gemm.c:42-63). */
+int32_t pgb200FillUniformF64(void *stream, double *dst, int64_t row0,
+                             int64_t rows, int64_t cols, int64_t ld,
+                             uint64_t seed, uint32_t array_id, double lo,
+                             double hi);
+int32_t pgb200FillUniformF32(void *stream, float *dst, int64_t row0,
+                             int64_t rows, int64_t cols, int64_t ld,
+                             uint64_t seed, uint32_t array_id, float lo,
+                             float hi);
+
+/* Which kernel family served the last compute call of this thread:
+ * 0 none yet, 1 plain SIMT kernels, 2 DMMA tensor path, 3 tcgen05 3xTF32 path,
+ * 4 HBM-streaming mat-vec.  Lets tests assert that the fast path ran. */
+int32_t pgb200LastPath(void);
+
+/* Every device-side wait in the tensor-core kernels (mbarrier, tensor-memory
+ * handshakes) has an iteration limit; a kernel whose wait expires records a code
+ * in a host-visible status word and returns instead of hanging.  This reads
+ * and clears that word: PGB200_OK or PGB200_ERR_TIMEOUT.  Call it after the
+ * stream has been synchronised.  (The reference runtime has no such check: its
+ * wrappers only report launch errors, CudaRuntimeWrappers.cpp:90-97.) */
+int32_t pgb200PollDeviceStatus(void);
+
+/* Measured peak of the current GPU, the denominators of the fp64 rooflines:
+ * kind 0 = fp64 tensor (best of the mma.sync .f64 shapes; 10/11/12/13 select
+ * m16n8k4 / k8 / k16 / m8n8k4), 1 = fp64 FMA, in GFLOP/s from register-only
+ * issue loops; 2 = read-only HBM sweep over 2 GiB in GB/s.  Synchronises the
+ * stream.  No counterpart in the reference. */
+int32_t pgb200ProbePeak(void *stream, int32_t kind, double *out);
+
+/* How many of this library's kernels this thread has launched so far. */
+int64_t pgb200LaunchCount(void);
+
+/* Host-array drop-ins with the reference's own function names, argument order
+ * and array extents (C99 prototypes of PolyBench: inner dimension = the size
+ * argument).  Arrays are host memory, exactly what the C nests receive; each
+ * call stages operands to the GPU, runs the contraction(s) and copies the
+ * results back before returning.
+ *   pgb200_kernel_gemm  <- kernel_gemm  gemm.c:88-115
+ *   pgb200_kernel_2mm   <- kernel_2mm   2mm.c:92-121  (tmp is written too)
+ *   pgb200_kernel_mvt   <- kernel_mvt   mvt.c:93-111
+ *   pgb200_kernel_syrk  <- kernel_syrk  syrk.c:83-108
+ * The `_f32` forms are the -DDATA_TYPE_IS_FLOAT builds of the same sources. */
+int32_t pgb200_kernel_gemm(int ni, int nj, int nk, double alpha, double beta,
+                           double *C, const double *A, const double *B);
+int32_t pgb200_kernel_gemm_f32(int ni, int nj, int nk, float alpha, float beta,
+                               float *C, const float *A, const float *B);
+int32_t pgb200_kernel_2mm(int ni, int nj, int nk, int nl, double alpha,
+                          double beta, double *tmp, const double *A,
+                          const double *B, const double *C, double *D);
+int32_t pgb200_kernel_mvt(int n, double *x1, double *x2, const double *y_1,
+                          const double *y_2, const double *A);
+int32_t pgb200_kernel_syrk(int n, int m, double alpha, double beta, double *C,
+                           const double *A);
+int32_t pgb200_kernel_syrk_f32(int n, int m, float alpha, float beta, float *C,
+                               const float *A);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PGB200_H */

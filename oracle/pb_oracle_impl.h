@@ -1,0 +1,136 @@
+/* Type-generic body of the CPU oracle.  Included twice by pb_oracle.c with
+ * T / SUF defined (double/_f64 and float/_f32).  TEST INFRASTRUCTURE ONLY.
+ *
+ * Every kernel restates one PolyBench/C 4.2 loop nest of the reference
+ * (paths relative to tools/cgeist/Test/polybench/) with run-time sizes and
+ * leading dimensions.  Statement order, loop order and the association of
+ * each product are kept exactly as in the source, so that for equal inputs
+ * the result is bit-identical to the reference compiled without FP
+ * contraction. */
+
+#define CAT_(a, b) a##b
+#define CAT(a, b) CAT_(a, b)
+#define FN(name) CAT(name, SUF)
+
+/* linear-algebra/blas/gemm/gemm.c:104-113
+ *   for i { for j C[i][j] *= beta;
+ *           for k for j C[i][j] += alpha * A[i][k] * B[k][j]; } */
+void FN(pbo_gemm)(int64_t ni, int64_t nj, int64_t nk, T alpha, T beta,
+                  T *C, int64_t ldc, const T *A, int64_t lda,
+                  const T *B, int64_t ldb)
+{
+  for (int64_t i = 0; i < ni; i++) {
+    for (int64_t j = 0; j < nj; j++)
+      C[i * ldc + j] *= beta;
+    for (int64_t k = 0; k < nk; k++) {
+      for (int64_t j = 0; j < nj; j++)
+        C[i * ldc + j] += alpha * A[i * lda + k] * B[k * ldb + j];
+    }
+  }
+}
+
+/* linear-algebra/kernels/2mm/2mm.c:103-119
+ *   nest 1: tmp[i][j] = 0; for k tmp[i][j] += alpha * A[i][k] * B[k][j];
+ *   nest 2: D[i][j] *= beta; for k D[i][j] += tmp[i][k] * C[k][j]; */
+void FN(pbo_2mm)(int64_t ni, int64_t nj, int64_t nk, int64_t nl, T alpha,
+                 T beta, T *tmp, int64_t ldtmp, const T *A, int64_t lda,
+                 const T *B, int64_t ldb, const T *C, int64_t ldcc, T *D,
+                 int64_t ldd)
+{
+  for (int64_t i = 0; i < ni; i++)
+    for (int64_t j = 0; j < nj; j++) {
+      tmp[i * ldtmp + j] = (T)0.0;
+      for (int64_t k = 0; k < nk; ++k)
+        tmp[i * ldtmp + j] += alpha * A[i * lda + k] * B[k * ldb + j];
+    }
+  for (int64_t i = 0; i < ni; i++)
+    for (int64_t j = 0; j < nl; j++) {
+      D[i * ldd + j] *= beta;
+      for (int64_t k = 0; k < nj; ++k)
+        D[i * ldd + j] += tmp[i * ldtmp + k] * C[k * ldcc + j];
+    }
+}
+
+/* linear-algebra/kernels/mvt/mvt.c:102-109
+ *   nest 1: x1[i] = x1[i] + A[i][j] * y_1[j];
+ *   nest 2: x2[i] = x2[i] + A[j][i] * y_2[j];
+ * [row0,row1) restricts the outer i of both nests (the full kernel is
+ * row0=0,row1=n); each x[i] depends on no other x, so a restricted run is
+ * bit-identical to the full one on those entries. */
+void FN(pbo_mvt_range)(int64_t n, int64_t row0, int64_t row1, T *x1, T *x2,
+                       const T *y1, const T *y2, const T *A, int64_t lda)
+{
+  for (int64_t i = row0; i < row1; i++)
+    for (int64_t j = 0; j < n; j++)
+      x1[i] = x1[i] + A[i * lda + j] * y1[j];
+  for (int64_t i = row0; i < row1; i++)
+    for (int64_t j = 0; j < n; j++)
+      x2[i] = x2[i] + A[j * lda + i] * y2[j];
+}
+
+void FN(pbo_mvt)(int64_t n, T *x1, T *x2, const T *y1, const T *y2,
+                 const T *A, int64_t lda)
+{
+  FN(pbo_mvt_range)(n, 0, n, x1, x2, y1, y2, A, lda);
+}
+
+/* linear-algebra/blas/syrk/syrk.c:97-106
+ *   for i { for j<=i C[i][j] *= beta;
+ *           for k for j<=i C[i][j] += alpha * A[i][k] * A[j][k]; }
+ * The strict upper triangle of C is never touched.  [row0,row1) restricts i;
+ * A must still hold rows 0..row1-1. */
+void FN(pbo_syrk_range)(int64_t row0, int64_t row1, int64_t m, T alpha,
+                        T beta, T *C, int64_t ldc, const T *A, int64_t lda)
+{
+  for (int64_t i = row0; i < row1; i++) {
+    for (int64_t j = 0; j <= i; j++)
+      C[i * ldc + j] *= beta;
+    for (int64_t k = 0; k < m; k++) {
+      for (int64_t j = 0; j <= i; j++)
+        C[i * ldc + j] += alpha * A[i * lda + k] * A[j * lda + k];
+    }
+  }
+}
+
+void FN(pbo_syrk)(int64_t n, int64_t m, T alpha, T beta, T *C, int64_t ldc,
+                  const T *A, int64_t lda)
+{
+  FN(pbo_syrk_range)(0, n, m, alpha, beta, C, ldc, A, lda);
+}
+
+/* Same statements as pbo_gemm, but with a double accumulator per output and
+ * the fp32 inputs promoted: the "truth" that fp32 results are also gated on
+ * (the sequential fp32 sum itself drifts from it as K grows). */
+void FN(pbo_gemm_acc64)(int64_t ni, int64_t nj, int64_t nk, T alpha, T beta,
+                        double *Cout, int64_t ldo, const T *C, int64_t ldc,
+                        const T *A, int64_t lda, const T *B, int64_t ldb)
+{
+  for (int64_t i = 0; i < ni; i++) {
+    for (int64_t j = 0; j < nj; j++)
+      Cout[i * ldo + j] = (double)beta * (double)C[i * ldc + j];
+    for (int64_t k = 0; k < nk; k++) {
+      const double a = (double)alpha * (double)A[i * lda + k];
+      for (int64_t j = 0; j < nj; j++)
+        Cout[i * ldo + j] += a * (double)B[k * ldb + j];
+    }
+  }
+}
+
+void FN(pbo_syrk_range_acc64)(int64_t row0, int64_t row1, int64_t m, T alpha,
+                              T beta, double *Cout, int64_t ldo, const T *C,
+                              int64_t ldc, const T *A, int64_t lda)
+{
+  for (int64_t i = row0; i < row1; i++) {
+    for (int64_t j = 0; j <= i; j++)
+      Cout[i * ldo + j] = (double)beta * (double)C[i * ldc + j];
+    for (int64_t k = 0; k < m; k++) {
+      const double a = (double)alpha * (double)A[i * lda + k];
+      for (int64_t j = 0; j <= i; j++)
+        Cout[i * ldo + j] += a * (double)A[j * lda + k];
+    }
+  }
+}
+
+#undef FN
+#undef CAT
+#undef CAT_

@@ -1,0 +1,220 @@
+"""polygeist_b200 - Python host side of libpgb200.
+
+The product is the C-ABI shared library (include/pgb200.h).  This package
+  * builds / loads it (`load()`), with typed ctypes signatures for every symbol
+    the header declares;
+  * offers thin array-level wrappers (`dgemm`, `sgemm`, `dsyrk`, `ssyrk`,
+    `dgemv`, `dmvt`, `fill_uniform`) that accept torch CUDA tensors (used in
+    place) or numpy arrays (host memory, staged by the library);
+  * mirrors the reference's PolyBench kernel functions for host arrays in
+    `polygeist_b200.polybench` (kernel_gemm, kernel_2mm, kernel_mvt,
+    kernel_syrk: same names, argument order and in-place semantics).
+
+There is no CPU fallback: if the library cannot be loaded, or no sm_100 GPU
+is present, calls raise.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libpgb200.so")
+
+OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED = range(6)
+PATH_NONE, PATH_SIMT, PATH_DMMA, PATH_TCGEN05, PATH_STREAM = range(5)
+
+
+class PGB200Error(RuntimeError):
+    def __init__(self, status, msg):
+        super().__init__(f"libpgb200 status {status}: {msg}")
+        self.status = status
+
+
+class Config(C.Structure):
+    _fields_ = [("log_level", C.c_int32), ("sgemm_chunk_kblocks", C.c_int32),
+                ("force_generic", C.c_int32), ("reserved", C.c_int32 * 5)]
+
+
+_i32, _i64, _vp, _f64, _f32 = C.c_int32, C.c_int64, C.c_void_p, C.c_double, C.c_float
+_int = C.c_int
+
+# name -> (restype, argtypes); must list every symbol of include/pgb200.h.
+SIGNATURES = {
+    "pgb200Init": (_i32, [C.POINTER(Config)]),
+    "pgb200Shutdown": (_i32, []),
+    "pgb200GetLastErrorString": (C.c_char_p, []),
+    "pgb200Version": (_i32, []),
+    "pgb200Dgemm": (_i32, [_vp, _i64, _i64, _i64, _f64, _vp, _i64, _vp, _i64, _f64, _vp, _i64]),
+    "pgb200Sgemm": (_i32, [_vp, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64, _f32, _vp, _i64]),
+    "pgb200Dsyrk": (_i32, [_vp, _i64, _i64, _f64, _vp, _i64, _f64, _vp, _i64]),
+    "pgb200Ssyrk": (_i32, [_vp, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
+    "pgb200SsyrkRows": (_i32, [_vp, _i64, _i64, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
+    "pgb200Dgemv": (_i32, [_vp, _i32, _i64, _i64, _f64, _vp, _i64, _vp, _f64, _vp]),
+    "pgb200Dmvt": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp]),
+    "pgb200FillUniformF64": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, C.c_uint64, C.c_uint32, _f64, _f64]),
+    "pgb200FillUniformF32": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, C.c_uint64, C.c_uint32, _f32, _f32]),
+    "pgb200LastPath": (_i32, []),
+    "pgb200PollDeviceStatus": (_i32, []),
+    "pgb200LaunchCount": (_i64, []),
+    "pgb200ProbePeak": (_i32, [_vp, _i32, C.POINTER(_f64)]),
+    "pgb200_kernel_gemm": (_i32, [_int, _int, _int, _f64, _f64, _vp, _vp, _vp]),
+    "pgb200_kernel_gemm_f32": (_i32, [_int, _int, _int, _f32, _f32, _vp, _vp, _vp]),
+    "pgb200_kernel_2mm": (_i32, [_int, _int, _int, _int, _f64, _f64, _vp, _vp, _vp, _vp, _vp]),
+    "pgb200_kernel_mvt": (_i32, [_int, _vp, _vp, _vp, _vp, _vp]),
+    "pgb200_kernel_syrk": (_i32, [_int, _int, _f64, _f64, _vp, _vp]),
+    "pgb200_kernel_syrk_f32": (_i32, [_int, _int, _f32, _f32, _vp, _vp]),
+}
+
+_lib = None
+
+
+def load(build_if_missing=True):
+    """Return the ctypes handle of libpgb200.so (building it in-tree first when
+    it is absent and nvcc is available)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        if not build_if_missing:
+            raise ImportError(f"{LIB_PATH} is missing; run python -m polygeist_b200.build")
+        from . import build as _b
+        _b.build()
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here = header/library mismatch
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(status):
+    if status != OK:
+        raise PGB200Error(status, load().pgb200GetLastErrorString().decode())
+
+
+def init(log_level=0, sgemm_chunk_kblocks=0, force_generic=0):
+    cfg = Config(log_level, sgemm_chunk_kblocks, force_generic)
+    check(load().pgb200Init(C.byref(cfg)))
+
+
+def last_path():
+    return load().pgb200LastPath()
+
+
+def launch_count():
+    return load().pgb200LaunchCount()
+
+
+def poll_device_status():
+    check(load().pgb200PollDeviceStatus())
+
+
+# ---------------------------------------------------------------------------
+# array plumbing: torch CUDA tensors or numpy arrays
+# ---------------------------------------------------------------------------
+def _is_torch(a):
+    return type(a).__module__.startswith("torch")
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    return a.data_ptr() if _is_torch(a) else a.ctypes.data
+
+
+def _ld(a):
+    """Leading dimension (in elements) of a row-major 2-D array/tensor."""
+    if _is_torch(a):
+        assert a.dim() == 2 and (a.stride(1) == 1 or a.shape[1] <= 1)
+        return max(a.stride(0), a.shape[1], 1) if a.shape[0] > 1 else max(a.shape[1], 1)
+    assert a.ndim == 2 and (a.strides[1] == a.itemsize or a.shape[1] <= 1)
+    return max(a.strides[0] // a.itemsize, a.shape[1], 1) if a.shape[0] > 1 else max(a.shape[1], 1)
+
+
+def _is_f64(a):
+    return "float64" in str(a.dtype)
+
+
+def _stream(stream):
+    if stream is None:
+        return None
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+def current_stream_for(*arrays):
+    """torch's current stream when any operand is a CUDA tensor, else null."""
+    for a in arrays:
+        if a is not None and _is_torch(a) and a.is_cuda:
+            import torch
+            return torch.cuda.current_stream(a.device).cuda_stream
+    return None
+
+
+def gemm(alpha, A, B, beta, Cm, stream=None):
+    """Cm = alpha*A@B + beta*Cm in place (fp64 -> pgb200Dgemm, fp32 -> pgb200Sgemm)."""
+    M, K = A.shape
+    N = B.shape[1]
+    assert B.shape[0] == K and tuple(Cm.shape) == (M, N)
+    s = _stream(stream) if stream is not None else current_stream_for(A, B, Cm)
+    fn = load().pgb200Dgemm if _is_f64(Cm) else load().pgb200Sgemm
+    check(fn(s, M, N, K, alpha, _ptr(A), _ld(A), _ptr(B), _ld(B), beta, _ptr(Cm), _ld(Cm)))
+    return Cm
+
+
+def syrk(alpha, A, beta, Cm, stream=None, rows=None):
+    """Lower triangle of Cm = alpha*A@A^T + beta*Cm in place; `rows=(r0,r1)`
+    restricts the update to that row block (fp32 only)."""
+    N, K = A.shape
+    assert tuple(Cm.shape) == (N, N)
+    s = _stream(stream) if stream is not None else current_stream_for(A, Cm)
+    if rows is not None:
+        assert not _is_f64(Cm)
+        check(load().pgb200SsyrkRows(s, N, K, rows[0], rows[1], alpha, _ptr(A), _ld(A), beta,
+                                     _ptr(Cm), _ld(Cm)))
+        return Cm
+    fn = load().pgb200Dsyrk if _is_f64(Cm) else load().pgb200Ssyrk
+    check(fn(s, N, K, alpha, _ptr(A), _ld(A), beta, _ptr(Cm), _ld(Cm)))
+    return Cm
+
+
+def gemv(trans, alpha, A, x, beta, y, stream=None):
+    M, N = A.shape
+    s = _stream(stream) if stream is not None else current_stream_for(A, x, y)
+    check(load().pgb200Dgemv(s, 1 if trans else 0, M, N, alpha, _ptr(A), _ld(A), _ptr(x), beta,
+                             _ptr(y)))
+    return y
+
+
+def mvt(A, y1, y2, x1, x2, stream=None):
+    """x1 += A@y1 ; x2 += A^T@y2 in one pass over A."""
+    N = A.shape[0]
+    assert A.shape[1] == N
+    s = _stream(stream) if stream is not None else current_stream_for(A, x1, x2)
+    check(load().pgb200Dmvt(s, N, _ptr(A), _ld(A), _ptr(y1), _ptr(y2), _ptr(x1), _ptr(x2)))
+    return x1, x2
+
+
+def fill_uniform(t, seed, array_id, lo, hi, row0=0, logical_cols=None, stream=None):
+    """Fill a CUDA tensor (1-D or row-major 2-D) with the harness generator."""
+    if t.dim() == 1:
+        rows, cols, ld = 1, t.shape[0], max(t.shape[0], 1)
+    else:
+        rows, cols, ld = t.shape[0], t.shape[1], _ld(t)
+    assert logical_cols is None or logical_cols == cols
+    s = _stream(stream) if stream is not None else current_stream_for(t)
+    fn = load().pgb200FillUniformF64 if _is_f64(t) else load().pgb200FillUniformF32
+    check(fn(s, _ptr(t), row0, rows, cols, ld, seed, array_id, lo, hi))
+    return t
+
+
+PEAK_DMMA, PEAK_DFMA, PEAK_HBM_READ, PEAK_TF32 = 0, 1, 2, 3
+
+
+def probe_peak(kind, stream=None):
+    """Measured peak of this GPU for `kind` (GFLOP/s or GB/s): a register-only
+    tensor/FMA issue loop or a read-only HBM sweep.  Roofline denominators."""
+    out = _f64(0.0)
+    check(load().pgb200ProbePeak(_stream(stream), kind, C.byref(out)))
+    return out.value

@@ -1,0 +1,333 @@
+// fp64 GEMM / SYRK on the DMMA tensor path (tcgen05 has no f64 kind, so the
+// fp64 tensor instruction on sm_100a is the warp-level mma.sync .f64).
+//
+// Persistent kernel, one CTA per SM, 128x128 output tile per CTA iteration:
+//   warp 8      producer: one elected lane issues two 3-D TMA loads per K-step
+//               into a STAGES-deep shared-memory ring guarded by mbarriers;
+//   warps 0-7   consumers: 2x4 warp grid, each a 64x32 sub-tile held as
+//               4x4 m16n8 accumulator fragments (128 registers), fed by
+//               conflict-free 64-bit shared loads, then the alpha/beta epilogue.
+//
+// Shared-memory layout.  A 2-D row-major operand with 8-byte elements cannot be
+// read conflict-free in the mma fragment pattern (8 rows x 4 k) from a 128-byte
+// swizzled tile, so each operand is described to TMA as a 3-D tensor
+//   A[M][K]   -> dims (4, M, K/4), strides (lda*8, 32)  box (4, 128, BK/4)
+//   B[K][N]   -> dims (4, K, N/4), strides (ldb*8, 32)  box (4, BK, 32)
+//   B^T[N][K] -> like A (for the rank-k update, B(k,n) = A[n][k])
+// which lands as [k/4][row][4] resp. [n/4][k][4] doubles: the 16 lanes of a
+// half-warp then read 128 contiguous bytes.  The innermost TMA coordinate is
+// always 0, so every copy starts on a 16-byte boundary.  Out-of-range rows,
+// columns and K are zero-filled by TMA; the epilogue masks the stores.
+#include "pgb200_internal.h"
+
+namespace pgb200 {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 16;
+constexpr int STAGES = 6;
+constexpr int CONSUMER_WARPS = 8;
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int A_STAGE_BYTES = BM * BK * 8;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 8;  // 16 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;  // try_wait rounds before giving up
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait: false when the limit was reached.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+// Records a failure code where the host can read it (mapped pinned memory).
+__device__ __forceinline__ void report_status(int32_t *status, int32_t code, int32_t detail) {
+  volatile int32_t *s = status;
+  s[1] = detail;
+  s[0] = code;
+  __threadfence_system();
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void dmma_m16n8k4(double (&d)[4], const double (&a)[2], double b) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k4.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5}, {%6}, "
+      "{%0,%1,%2,%3};"
+      : "+d"(d[0]), "+d"(d[1]), "+d"(d[2]), "+d"(d[3])
+      : "d"(a[0]), "d"(a[1]), "d"(b));
+}
+
+// Tile enumeration.  Full: tiles walk down groups of 8 tile-rows so that the
+// CTAs running together share A row panels and B column panels in L2.
+// Lower: only tiles that intersect j <= i, row by row.
+struct TileMap {
+  int64_t tiles_m, tiles_n, total;
+  int lower;
+  __device__ void get(int64_t idx, int64_t *tm, int64_t *tn) const {
+    if (lower) {
+      // idx = tm*(tm+1)/2 + tn with tn <= tm (BM == BN).
+      int64_t r = (int64_t)((sqrt(8.0 * (double)idx + 1.0) - 1.0) * 0.5);
+      while (r * (r + 1) / 2 > idx) r--;
+      while ((r + 1) * (r + 2) / 2 <= idx) r++;
+      *tm = r;
+      *tn = idx - r * (r + 1) / 2;
+    } else {
+      constexpr int64_t G = 8;
+      const int64_t per_group = G * tiles_n;
+      const int64_t grp = idx / per_group;
+      const int64_t first = grp * G;
+      const int64_t rows = (tiles_m - first < G) ? (tiles_m - first) : G;
+      const int64_t in = idx - grp * per_group;
+      *tm = first + in % rows;
+      *tn = in / rows;
+    }
+  }
+};
+
+template <bool TRANSB>
+__global__ void __launch_bounds__(THREADS, 1)
+dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                 int64_t M, int64_t N, int64_t K, double alpha, double beta,
+                 double *__restrict__ C, int64_t ldc, TileMap tiles, int32_t *status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES];
+  // 1024-byte aligned ring base.
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, CONSUMER_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int64_t nkb = (K + BK - 1) / BK;
+
+  if (warp == CONSUMER_WARPS) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < tiles.total && ok; t += gridDim.x) {
+        int64_t tm, tn;
+        tiles.get(t, &tm, &tn);
+        for (int64_t kb = 0; kb < nkb; kb++) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) {
+            report_status(status, 1, (int32_t)blockIdx.x);
+            ok = false;
+            break;
+          }
+          const uint32_t dstA = ring + stage * STAGE_BYTES;
+          const uint32_t dstB = dstA + A_STAGE_BYTES;
+          mbar_expect_tx(full0 + 8 * stage, STAGE_BYTES);
+          tma_load_3d(dstA, &mapA, full0 + 8 * stage, 0, (int)(tm * BM), (int)(kb * (BK / 4)));
+          if (TRANSB)
+            tma_load_3d(dstB, &mapB, full0 + 8 * stage, 0, (int)(tn * BN), (int)(kb * (BK / 4)));
+          else
+            tma_load_3d(dstB, &mapB, full0 + 8 * stage, 0, (int)(kb * BK), (int)(tn * (BN / 4)));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------- consumers --------------------------------
+  const int g = lane >> 2, t4 = lane & 3;
+  const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps -> 64 x 32 sub-tiles
+  uint32_t stage = 0, phase = 0;
+  for (int64_t t = blockIdx.x; t < tiles.total; t += gridDim.x) {
+    int64_t tm, tn;
+    tiles.get(t, &tm, &tn);
+    double acc[4][4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+#pragma unroll
+        for (int r = 0; r < 4; r++) acc[i][j][r] = 0.0;
+
+    for (int64_t kb = 0; kb < nkb; kb++) {
+      if (!mbar_wait(full0 + 8 * stage, phase)) {
+        report_status(status, 2, (int32_t)blockIdx.x);
+        return;
+      }
+      const double *As = reinterpret_cast<const double *>(ring_ptr + stage * STAGE_BYTES);
+      const double *Bs = reinterpret_cast<const double *>(ring_ptr + stage * STAGE_BYTES +
+                                                          A_STAGE_BYTES);
+#pragma unroll
+      for (int kk = 0; kk < BK / 4; kk++) {
+        double a[4][2], b[4];
+#pragma unroll
+        for (int mt = 0; mt < 4; mt++) {
+          const int row = wm * 64 + mt * 16 + g;
+          a[mt][0] = As[(kk * BM + row) * 4 + t4];
+          a[mt][1] = As[(kk * BM + row + 8) * 4 + t4];
+        }
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+          const int col = wn * 32 + nt * 8 + g;
+          if (TRANSB)
+            b[nt] = Bs[(kk * BN + col) * 4 + t4];
+          else
+            b[nt] = Bs[((col >> 2) * BK + kk * 4 + t4) * 4 + (col & 3)];
+        }
+#pragma unroll
+        for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+          for (int nt = 0; nt < 4; nt++) dmma_m16n8k4(acc[mt][nt], a[mt], b[nt]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * stage);
+      if (++stage == STAGES) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+
+    // Epilogue: C = alpha*acc + beta*C; each thread owns pairs of adjacent
+    // columns (16-byte accesses when C allows it).
+    const int64_t m_base = tm * BM + wm * 64, n_base = tn * BN + wn * 32;
+    const bool vec_ok = ((ldc & 1) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+#pragma unroll
+    for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        const int64_t r = m_base + mt * 16 + g + 8 * h;
+        if (r >= M) continue;
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+          const int64_t c = n_base + nt * 8 + 2 * t4;
+          if (c >= N) continue;
+          // lower: columns beyond the diagonal of this row are not touched.
+          const int64_t lim = tiles.lower ? (r < N - 1 ? r : N - 1) : N - 1;
+          if (c > lim) continue;
+          double v0 = alpha * acc[mt][nt][2 * h], v1 = alpha * acc[mt][nt][2 * h + 1];
+          double *dst = C + r * ldc + c;
+          if (c + 1 <= lim) {
+            if (vec_ok) {
+              if (beta != 0.0) {
+                const double2 old = *reinterpret_cast<const double2 *>(dst);
+                v0 = fma(beta, old.x, v0);
+                v1 = fma(beta, old.y, v1);
+              }
+              *reinterpret_cast<double2 *>(dst) = make_double2(v0, v1);
+            } else {
+              if (beta != 0.0) {
+                v0 = fma(beta, dst[0], v0);
+                v1 = fma(beta, dst[1], v1);
+              }
+              dst[0] = v0;
+              dst[1] = v1;
+            }
+          } else {
+            if (beta != 0.0) v0 = fma(beta, dst[0], v0);
+            dst[0] = v0;
+          }
+        }
+      }
+  }
+}
+
+}  // namespace
+
+int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha, const double *A,
+                  int64_t lda, const double *B, int64_t ldb, bool transB, double beta, double *C,
+                  int64_t ldc, bool lower) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  // TMA rules: 16-byte aligned bases and row pitches; the 3-D views need K
+  // (and N for a row-major B) to be multiples of 4 elements.
+  if (K == 0 || (K % 4) != 0 || (lda % 2) != 0 || (ldb % 2) != 0 || !aligned16(A) ||
+      !aligned16(B))
+    return PGB200_ERR_UNSUPPORTED;
+  if (!transB && (N % 4) != 0) return PGB200_ERR_UNSUPPORTED;
+  if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31))
+    return PGB200_ERR_UNSUPPORTED;
+
+  CUtensorMap mapA, mapB;
+  {
+    const uint64_t dims[3] = {4, (uint64_t)M, (uint64_t)(K / 4)};
+    const uint64_t str[2] = {(uint64_t)lda * 8, 32};
+    const uint32_t box[3] = {4, BM, BK / 4};
+    PGB_TRY(encode_tensor_map(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 3, A, dims, str, box,
+                              CU_TENSOR_MAP_SWIZZLE_NONE));
+  }
+  if (transB) {
+    const uint64_t dims[3] = {4, (uint64_t)N, (uint64_t)(K / 4)};
+    const uint64_t str[2] = {(uint64_t)ldb * 8, 32};
+    const uint32_t box[3] = {4, BN, BK / 4};
+    PGB_TRY(encode_tensor_map(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 3, B, dims, str, box,
+                              CU_TENSOR_MAP_SWIZZLE_NONE));
+  } else {
+    const uint64_t dims[3] = {4, (uint64_t)K, (uint64_t)(N / 4)};
+    const uint64_t str[2] = {(uint64_t)ldb * 8, 32};
+    const uint32_t box[3] = {4, BK, BN / 4};
+    PGB_TRY(encode_tensor_map(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 3, B, dims, str, box,
+                              CU_TENSOR_MAP_SWIZZLE_NONE));
+  }
+  TileMap tiles;
+  tiles.tiles_m = (M + BM - 1) / BM;
+  tiles.tiles_n = (N + BN - 1) / BN;
+  tiles.lower = lower ? 1 : 0;
+  if (lower) {
+    // Square lower-triangular update only (row0 == 0, M == N).
+    if (M != N) return PGB200_ERR_UNSUPPORTED;
+    tiles.total = tiles.tiles_m * (tiles.tiles_m + 1) / 2;
+  } else {
+    tiles.total = tiles.tiles_m * tiles.tiles_n;
+  }
+  const unsigned grid = (unsigned)(tiles.total < rt->num_sms ? tiles.total : rt->num_sms);
+  if (transB) {
+    PGB_CUDA(cudaFuncSetAttribute(dmma_gemm_kernel<true>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    dmma_gemm_kernel<true><<<grid, THREADS, SMEM_BYTES, s>>>(mapA, mapB, M, N, K, alpha, beta, C,
+                                                              ldc, tiles, rt->status_dev);
+  } else {
+    PGB_CUDA(cudaFuncSetAttribute(dmma_gemm_kernel<false>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    dmma_gemm_kernel<false><<<grid, THREADS, SMEM_BYTES, s>>>(mapA, mapB, M, N, K, alpha, beta, C,
+                                                               ldc, tiles, rt->status_dev);
+  }
+  note_launch(PATH_DMMA);
+  PGB_CUDA(cudaGetLastError());
+  return PGB200_OK;
+}
+
+}  // namespace pgb200

@@ -1,0 +1,120 @@
+// Internal declarations shared by the translation units of libpgb200.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "pgb200.h"
+
+namespace pgb200 {
+
+// ---------------------------------------------------------------------------
+// Error convention: same message shape as the reference runtime wrappers
+// ("'<expr>' failed with '<msg>'", CudaRuntimeWrappers.cpp:29-50); the call
+// returns a status instead of aborting.
+// ---------------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+int32_t report_cuda(cudaError_t e, const char *expr);
+
+#define PGB_CUDA(expr)                                              \
+  do {                                                              \
+    cudaError_t e__ = (expr);                                       \
+    if (e__ != cudaSuccess) return ::pgb200::report_cuda(e__, #expr); \
+  } while (0)
+
+#define PGB_TRY(expr)                      \
+  do {                                     \
+    int32_t s__ = (expr);                  \
+    if (s__ != PGB200_OK) return s__;      \
+  } while (0)
+
+#define PGB_REQUIRE(cond, ...)             \
+  do {                                     \
+    if (!(cond)) {                         \
+      ::pgb200::set_error(__VA_ARGS__);    \
+      return PGB200_ERR_INVALID;           \
+    }                                      \
+  } while (0)
+
+enum Path : int32_t { PATH_NONE = 0, PATH_SIMT = 1, PATH_DMMA = 2, PATH_TCGEN05 = 3, PATH_STREAM = 4 };
+
+struct Runtime {
+  pgb200Config cfg;
+  int num_sms;
+  int cc_major;
+  // Device-visible status word in mapped pinned host memory: kernels store a
+  // non-zero code there when a bounded wait expires.
+  volatile int32_t *status_host;
+  int32_t *status_dev;
+};
+
+// Lazily initialises the runtime for the current device; fails (no CPU
+// fallback) when there is no sm_100 GPU.
+int32_t get_runtime(Runtime **rt);
+void note_launch(Path p, int n = 1);
+int log_level();
+
+// Per-(device,stream) scratch memory, grown on demand and kept until
+// pgb200Shutdown().  Contents are undefined between calls.
+int32_t get_workspace(cudaStream_t stream, size_t bytes, void **ptr);
+
+// cuTensorMapEncodeTiled looked up through the runtime (no link against
+// libcuda).  `dims`/`box` innermost first; `strides_bytes` for dims 1..rank-1.
+int32_t encode_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank,
+                          const void *base, const uint64_t *dims,
+                          const uint64_t *strides_bytes, const uint32_t *box,
+                          CUtensorMapSwizzle swizzle);
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// A caller array that may live on the host: staged to the device on demand.
+template <typename T>
+struct Staged {
+  T *dev = nullptr;       // pointer the kernels use
+  int64_t ld = 0;         // its leading dimension
+  T *host = nullptr;      // non-null when staged
+  int64_t host_ld = 0;
+  int64_t rows = 0, cols = 0;
+  bool copy_back = false;
+};
+
+bool is_host_pointer(const void *p);
+
+// in: copy host->device when staged; out: copy device->host in finish().
+template <typename T>
+int32_t stage(cudaStream_t s, const T *p, int64_t rows, int64_t cols, int64_t ld,
+              bool in, bool out, Staged<T> *st);
+template <typename T>
+int32_t finish(cudaStream_t s, Staged<T> *st);
+
+// ---------------------------------------------------------------------------
+// Kernel families (each in its own .cu).  All pointers are device pointers.
+// ---------------------------------------------------------------------------
+// Plain SIMT kernels: any size, any alignment.  transB: B(k,j) = B[j*ldb+k].
+// lower: only rows [row0,row1) x columns j<=i are computed and written.
+template <typename T>
+int32_t simt_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, T alpha, const T *A,
+                  int64_t lda, const T *B, int64_t ldb, bool transB, T beta, T *C,
+                  int64_t ldc, bool lower, int64_t row0);
+
+// fp64 DMMA path.  Returns PGB200_ERR_UNSUPPORTED when the operands do not
+// meet its alignment rules (the caller then takes the SIMT path).
+int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
+                  const double *A, int64_t lda, const double *B, int64_t ldb, bool transB,
+                  double beta, double *C, int64_t ldc, bool lower);
+
+// fp32 3xTF32 tcgen05 path; rows [row0,row0+M) of a lower-triangular update
+// when `lower`.  Same UNSUPPORTED convention.
+int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha,
+                    const float *A, int64_t lda, const float *B, int64_t ldb, bool transB,
+                    float beta, float *C, int64_t ldc, bool lower, int64_t row0);
+
+// HBM-streaming mat-vec: y1 = beta*y1 + alpha*A*x1 (if y1) and
+// y2 = beta*y2 + alpha*A^T*x2 (if y2) in one pass over A[MxN].
+int32_t stream_matvec(cudaStream_t s, int64_t M, int64_t N, const double *A, int64_t lda,
+                      double alpha, double beta, const double *x1, double *y1,
+                      const double *x2, double *y2);
+
+}  // namespace pgb200

@@ -1,0 +1,194 @@
+// HBM-streaming fp64 matrix-vector kernels.
+//
+// One pass over A[MxN] (row-major) produces, per tile, partial row dots
+// (for y1 = A*x1) and partial column sums (for y2 = A^T*x2); a second tiny
+// kernel adds the partials in a fixed order, so the result is deterministic
+// (no floating-point atomics).  With both outputs requested the pair of
+// PolyBench mvt nests (kernels/mvt/mvt.c:102-109) costs one read of A instead
+// of two.
+//
+// Tile = TR rows x TC columns per CTA iteration, 8 warps.  Warp w owns rows
+// w, w+8, ... of the tile; within a row, lane l loads 128-bit pairs at columns
+// 2l + 64q (q < Q), so every load instruction of a warp covers 512 contiguous
+// bytes.  Row dots are reduced with shuffles once per row; column sums stay in
+// registers for all rows of the tile and are combined across the 8 warps
+// through shared memory at the end of the tile.
+#include "pgb200_internal.h"
+
+namespace pgb200 {
+
+namespace {
+
+constexpr int MV_WARPS = 8;
+constexpr int MV_Q = 4;                    // 128-bit loads per lane per row
+constexpr int MV_TC = 64 * MV_Q;           // 256 columns per tile
+constexpr int MV_ROWS_PER_WARP = 32;
+constexpr int MV_TR = MV_WARPS * MV_ROWS_PER_WARP;  // 256 rows per tile
+constexpr int MV_RU = 4;                   // rows in flight per warp
+
+__device__ __forceinline__ double2 ldg_stream_v2(const double *p) {
+  double2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.f64 {%0,%1}, [%2];"
+               : "=d"(v.x), "=d"(v.y)
+               : "l"(p));
+  return v;
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(MV_WARPS * 32, 2)
+matvec_tile_kernel(const double *__restrict__ A, int64_t lda, int64_t M, int64_t N,
+                   const double *__restrict__ x1, const double *__restrict__ x2,
+                   double *__restrict__ p1 /* [tiles_c][M] */,
+                   double *__restrict__ p2 /* [tiles_r][N] */, int64_t tiles_r, int64_t tiles_c) {
+  __shared__ double red[MV_WARPS][MV_TC];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t ntiles = tiles_r * tiles_c;
+  for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int64_t tr = tile / tiles_c, tc = tile - tr * tiles_c;
+    const int64_t r0 = tr * MV_TR, c0 = tc * MV_TC;
+    double xv[MV_Q][2];
+    double colacc[MV_Q][2];
+#pragma unroll
+    for (int q = 0; q < MV_Q; q++) {
+      const int64_t c = c0 + 64 * q + 2 * lane;
+      xv[q][0] = (x1 && c < N) ? x1[c] : 0.0;
+      xv[q][1] = (x1 && c + 1 < N) ? x1[c + 1] : 0.0;
+      colacc[q][0] = 0.0;
+      colacc[q][1] = 0.0;
+    }
+    for (int it = 0; it < MV_ROWS_PER_WARP / MV_RU; it++) {
+      double a[MV_RU][MV_Q][2];
+      double w[MV_RU];
+#pragma unroll
+      for (int u = 0; u < MV_RU; u++) {
+        const int64_t r = r0 + warp + MV_WARPS * (it * MV_RU + u);
+        const bool rok = r < M;
+        w[u] = (x2 && rok) ? x2[r] : 0.0;
+        const double *row = A + r * lda;
+#pragma unroll
+        for (int q = 0; q < MV_Q; q++) {
+          const int64_t c = c0 + 64 * q + 2 * lane;
+          if (VEC) {
+            if (rok && c < N) {  // N even on this path: c+1 < N too
+              const double2 v = ldg_stream_v2(row + c);
+              a[u][q][0] = v.x;
+              a[u][q][1] = v.y;
+            } else {
+              a[u][q][0] = 0.0;
+              a[u][q][1] = 0.0;
+            }
+          } else {
+            a[u][q][0] = (rok && c < N) ? __ldg(row + c) : 0.0;
+            a[u][q][1] = (rok && c + 1 < N) ? __ldg(row + c + 1) : 0.0;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < MV_RU; u++) {
+        double dot = 0.0;
+#pragma unroll
+        for (int q = 0; q < MV_Q; q++) {
+          dot = fma(a[u][q][0], xv[q][0], dot);
+          dot = fma(a[u][q][1], xv[q][1], dot);
+          colacc[q][0] = fma(a[u][q][0], w[u], colacc[q][0]);
+          colacc[q][1] = fma(a[u][q][1], w[u], colacc[q][1]);
+        }
+        if (p1) {
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+          const int64_t r = r0 + warp + MV_WARPS * (it * MV_RU + u);
+          if (lane == 0 && r < M) p1[tc * M + r] = dot;
+        }
+      }
+    }
+    if (p2) {
+#pragma unroll
+      for (int q = 0; q < MV_Q; q++) {
+        red[warp][64 * q + 2 * lane] = colacc[q][0];
+        red[warp][64 * q + 2 * lane + 1] = colacc[q][1];
+      }
+      __syncthreads();
+      {
+        const int c = threadIdx.x;  // 256 threads, 256 columns
+        double sum = 0.0;
+#pragma unroll
+        for (int ww = 0; ww < MV_WARPS; ww++) sum += red[ww][c];
+        if (c0 + c < N) p2[tr * N + c0 + c] = sum;
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// y[i] = beta*y[i] + alpha * sum_p part[p*len + i], p ascending.
+__global__ void matvec_reduce_kernel(double *__restrict__ y, const double *__restrict__ part,
+                                     int64_t nparts, int64_t len, double alpha, double beta) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= len) return;
+  double sum = 0.0;
+  for (int64_t p = 0; p < nparts; p++) sum += part[p * len + i];
+  double v = alpha * sum;
+  if (beta != 0.0) v = fma(beta, y[i], v);
+  y[i] = v;
+}
+
+__global__ void vec_scale_kernel(double *y, int64_t len, double beta) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i < len) y[i] = (beta == 0.0) ? 0.0 : beta * y[i];
+}
+
+}  // namespace
+
+int32_t stream_matvec(cudaStream_t s, int64_t M, int64_t N, const double *A, int64_t lda,
+                      double alpha, double beta, const double *x1, double *y1, const double *x2,
+                      double *y2) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  if (!y1 && !y2) return PGB200_OK;
+  if (M == 0 || N == 0) {
+    // Empty sum: y = beta*y.
+    if (y1 && M > 0) {
+      vec_scale_kernel<<<(unsigned)((M + 255) / 256), 256, 0, s>>>(y1, M, beta);
+      note_launch(PATH_STREAM);
+    }
+    if (y2 && N > 0) {
+      vec_scale_kernel<<<(unsigned)((N + 255) / 256), 256, 0, s>>>(y2, N, beta);
+      note_launch(PATH_STREAM);
+    }
+    PGB_CUDA(cudaGetLastError());
+    return PGB200_OK;
+  }
+  const int64_t tiles_r = (M + MV_TR - 1) / MV_TR, tiles_c = (N + MV_TC - 1) / MV_TC;
+  const size_t n1 = y1 ? (size_t)tiles_c * M : 0, n2 = y2 ? (size_t)tiles_r * N : 0;
+  void *ws = nullptr;
+  PGB_TRY(get_workspace(s, (n1 + n2) * sizeof(double), &ws));
+  double *p1 = y1 ? static_cast<double *>(ws) : nullptr;
+  double *p2 = y2 ? static_cast<double *>(ws) + n1 : nullptr;
+  const int64_t ntiles = tiles_r * tiles_c;
+  const int64_t cap = (int64_t)rt->num_sms * 2;
+  const unsigned grid = (unsigned)(ntiles < cap ? ntiles : cap);
+  const bool vec = aligned16(A) && (lda % 2 == 0) && (N % 2 == 0);
+  if (vec)
+    matvec_tile_kernel<true><<<grid, MV_WARPS * 32, 0, s>>>(A, lda, M, N, y1 ? x1 : nullptr,
+                                                            y2 ? x2 : nullptr, p1, p2, tiles_r,
+                                                            tiles_c);
+  else
+    matvec_tile_kernel<false><<<grid, MV_WARPS * 32, 0, s>>>(A, lda, M, N, y1 ? x1 : nullptr,
+                                                             y2 ? x2 : nullptr, p1, p2, tiles_r,
+                                                             tiles_c);
+  note_launch(PATH_STREAM);
+  if (y1) {
+    matvec_reduce_kernel<<<(unsigned)((M + 255) / 256), 256, 0, s>>>(y1, p1, tiles_c, M, alpha,
+                                                                     beta);
+    note_launch(PATH_STREAM);
+  }
+  if (y2) {
+    matvec_reduce_kernel<<<(unsigned)((N + 255) / 256), 256, 0, s>>>(y2, p2, tiles_r, N, alpha,
+                                                                     beta);
+    note_launch(PATH_STREAM);
+  }
+  PGB_CUDA(cudaGetLastError());
+  return PGB200_OK;
+}
+
+}  // namespace pgb200

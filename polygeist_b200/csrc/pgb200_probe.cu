@@ -1,0 +1,169 @@
+// Peak probes: the roofline denominators that a plain copy / bf16 GEMM
+// measurement does not give - fp64 tensor (DMMA) and fp64 FMA issue rate from
+// register-only loops, and a read-only HBM sweep.  Harness utilities, timed with
+// CUDA events inside the call.
+#include "pgb200_internal.h"
+
+namespace pgb200 {
+namespace {
+
+template <int SHAPE>  // 4, 8, 16: m16n8k{4,8,16}; 0: m8n8k4
+__global__ void __launch_bounds__(512) dmma_probe_kernel(double *sink, int iters, double seed) {
+  double acc[8][4];
+#pragma unroll
+  for (int c = 0; c < 8; c++)
+#pragma unroll
+    for (int r = 0; r < 4; r++) acc[c][r] = seed * (c + r);
+  double a[8], b[4];
+#pragma unroll
+  for (int i = 0; i < 8; i++) a[i] = seed + i * 1e-9 + threadIdx.x * 1e-12;
+#pragma unroll
+  for (int i = 0; i < 4; i++) b[i] = seed - i * 1e-9;
+  for (int it = 0; it < iters; it++) {
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+      if (SHAPE == 4)
+        asm volatile(
+            "mma.sync.aligned.m16n8k4.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5}, {%6}, "
+            "{%0,%1,%2,%3};"
+            : "+d"(acc[c][0]), "+d"(acc[c][1]), "+d"(acc[c][2]), "+d"(acc[c][3])
+            : "d"(a[0]), "d"(a[1]), "d"(b[0]));
+      else if (SHAPE == 8)
+        asm volatile(
+            "mma.sync.aligned.m16n8k8.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+            "{%8,%9}, {%0,%1,%2,%3};"
+            : "+d"(acc[c][0]), "+d"(acc[c][1]), "+d"(acc[c][2]), "+d"(acc[c][3])
+            : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(b[0]), "d"(b[1]));
+      else if (SHAPE == 16)
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, "
+            "{%4,%5,%6,%7,%8,%9,%10,%11}, {%12,%13,%14,%15}, {%0,%1,%2,%3};"
+            : "+d"(acc[c][0]), "+d"(acc[c][1]), "+d"(acc[c][2]), "+d"(acc[c][3])
+            : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(a[4]), "d"(a[5]), "d"(a[6]),
+              "d"(a[7]), "d"(b[0]), "d"(b[1]), "d"(b[2]), "d"(b[3]));
+      else
+        asm volatile(
+            "mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+            : "+d"(acc[c][0]), "+d"(acc[c][1])
+            : "d"(a[0]), "d"(b[0]));
+    }
+  }
+  double s = 0;
+#pragma unroll
+  for (int c = 0; c < 8; c++)
+#pragma unroll
+    for (int r = 0; r < 4; r++) s += acc[c][r];
+  if (s == 123.456) sink[0] = s;
+}
+
+__global__ void __launch_bounds__(512) dfma_probe_kernel(double *sink, int iters, double seed) {
+  double acc[16];
+#pragma unroll
+  for (int c = 0; c < 16; c++) acc[c] = seed * c;
+  const double a = seed + threadIdx.x * 1e-12, b = 1.0 - seed * 1e-9;
+  for (int it = 0; it < iters; it++) {
+#pragma unroll
+    for (int c = 0; c < 16; c++) acc[c] = fma(acc[c], b, a);
+  }
+  double s = 0;
+#pragma unroll
+  for (int c = 0; c < 16; c++) s += acc[c];
+  if (s == 123.456) sink[0] = s;
+}
+
+__global__ void __launch_bounds__(512) hbm_read_probe_kernel(const double2 *__restrict__ src,
+                                                             int64_t n16, double *sink) {
+  double s = 0;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n16; i += 4 * stride) {
+    double2 v0, v1, v2, v3;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.f64 {%0,%1}, [%2];" : "=d"(v0.x), "=d"(v0.y) : "l"(src + i));
+    asm volatile("ld.global.nc.L1::no_allocate.v2.f64 {%0,%1}, [%2];" : "=d"(v1.x), "=d"(v1.y) : "l"(src + i + stride));
+    asm volatile("ld.global.nc.L1::no_allocate.v2.f64 {%0,%1}, [%2];" : "=d"(v2.x), "=d"(v2.y) : "l"(src + i + 2 * stride));
+    asm volatile("ld.global.nc.L1::no_allocate.v2.f64 {%0,%1}, [%2];" : "=d"(v3.x), "=d"(v3.y) : "l"(src + i + 3 * stride));
+    s += v0.x + v0.y + v1.x + v1.y + v2.x + v2.y + v3.x + v3.y;
+  }
+  for (; i < n16; i += stride) s += src[i].x + src[i].y;
+  if (s == 123.456) sink[0] = s;
+}
+
+template <typename F>
+int32_t time_best(cudaStream_t s, int reps, F launch, float *best_ms) {
+  cudaEvent_t e0, e1;
+  PGB_CUDA(cudaEventCreate(&e0));
+  PGB_CUDA(cudaEventCreate(&e1));
+  float best = 1e30f;
+  for (int r = 0; r < reps + 2; r++) {
+    PGB_CUDA(cudaEventRecord(e0, s));
+    launch();
+    PGB_CUDA(cudaEventRecord(e1, s));
+    PGB_CUDA(cudaEventSynchronize(e1));
+    float ms = 0;
+    PGB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    if (r >= 2 && ms < best) best = ms;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  PGB_CUDA(cudaGetLastError());
+  *best_ms = best;
+  return PGB200_OK;
+}
+
+}  // namespace
+}  // namespace pgb200
+
+using namespace pgb200;
+
+extern "C" int32_t pgb200ProbePeak(void *stream, int32_t kind, double *out) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(out, "ProbePeak: out is null");
+  cudaStream_t s = (cudaStream_t)stream;
+  void *ws = nullptr;
+  const int grid = rt->num_sms * 2, threads = 512, iters = 2048;
+  float ms = 0;
+  if (kind == 0 || kind == 10 || kind == 11 || kind == 12 || kind == 13) {
+    PGB_TRY(get_workspace(s, 4096, &ws));
+    double *sink = static_cast<double *>(ws);
+    double best = 0;
+    const int shapes[4] = {4, 8, 16, 0};
+    for (int i = 0; i < 4; i++) {
+      if (kind != 0 && kind != 10 + i) continue;
+      const int sh = shapes[i];
+      PGB_TRY(time_best(s, 5, [&] {
+        if (sh == 4) dmma_probe_kernel<4><<<grid, threads, 0, s>>>(sink, iters, 1e-3);
+        if (sh == 8) dmma_probe_kernel<8><<<grid, threads, 0, s>>>(sink, iters, 1e-3);
+        if (sh == 16) dmma_probe_kernel<16><<<grid, threads, 0, s>>>(sink, iters, 1e-3);
+        if (sh == 0) dmma_probe_kernel<0><<<grid, threads, 0, s>>>(sink, iters, 1e-3);
+      }, &ms));
+      const double mnk = sh == 0 ? 8.0 * 8 * 4 : 16.0 * 8 * sh;
+      const double flop = 2.0 * mnk * 8 * iters * (threads / 32) * (double)grid;
+      const double gf = flop / (ms * 1e-3) * 1e-9;
+      if (gf > best) best = gf;
+    }
+    *out = best;
+    return PGB200_OK;
+  }
+  if (kind == 1) {
+    PGB_TRY(get_workspace(s, 4096, &ws));
+    double *sink = static_cast<double *>(ws);
+    PGB_TRY(time_best(s, 5, [&] { dfma_probe_kernel<<<grid, threads, 0, s>>>(sink, iters * 8, 1e-3); }, &ms));
+    *out = 2.0 * 16 * iters * 8 * threads * (double)grid / (ms * 1e-3) * 1e-9;
+    return PGB200_OK;
+  }
+  if (kind == 2) {
+    const size_t bytes = size_t(2) << 30;
+    PGB_TRY(get_workspace(s, bytes, &ws));
+    PGB_CUDA(cudaMemsetAsync(ws, 0, bytes, s));
+    double *sink = static_cast<double *>(ws);
+    PGB_TRY(time_best(s, 5, [&] {
+      hbm_read_probe_kernel<<<rt->num_sms * 4, threads, 0, s>>>(
+          reinterpret_cast<const double2 *>(static_cast<char *>(ws) + 4096), (int64_t)((bytes - 4096) / 16), sink);
+    }, &ms));
+    *out = (double)(bytes - 4096) / (ms * 1e-3) * 1e-9;
+    return PGB200_OK;
+  }
+  set_error("ProbePeak: unknown kind %d", kind);
+  return PGB200_ERR_INVALID;
+}

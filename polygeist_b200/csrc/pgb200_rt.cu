@@ -1,0 +1,543 @@
+// libpgb200 runtime: life cycle, error reporting, pointer classification and
+// staging, scratch memory, tensor-map encoding, the harness generator, and the
+// exported C ABI that dispatches to the kernel families.
+#include <stdarg.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <utility>
+
+#include "pgb200_internal.h"
+
+namespace pgb200 {
+
+static thread_local char tls_error[512] = "";
+static thread_local int32_t tls_path = PATH_NONE;
+static thread_local int64_t tls_launches = 0;
+
+static std::mutex g_mu;
+static bool g_have_cfg = false;
+static pgb200Config g_cfg = {};
+static std::map<int, Runtime *> g_rt;  // per device
+struct Ws {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+};
+static std::map<std::pair<int, cudaStream_t>, Ws> g_ws;
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tls_error, sizeof(tls_error), fmt, ap);
+  va_end(ap);
+  fprintf(stderr, "pgb200: %s\n", tls_error);
+}
+
+int32_t report_cuda(cudaError_t e, const char *expr) {
+  snprintf(tls_error, sizeof(tls_error), "'%s' failed with '%s'", expr, cudaGetErrorName(e));
+  fprintf(stderr, "%s\n", tls_error);
+  return PGB200_ERR_CUDA;
+}
+
+int log_level() { return g_have_cfg ? g_cfg.log_level : 0; }
+
+void note_launch(Path p, int n) {
+  tls_path = p;
+  tls_launches += n;
+}
+
+int32_t get_runtime(Runtime **out) {
+  int dev = 0;
+  PGB_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_rt.find(dev);
+  if (it != g_rt.end()) {
+    *out = it->second;
+    return PGB200_OK;
+  }
+  cudaDeviceProp prop;
+  PGB_CUDA(cudaGetDeviceProperties(&prop, dev));
+  if (prop.major != 10) {
+    set_error("device %d is sm_%d%d; libpgb200 kernels are built for sm_100a only", dev,
+              prop.major, prop.minor);
+    return PGB200_ERR_UNSUPPORTED;
+  }
+  Runtime *rt = new Runtime();
+  rt->cfg = g_cfg;
+  rt->num_sms = prop.multiProcessorCount;
+  rt->cc_major = prop.major;
+  void *h = nullptr;
+  PGB_CUDA(cudaHostAlloc(&h, sizeof(int32_t) * 4, cudaHostAllocMapped));
+  memset(h, 0, sizeof(int32_t) * 4);
+  rt->status_host = static_cast<volatile int32_t *>(h);
+  void *d = nullptr;
+  PGB_CUDA(cudaHostGetDevicePointer(&d, h, 0));
+  rt->status_dev = static_cast<int32_t *>(d);
+  if (!g_encode) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    PGB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (!fn || q != cudaDriverEntryPointSuccess) {
+      set_error("cuTensorMapEncodeTiled is not available from this driver");
+      return PGB200_ERR_UNSUPPORTED;
+    }
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  g_rt[dev] = rt;
+  *out = rt;
+  return PGB200_OK;
+}
+
+int32_t get_workspace(cudaStream_t stream, size_t bytes, void **ptr) {
+  int dev = 0;
+  PGB_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(g_mu);
+  Ws &w = g_ws[std::make_pair(dev, stream)];
+  if (w.bytes < bytes) {
+    if (w.ptr) {
+      // The old block may still be in use by work queued on `stream`.
+      PGB_CUDA(cudaStreamSynchronize(stream));
+      PGB_CUDA(cudaFree(w.ptr));
+      w.ptr = nullptr;
+      w.bytes = 0;
+    }
+    size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    PGB_CUDA(cudaMalloc(&w.ptr, want));
+    w.bytes = want;
+  }
+  *ptr = w.ptr;
+  return PGB200_OK;
+}
+
+int32_t encode_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank,
+                          const void *base, const uint64_t *dims,
+                          const uint64_t *strides_bytes, const uint32_t *box,
+                          CUtensorMapSwizzle swizzle) {
+  cuuint64_t d[5], st[5];
+  cuuint32_t b[5], es[5];
+  for (int i = 0; i < rank; i++) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) st[i] = strides_bytes[i];
+  }
+  CUresult r = g_encode(map, dtype, (cuuint32_t)rank, const_cast<void *>(base), d, st, b, es,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("'cuTensorMapEncodeTiled' failed with 'CUresult %d'", (int)r);
+    return PGB200_ERR_CUDA;
+  }
+  return PGB200_OK;
+}
+
+bool is_host_pointer(const void *p) {
+  cudaPointerAttributes a;
+  cudaError_t e = cudaPointerGetAttributes(&a, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return true;
+  }
+  return a.type == cudaMemoryTypeUnregistered || a.type == cudaMemoryTypeHost;
+}
+
+template <typename T>
+int32_t stage(cudaStream_t s, const T *p, int64_t rows, int64_t cols, int64_t ld, bool in,
+              bool out, Staged<T> *st) {
+  st->rows = rows;
+  st->cols = cols;
+  if (rows == 0 || cols == 0 || !is_host_pointer(p)) {
+    st->dev = const_cast<T *>(p);
+    st->ld = ld;
+    st->host = nullptr;
+    return PGB200_OK;
+  }
+  st->host = const_cast<T *>(p);
+  st->host_ld = ld;
+  st->copy_back = out;
+  // Pad the device pitch to 16 bytes so staged operands always meet the
+  // alignment rules of the tensor-core paths.
+  const int64_t per16 = 16 / (int64_t)sizeof(T);
+  st->ld = (cols + per16 - 1) / per16 * per16;
+  void *d = nullptr;
+  PGB_CUDA(cudaMallocAsync(&d, (size_t)rows * st->ld * sizeof(T), s));
+  st->dev = static_cast<T *>(d);
+  if (in)
+    PGB_CUDA(cudaMemcpy2DAsync(st->dev, st->ld * sizeof(T), p, ld * sizeof(T), cols * sizeof(T),
+                               rows, cudaMemcpyHostToDevice, s));
+  return PGB200_OK;
+}
+
+template <typename T>
+int32_t finish(cudaStream_t s, Staged<T> *st) {
+  if (!st->host) return PGB200_OK;
+  if (st->copy_back)
+    PGB_CUDA(cudaMemcpy2DAsync(st->host, st->host_ld * sizeof(T), st->dev, st->ld * sizeof(T),
+                               st->cols * sizeof(T), st->rows, cudaMemcpyDeviceToHost, s));
+  PGB_CUDA(cudaFreeAsync(st->dev, s));
+  st->host = nullptr;
+  return PGB200_OK;
+}
+
+template int32_t stage<double>(cudaStream_t, const double *, int64_t, int64_t, int64_t, bool,
+                               bool, Staged<double> *);
+template int32_t stage<float>(cudaStream_t, const float *, int64_t, int64_t, int64_t, bool, bool,
+                              Staged<float> *);
+template int32_t finish<double>(cudaStream_t, Staged<double> *);
+template int32_t finish<float>(cudaStream_t, Staged<float> *);
+
+// ---------------------------------------------------------------------------
+// Harness generator (see pgb200.h for the recurrence).
+// ---------------------------------------------------------------------------
+__host__ __device__ inline uint64_t splitmix64(uint64_t z) {
+  z += 0x9e3779b97f4a7c15ull;
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+  return z ^ (z >> 31);
+}
+
+__global__ void fill_f64_kernel(double *dst, int64_t row0, int64_t rows, int64_t cols,
+                                int64_t ld, uint64_t h, double lo, double span) {
+  const int64_t total = rows * cols;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const uint64_t x = splitmix64(h + (uint64_t)((row0 + r) * cols + c));
+    const double u = __dmul_rn((double)(x >> 11), 0x1.0p-53);
+    dst[r * ld + c] = __dadd_rn(lo, __dmul_rn(span, u));
+  }
+}
+
+__global__ void fill_f32_kernel(float *dst, int64_t row0, int64_t rows, int64_t cols, int64_t ld,
+                                uint64_t h, float lo, float span) {
+  const int64_t total = rows * cols;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const uint64_t x = splitmix64(h + (uint64_t)((row0 + r) * cols + c));
+    const float u = __fmul_rn((float)(uint32_t)(x >> 40), 0x1.0p-24f);
+    dst[r * ld + c] = __fadd_rn(lo, __fmul_rn(span, u));
+  }
+}
+
+static int fill_grid(int64_t total, int sms) {
+  int64_t g = (total + 255) / 256;
+  int64_t cap = (int64_t)sms * 16;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace pgb200
+
+using namespace pgb200;
+
+// ===========================================================================
+// Exported C ABI
+// ===========================================================================
+extern "C" {
+
+int32_t pgb200Init(const pgb200Config *cfg) {
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (cfg) g_cfg = *cfg;
+    g_have_cfg = true;
+    for (auto &kv : g_rt) kv.second->cfg = g_cfg;
+  }
+  Runtime *rt = nullptr;
+  return get_runtime(&rt);
+}
+
+int32_t pgb200Shutdown(void) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  int cur = 0;
+  cudaGetDevice(&cur);
+  for (auto &kv : g_ws) {
+    cudaSetDevice(kv.first.first);
+    cudaDeviceSynchronize();
+    if (kv.second.ptr) cudaFree(kv.second.ptr);
+  }
+  g_ws.clear();
+  for (auto &kv : g_rt) {
+    cudaSetDevice(kv.first);
+    cudaFreeHost(const_cast<int32_t *>(kv.second->status_host));
+    delete kv.second;
+  }
+  g_rt.clear();
+  cudaSetDevice(cur);
+  return PGB200_OK;
+}
+
+const char *pgb200GetLastErrorString(void) { return tls_error; }
+int32_t pgb200Version(void) { return 100; }
+int32_t pgb200LastPath(void) { return tls_path; }
+int64_t pgb200LaunchCount(void) { return tls_launches; }
+
+int32_t pgb200PollDeviceStatus(void) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  int32_t v = rt->status_host[0];
+  if (v != 0) {
+    set_error("a device-side bounded wait expired (code %d, detail %d)", v, rt->status_host[1]);
+    rt->status_host[0] = 0;
+    rt->status_host[1] = 0;
+    return PGB200_ERR_TIMEOUT;
+  }
+  return PGB200_OK;
+}
+
+int32_t pgb200FillUniformF64(void *stream, double *dst, int64_t row0, int64_t rows, int64_t cols,
+                             int64_t ld, uint64_t seed, uint32_t array_id, double lo, double hi) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(dst && rows >= 0 && cols >= 0 && ld >= cols, "FillUniformF64: bad arguments");
+  if (rows * cols == 0) return PGB200_OK;
+  PGB_REQUIRE(!is_host_pointer(dst), "FillUniformF64: dst must be device memory");
+  const uint64_t h = splitmix64(seed ^ ((uint64_t)array_id << 56));
+  fill_f64_kernel<<<fill_grid(rows * cols, rt->num_sms), 256, 0, (cudaStream_t)stream>>>(
+      dst, row0, rows, cols, ld, h, lo, hi - lo);
+  note_launch(PATH_SIMT);
+  PGB_CUDA(cudaGetLastError());
+  return PGB200_OK;
+}
+
+int32_t pgb200FillUniformF32(void *stream, float *dst, int64_t row0, int64_t rows, int64_t cols,
+                             int64_t ld, uint64_t seed, uint32_t array_id, float lo, float hi) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(dst && rows >= 0 && cols >= 0 && ld >= cols, "FillUniformF32: bad arguments");
+  if (rows * cols == 0) return PGB200_OK;
+  PGB_REQUIRE(!is_host_pointer(dst), "FillUniformF32: dst must be device memory");
+  const uint64_t h = splitmix64(seed ^ ((uint64_t)array_id << 56));
+  fill_f32_kernel<<<fill_grid(rows * cols, rt->num_sms), 256, 0, (cudaStream_t)stream>>>(
+      dst, row0, rows, cols, ld, h, lo, hi - lo);
+  note_launch(PATH_SIMT);
+  PGB_CUDA(cudaGetLastError());
+  return PGB200_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// GEMM / SYRK dispatch: validate, stage host operands, pick the kernel family.
+// ---------------------------------------------------------------------------
+namespace pgb200 {
+
+static int32_t fast_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
+                         const double *A, int64_t lda, const double *B, int64_t ldb, bool transB,
+                         double beta, double *C, int64_t ldc, bool lower, int64_t row0) {
+  if (row0 != 0) return PGB200_ERR_UNSUPPORTED;
+  return dmma_gemm(s, M, N, K, alpha, A, lda, B, ldb, transB, beta, C, ldc, lower);
+}
+static int32_t fast_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha,
+                         const float *A, int64_t lda, const float *B, int64_t ldb, bool transB,
+                         float beta, float *C, int64_t ldc, bool lower, int64_t row0) {
+  return tf32x3_gemm(s, M, N, K, alpha, A, lda, B, ldb, transB, beta, C, ldc, lower, row0);
+}
+
+// Device-pointer core shared by gemm and syrk.
+template <typename T>
+static int32_t gemm_device(cudaStream_t s, int64_t M, int64_t N, int64_t K, T alpha, const T *A,
+                           int64_t lda, const T *B, int64_t ldb, bool transB, T beta, T *C,
+                           int64_t ldc, bool lower, int64_t row0) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  if (M == 0 || N == 0) return PGB200_OK;
+  if (!rt->cfg.force_generic) {
+    int32_t st = fast_gemm(s, M, N, K, alpha, A, lda, B, ldb, transB, beta, C, ldc, lower, row0);
+    if (st != PGB200_ERR_UNSUPPORTED) return st;
+  }
+  return simt_gemm<T>(s, M, N, K, alpha, A, lda, B, ldb, transB, beta, C, ldc, lower, row0);
+}
+
+template <typename T>
+static int32_t gemm_entry(void *stream, int64_t M, int64_t N, int64_t K, T alpha, const T *A,
+                          int64_t lda, const T *B, int64_t ldb, T beta, T *C, int64_t ldc) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative size (M=%lld N=%lld K=%lld)",
+              (long long)M, (long long)N, (long long)K);
+  if (M == 0 || N == 0) return PGB200_OK;
+  PGB_REQUIRE(C && ldc >= N, "gemm: C is null or ldc (%lld) < N (%lld)", (long long)ldc,
+              (long long)N);
+  PGB_REQUIRE(K == 0 || (A && B && lda >= K && ldb >= N),
+              "gemm: A/B null or lda (%lld) < K (%lld) or ldb (%lld) < N (%lld)", (long long)lda,
+              (long long)K, (long long)ldb, (long long)N);
+  cudaStream_t s = (cudaStream_t)stream;
+  Staged<T> sa, sb, sc;
+  PGB_TRY(stage<T>(s, A, M, K, lda, true, false, &sa));
+  PGB_TRY(stage<T>(s, B, K, N, ldb, true, false, &sb));
+  PGB_TRY(stage<T>(s, C, M, N, ldc, beta != (T)0, true, &sc));
+  const bool staged = sa.host || sb.host || sc.host;
+  int32_t st = gemm_device<T>(s, M, N, K, alpha, sa.dev, sa.ld, sb.dev, sb.ld, false, beta,
+                              sc.dev, sc.ld, false, 0);
+  PGB_TRY(finish(s, &sa));
+  PGB_TRY(finish(s, &sb));
+  PGB_TRY(finish(s, &sc));
+  if (staged) PGB_CUDA(cudaStreamSynchronize(s));
+  return st;
+}
+
+template <typename T>
+static int32_t syrk_entry(void *stream, int64_t N, int64_t K, int64_t row0, int64_t row1, T alpha,
+                          const T *A, int64_t lda, T beta, T *C, int64_t ldc) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(N >= 0 && K >= 0 && row0 >= 0 && row0 <= row1 && row1 <= N,
+              "syrk: bad sizes (N=%lld K=%lld rows [%lld,%lld))", (long long)N, (long long)K,
+              (long long)row0, (long long)row1);
+  if (row1 == row0) return PGB200_OK;
+  PGB_REQUIRE(C && ldc >= N, "syrk: C is null or ldc (%lld) < N (%lld)", (long long)ldc,
+              (long long)N);
+  PGB_REQUIRE(K == 0 || (A && lda >= K), "syrk: A is null or lda (%lld) < K (%lld)",
+              (long long)lda, (long long)K);
+  cudaStream_t s = (cudaStream_t)stream;
+  Staged<T> sa, sc;
+  PGB_TRY(stage<T>(s, A, row1, K, lda, true, false, &sa));
+  // The whole row block of C travels both ways; its strict upper triangle is
+  // never touched on the device, so it comes back unchanged.
+  PGB_TRY(stage<T>(s, C + row0 * ldc, row1 - row0, N, ldc, true, true, &sc));
+  const bool staged = sa.host || sc.host;
+  // Rows [row0,row1) of C against columns [0,row1): an (row1-row0) x row1
+  // product A[row0:row1,:] * A[0:row1,:]^T masked to j <= i.
+  int32_t st = gemm_device<T>(s, row1 - row0, row1, K, alpha, sa.dev + row0 * sa.ld, sa.ld,
+                              sa.dev, sa.ld, true, beta, sc.dev, sc.ld, true, row0);
+  PGB_TRY(finish(s, &sa));
+  PGB_TRY(finish(s, &sc));
+  if (staged) PGB_CUDA(cudaStreamSynchronize(s));
+  return st;
+}
+
+static int32_t matvec_entry(void *stream, int64_t M, int64_t N, const double *A, int64_t lda,
+                            double alpha, double beta, const double *x1, double *y1,
+                            const double *x2, double *y2) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(M >= 0 && N >= 0, "matvec: negative size");
+  PGB_REQUIRE(M == 0 || N == 0 || (A && lda >= N), "matvec: A is null or lda (%lld) < N (%lld)",
+              (long long)lda, (long long)N);
+  PGB_REQUIRE((!y1 || x1 || N == 0) && (!y2 || x2 || M == 0), "matvec: null vector");
+  cudaStream_t s = (cudaStream_t)stream;
+  Staged<double> sa, sx1, sy1, sx2, sy2;
+  PGB_TRY(stage<double>(s, A, M, N, lda, true, false, &sa));
+  if (y1) {
+    PGB_TRY(stage<double>(s, x1, 1, N, N, true, false, &sx1));
+    PGB_TRY(stage<double>(s, y1, 1, M, M, beta != 0.0, true, &sy1));
+  }
+  if (y2) {
+    PGB_TRY(stage<double>(s, x2, 1, M, M, true, false, &sx2));
+    PGB_TRY(stage<double>(s, y2, 1, N, N, beta != 0.0, true, &sy2));
+  }
+  const bool staged = sa.host || sx1.host || sy1.host || sx2.host || sy2.host;
+  int32_t st = stream_matvec(s, M, N, sa.dev, sa.ld, alpha, beta, y1 ? sx1.dev : nullptr,
+                             y1 ? sy1.dev : nullptr, y2 ? sx2.dev : nullptr,
+                             y2 ? sy2.dev : nullptr);
+  PGB_TRY(finish(s, &sa));
+  PGB_TRY(finish(s, &sx1));
+  PGB_TRY(finish(s, &sy1));
+  PGB_TRY(finish(s, &sx2));
+  PGB_TRY(finish(s, &sy2));
+  if (staged) PGB_CUDA(cudaStreamSynchronize(s));
+  return st;
+}
+
+}  // namespace pgb200
+
+extern "C" {
+
+int32_t pgb200Dgemm(void *stream, int64_t M, int64_t N, int64_t K, double alpha, const double *A,
+                    int64_t lda, const double *B, int64_t ldb, double beta, double *C,
+                    int64_t ldc) {
+  return gemm_entry<double>(stream, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
+}
+
+int32_t pgb200Sgemm(void *stream, int64_t M, int64_t N, int64_t K, float alpha, const float *A,
+                    int64_t lda, const float *B, int64_t ldb, float beta, float *C, int64_t ldc) {
+  return gemm_entry<float>(stream, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
+}
+
+int32_t pgb200Dsyrk(void *stream, int64_t N, int64_t K, double alpha, const double *A,
+                    int64_t lda, double beta, double *C, int64_t ldc) {
+  return syrk_entry<double>(stream, N, K, 0, N, alpha, A, lda, beta, C, ldc);
+}
+
+int32_t pgb200Ssyrk(void *stream, int64_t N, int64_t K, float alpha, const float *A, int64_t lda,
+                    float beta, float *C, int64_t ldc) {
+  return syrk_entry<float>(stream, N, K, 0, N, alpha, A, lda, beta, C, ldc);
+}
+
+int32_t pgb200SsyrkRows(void *stream, int64_t N, int64_t K, int64_t row0, int64_t row1,
+                        float alpha, const float *A, int64_t lda, float beta, float *C,
+                        int64_t ldc) {
+  return syrk_entry<float>(stream, N, K, row0, row1, alpha, A, lda, beta, C, ldc);
+}
+
+int32_t pgb200Dgemv(void *stream, int32_t transA, int64_t M, int64_t N, double alpha,
+                    const double *A, int64_t lda, const double *x, double beta, double *y) {
+  PGB_REQUIRE(y || (transA ? N : M) == 0, "gemv: y is null");
+  if (transA) return matvec_entry(stream, M, N, A, lda, alpha, beta, nullptr, nullptr, x, y);
+  return matvec_entry(stream, M, N, A, lda, alpha, beta, x, y, nullptr, nullptr);
+}
+
+int32_t pgb200Dmvt(void *stream, int64_t N, const double *A, int64_t lda, const double *y1,
+                   const double *y2, double *x1, double *x2) {
+  PGB_REQUIRE(N == 0 || (x1 && x2 && y1 && y2), "mvt: null vector");
+  return matvec_entry(stream, N, N, A, lda, 1.0, 1.0, y1, x1, y2, x2);
+}
+
+// ---- host-array drop-ins with the reference's signatures -------------------
+
+int32_t pgb200_kernel_gemm(int ni, int nj, int nk, double alpha, double beta, double *C,
+                           const double *A, const double *B) {
+  return pgb200Dgemm(nullptr, ni, nj, nk, alpha, A, nk, B, nj, beta, C, nj);
+}
+
+int32_t pgb200_kernel_gemm_f32(int ni, int nj, int nk, float alpha, float beta, float *C,
+                               const float *A, const float *B) {
+  return pgb200Sgemm(nullptr, ni, nj, nk, alpha, A, nk, B, nj, beta, C, nj);
+}
+
+int32_t pgb200_kernel_2mm(int ni, int nj, int nk, int nl, double alpha, double beta, double *tmp,
+                          const double *A, const double *B, const double *C, double *D) {
+  // tmp = alpha*A*B stays in HBM between the two contractions; it is copied
+  // back once because the C source leaves it as a live-out array.
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(ni >= 0 && nj >= 0 && nk >= 0 && nl >= 0, "kernel_2mm: negative size");
+  cudaStream_t s = nullptr;
+  Staged<double> sa, sb, sc, sd, st;
+  PGB_TRY(stage<double>(s, A, ni, nk, nk, true, false, &sa));
+  PGB_TRY(stage<double>(s, B, nk, nj, nj, true, false, &sb));
+  PGB_TRY(stage<double>(s, C, nj, nl, nl, true, false, &sc));
+  PGB_TRY(stage<double>(s, D, ni, nl, nl, beta != 0.0, true, &sd));
+  PGB_TRY(stage<double>(s, tmp, ni, nj, nj, false, true, &st));
+  int32_t r = pgb200Dgemm(s, ni, nj, nk, alpha, sa.dev, sa.ld, sb.dev, sb.ld, 0.0, st.dev, st.ld);
+  if (r == PGB200_OK)
+    r = pgb200Dgemm(s, ni, nl, nj, 1.0, st.dev, st.ld, sc.dev, sc.ld, beta, sd.dev, sd.ld);
+  PGB_TRY(finish(s, &sa));
+  PGB_TRY(finish(s, &sb));
+  PGB_TRY(finish(s, &sc));
+  PGB_TRY(finish(s, &sd));
+  PGB_TRY(finish(s, &st));
+  PGB_CUDA(cudaStreamSynchronize(s));
+  return r;
+}
+
+int32_t pgb200_kernel_mvt(int n, double *x1, double *x2, const double *y_1, const double *y_2,
+                          const double *A) {
+  return pgb200Dmvt(nullptr, n, A, n, y_1, y_2, x1, x2);
+}
+
+int32_t pgb200_kernel_syrk(int n, int m, double alpha, double beta, double *C, const double *A) {
+  return pgb200Dsyrk(nullptr, n, m, alpha, A, m, beta, C, n);
+}
+
+int32_t pgb200_kernel_syrk_f32(int n, int m, float alpha, float beta, float *C, const float *A) {
+  return pgb200Ssyrk(nullptr, n, m, alpha, A, m, beta, C, n);
+}
+
+}  // extern "C"

@@ -1,0 +1,48 @@
+"""Host-array mirror of the reference's PolyBench kernel functions.
+
+Same names, argument order and in-place semantics as
+  kernel_gemm  tools/cgeist/Test/polybench/linear-algebra/blas/gemm/gemm.c:88-115
+  kernel_2mm   tools/cgeist/Test/polybench/linear-algebra/kernels/2mm/2mm.c:92-121
+  kernel_mvt   tools/cgeist/Test/polybench/linear-algebra/kernels/mvt/mvt.c:93-111
+  kernel_syrk  tools/cgeist/Test/polybench/linear-algebra/blas/syrk/syrk.c:83-108
+Arrays are C-contiguous numpy arrays in host memory with exactly the extents
+given by the size arguments (the C99-prototype form of the PolyBench
+signatures); float64 takes the DATA_TYPE=double build, float32 the
+-DDATA_TYPE_IS_FLOAT build.  Each call goes through the library's
+`pgb200_kernel_*` drop-in, which stages the operands to the GPU, runs the
+contraction and copies the live-out arrays back.
+"""
+import numpy as np
+
+from . import check, load
+
+
+def _req(a, shape):
+    if not (isinstance(a, np.ndarray) and a.flags["C_CONTIGUOUS"] and tuple(a.shape) == tuple(shape)):
+        raise ValueError(f"expected a C-contiguous numpy array of shape {tuple(shape)}")
+    return a.ctypes.data
+
+
+def kernel_gemm(ni, nj, nk, alpha, beta, C, A, B):
+    f = load().pgb200_kernel_gemm if C.dtype == np.float64 else load().pgb200_kernel_gemm_f32
+    check(f(ni, nj, nk, alpha, beta, _req(C, (ni, nj)), _req(A, (ni, nk)), _req(B, (nk, nj))))
+
+
+def kernel_2mm(ni, nj, nk, nl, alpha, beta, tmp, A, B, C, D):
+    if D.dtype != np.float64:
+        raise ValueError("kernel_2mm: float64 only")
+    check(load().pgb200_kernel_2mm(ni, nj, nk, nl, alpha, beta, _req(tmp, (ni, nj)),
+                                   _req(A, (ni, nk)), _req(B, (nk, nj)), _req(C, (nj, nl)),
+                                   _req(D, (ni, nl))))
+
+
+def kernel_mvt(n, x1, x2, y_1, y_2, A):
+    if A.dtype != np.float64:
+        raise ValueError("kernel_mvt: float64 only")
+    check(load().pgb200_kernel_mvt(n, _req(x1, (n,)), _req(x2, (n,)), _req(y_1, (n,)),
+                                   _req(y_2, (n,)), _req(A, (n, n))))
+
+
+def kernel_syrk(n, m, alpha, beta, C, A):
+    f = load().pgb200_kernel_syrk if C.dtype == np.float64 else load().pgb200_kernel_syrk_f32
+    check(f(n, m, alpha, beta, _req(C, (n, n)), _req(A, (n, m))))

@@ -1,0 +1,133 @@
+"""CPU tests of the oracle itself: it must reproduce the reference's golden
+dumps and, when the compiled reference kernels are present, match them bit
+for bit on seeded inputs."""
+import numpy as np
+import pytest
+
+from helpers import (MINI, SEED, assert_dump_equal, init_2mm, init_gemm, init_mvt, init_syrk,
+                     read_dump)
+from oracle import pbo, ref
+
+TYPES = [("f64", np.float64), ("f32", np.float32)]
+
+
+@pytest.mark.parametrize("tname,dtype", TYPES)
+def test_gemm_golden(tname, dtype):
+    ni, nj, nk = MINI["gemm"]
+    alpha, beta, C, A, B = init_gemm(ni, nj, nk, dtype)
+    pbo.gemm(alpha, beta, C, A, B)
+    assert_dump_equal(read_dump("gemm", tname)["C"], C)
+
+
+@pytest.mark.parametrize("tname,dtype", TYPES)
+def test_2mm_golden(tname, dtype):
+    ni, nj, nk, nl = MINI["2mm"]
+    alpha, beta, tmp, A, B, C, D = init_2mm(ni, nj, nk, nl, dtype)
+    pbo.mm2(alpha, beta, tmp, A, B, C, D)
+    assert_dump_equal(read_dump("2mm", tname)["D"], D)
+
+
+@pytest.mark.parametrize("tname,dtype", TYPES)
+def test_mvt_golden(tname, dtype):
+    (n,) = MINI["mvt"]
+    x1, x2, y1, y2, A = init_mvt(n, dtype)
+    pbo.mvt(x1, x2, y1, y2, A)
+    d = read_dump("mvt", tname)
+    assert_dump_equal(d["x1"], x1)
+    assert_dump_equal(d["x2"], x2)
+
+
+@pytest.mark.parametrize("tname,dtype", TYPES)
+def test_syrk_golden(tname, dtype):
+    n, m = MINI["syrk"]
+    alpha, beta, C, A = init_syrk(n, m, dtype)
+    C0 = C.copy()
+    pbo.syrk(alpha, beta, C, A)
+    assert_dump_equal(read_dump("syrk", tname)["C"], C)
+    iu = np.triu_indices(n, 1)
+    assert np.array_equal(C[iu], C0[iu]), "strict upper triangle must stay untouched"
+
+
+needs_ref = pytest.mark.skipif(not ref.available(), reason="compiled reference kernels absent")
+
+
+def _rand(shape, dtype, aid, lo=-1.0, hi=1.0):
+    return pbo.fill(shape[0], shape[1], dtype, SEED, aid, lo, hi)
+
+
+@needs_ref
+@pytest.mark.parametrize("tname,dtype", TYPES)
+def test_oracle_matches_compiled_reference(tname, dtype):
+    # The reference library is built with FMA contraction allowed, the oracle
+    # without; sums of products may differ in the last bits, never more.
+    tol = 1e-13 if dtype == np.float64 else 2e-5
+    ni, nj, nk, nl = 37, 53, 61, 29
+    A, B, C = _rand((ni, nk), dtype, 1), _rand((nk, nj), dtype, 2), _rand((ni, nj), dtype, 3)
+    C2 = C.copy()
+    pbo.gemm(1.5, 1.2, C, A, B)
+    ref.kernel_gemm(ni, nj, nk, 1.5, 1.2, C2, A, B)
+    assert np.max(np.abs(C - C2)) <= tol * np.max(np.abs(C2))
+
+    Cc, D = _rand((nj, nl), dtype, 4), _rand((ni, nl), dtype, 5)
+    D2 = D.copy()
+    tmp, tmp2 = np.zeros((ni, nj), dtype), np.zeros((ni, nj), dtype)
+    pbo.mm2(1.5, 1.2, tmp, A, B, Cc, D)
+    ref.kernel_2mm(ni, nj, nk, nl, 1.5, 1.2, tmp2, A, B, Cc, D2)
+    assert np.max(np.abs(D - D2)) <= tol * np.max(np.abs(D2))
+    assert np.max(np.abs(tmp - tmp2)) <= tol * np.max(np.abs(tmp2))
+
+    n = 67
+    Am = _rand((n, n), dtype, 6, 0.0, 1.0)
+    v = [pbo.fill_vec(n, dtype, SEED, 7 + k, 0.0, 1.0) for k in range(4)]
+    w = [x.copy() for x in v]
+    pbo.mvt(v[0], v[1], v[2], v[3], Am)
+    ref.kernel_mvt(n, w[0], w[1], w[2], w[3], Am)
+    for a, b in zip(v[:2], w[:2]):
+        assert np.max(np.abs(a - b)) <= tol * np.max(np.abs(b))
+
+    n, m = 45, 33
+    As, Cs = _rand((n, m), dtype, 11), _rand((n, n), dtype, 12)
+    Cs2 = Cs.copy()
+    pbo.syrk(1.5, 1.2, Cs, As)
+    ref.kernel_syrk(n, m, 1.5, 1.2, Cs2, As)
+    assert np.max(np.abs(Cs - Cs2)) <= tol * np.max(np.abs(Cs2))
+
+
+def test_row_restricted_oracle_is_bit_identical():
+    n, m = 40, 24
+    A, C = _rand((n, m), np.float64, 1), _rand((n, n), np.float64, 2)
+    full = pbo.syrk(1.5, 1.2, C.copy(), A)
+    part = C.copy()
+    pbo.syrk(1.5, 1.2, part, A, 10, 25)
+    assert np.array_equal(part[10:25], full[10:25])
+    assert np.array_equal(part[:10], C[:10]) and np.array_equal(part[25:], C[25:])
+
+    Am = _rand((n, n), np.float64, 3, 0.0, 1.0)
+    v = [pbo.fill_vec(n, np.float64, SEED, 4 + k, 0.0, 1.0) for k in range(4)]
+    f = [x.copy() for x in v]
+    pbo.mvt(f[0], f[1], f[2], f[3], Am)
+    p = [x.copy() for x in v]
+    pbo.mvt(p[0], p[1], p[2], p[3], Am, 5, 17)
+    assert np.array_equal(p[0][5:17], f[0][5:17]) and np.array_equal(p[1][5:17], f[1][5:17])
+
+
+def test_generator_properties():
+    a = pbo.fill(64, 48, np.float64, SEED, 1, -1.0, 1.0)
+    assert a.min() >= -1.0 and a.max() < 1.0 and abs(a.mean()) < 0.05
+    # counter-based: a row block generated on its own equals the same rows of the whole
+    b = pbo.fill(16, 48, np.float64, SEED, 1, -1.0, 1.0, row0=20)
+    assert np.array_equal(b, a[20:36])
+    # padded destination leaves the padding alone
+    buf = np.full((8, 20), 7.0, dtype=np.float32)
+    pbo.fill(8, 16, np.float32, SEED, 2, 0.0, 1.0, out=buf[:, :16])
+    assert np.all(buf[:, 16:] == 7.0) and buf[:, :16].max() < 1.0 and buf[:, :16].min() >= 0.0
+    c = pbo.fill(8, 16, np.float32, SEED, 3, 0.0, 1.0)
+    assert not np.array_equal(c, buf[:, :16])
+    # acc64 variant agrees with a numpy float64 evaluation
+    A = pbo.fill(9, 13, np.float32, SEED, 4, 0.0, 1.0)
+    B = pbo.fill(13, 11, np.float32, SEED, 5, 0.0, 1.0)
+    Cm = pbo.fill(9, 11, np.float32, SEED, 6, 0.0, 1.0)
+    t = pbo.gemm_acc64(1.5, 1.2, Cm, A, B)
+    e = np.float64(np.float32(1.5)) * (A.astype(np.float64) @ B.astype(np.float64)) + \
+        np.float64(np.float32(1.2)) * Cm.astype(np.float64)
+    assert np.max(np.abs(t - e)) < 1e-12
