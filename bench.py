@@ -1,0 +1,497 @@
+#!/usr/bin/env python
+"""Benchmark of the raised-contraction hot path (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl pgb200|reference]
+                    [--workload dgemm4096|sgemm1024|mvt32768|chain2mm]
+
+Default workload: BASELINE.json configs[1] - fp64 GEMM C = alpha*A*B + beta*C,
+M=N=K=4096, inputs uniform [-1,1) from a seed, alpha=1.5, beta=1.2.  With N>1
+ranks (torchrun) every rank owns a 4096-row block of A and C (weak scaling)
+and the shared operand B is broadcast from rank 0 by NCCL inside every step,
+K-chunked so that the transfer overlaps the product.
+
+`value`   device-resident throughput, CUDA events on the launching stream.
+`e2e`     same metric through the reference-facing drop-in (pgb200_kernel_gemm
+          with host arrays): H2D and D2H copies inside the timed region.
+`roofline`/`cpu_baseline`: see DESIGN.md.
+`--impl reference` times the reference's own compiled kernel_gemm
+(oracle/_ref) on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEED = 20261125
+ALPHA, BETA = 1.5, 1.2
+
+WORKLOADS = {
+    # name: (metric, unit, dtype, description)
+    "dgemm4096": dict(dtype="f64", M=4096, N=4096, K=4096, lo=-1.0, hi=1.0,
+                      desc="configs[1]: fp64 GEMM 4096^3, uniform [-1,1), alpha=1.5 beta=1.2"),
+    "sgemm1024": dict(dtype="f32", M=1024, N=1024, K=1024, lo=0.0, hi=1.0,
+                      desc="configs[0]: fp32 GEMM 1024^3, uniform [0,1), alpha=1.5 beta=1.2"),
+    "sgemm8192": dict(dtype="f32", M=8192, N=8192, K=8192, lo=0.0, hi=1.0,
+                      desc="fp32 GEMM 8192^3 (3xTF32), uniform [0,1)"),
+    "mvt16384": dict(dtype="f64", N=16384, lo=0.0, hi=1.0,
+                     desc="fp64 mat-vec pair, N=16384 (2.1 GB; the profiling-size case of configs[2])"),
+    "mvt32768": dict(dtype="f64", N=32768, lo=0.0, hi=1.0,
+                     desc="configs[2]: fp64 mat-vec pair x1+=A*y1, x2+=A^T*y2, N=32768, fused single pass"),
+    "chain2mm": dict(dtype="f64", ni=4096, nk=6144, nj=5120, nl=8192, lo=-1.0, hi=1.0,
+                     desc="configs[3]: fp64 chained GEMM tmp=alpha*A*B; D=tmp*C+beta*D"),
+}
+
+
+# ----------------------------------------------------------------------------- helpers
+class NvmlSampler:
+    """SM clock and throttle reasons polled from NVML (what nvidia-smi reads)
+    every few milliseconds on a thread, during the timed region only."""
+
+    def __init__(self, index, period_s=0.004):
+        import threading
+        self.index, self.period = index, period_s
+        self.sm, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self.ok = False
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if vis:
+                ids = [v for v in vis.split(",") if v != ""]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.ok:
+            self._thread.start()
+
+    def stop(self):
+        if not self.ok:
+            return None
+        self._stop.set()
+        self._thread.join(timeout=2)
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None,
+                "sm_max_mhz": self.max_mhz, "samples": len(self.sm),
+                "reasons": sorted(self.reasons), "source": "nvml"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples (fallback when NVML's Python
+    binding is unusable)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
+                 "100", "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def algorithmic_work(name, w):
+    """(units per step for `value`, label) - flop for contractions, bytes for mat-vec."""
+    if name.startswith("mvt"):
+        n = w["N"]
+        return n * n * 8 + 6 * n * 8
+    if name == "chain2mm":
+        return 2 * w["ni"] * w["nj"] * w["nk"] + 2 * w["ni"] * w["nl"] * w["nj"]
+    return 2 * w["M"] * w["N"] * w["K"]
+
+
+# ----------------------------------------------------------------------------- reference arm
+def run_reference(args, w, name):
+    """The reference's own CPU implementation of the path (oracle/_ref: kernel_gemm
+    etc. compiled unmodified from the reference sources), all host cores, each
+    thread running the unmodified kernel on an independent slab of rows."""
+    import concurrent.futures as cf
+
+    import numpy as np
+
+    from oracle import pbo, ref
+    if not ref.available():
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "oracle/_ref is not built and the reference tree is not mounted"}))
+        return
+    cores = os.cpu_count() or 1
+    np_dt = np.float64 if w["dtype"] == "f64" else np.float32
+    if name.startswith("mvt"):
+        n = 8192  # bounded sample: same nests on an 8192^2 matrix (0.5 GB)
+        A = pbo.fill(n, n, np_dt, SEED, 1, w["lo"], w["hi"])
+        v = [pbo.fill_vec(n, np_dt, SEED, 2 + k, w["lo"], w["hi"]) for k in range(4)]
+        sample = f"kernel_mvt at N={n} (1 thread: the nests are sequential)"
+        units = n * n * 8 + 6 * n * 8
+        used = 1
+
+        def step():
+            ref.kernel_mvt(n, v[0], v[1], v[2], v[3], A)
+    else:
+        if name == "chain2mm":
+            K, N = w["nk"], w["nj"]
+        else:
+            K, N = w["K"], w["N"]
+        rows_per = 32 if name != "sgemm1024" else 1024 // cores
+        used = cores
+        B = pbo.fill(K, N, np_dt, SEED, 2, w["lo"], w["hi"])
+        As = [pbo.fill(rows_per, K, np_dt, SEED, 1, w["lo"], w["hi"], row0=t * rows_per) for t in range(used)]
+        Cs = [pbo.fill(rows_per, N, np_dt, SEED, 3, w["lo"], w["hi"], row0=t * rows_per) for t in range(used)]
+        sample = (f"kernel_gemm on {used} independent {rows_per}-row slabs of the {K}x{N} problem, "
+                  f"one thread each")
+        units = 2 * rows_per * used * N * K
+        pool = cf.ThreadPoolExecutor(max_workers=used)
+
+        def step():
+            list(pool.map(lambda t: ref.kernel_gemm(rows_per, N, K, ALPHA, BETA, Cs[t], As[t], B),
+                          range(used)))
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    metric, unit, scale = metric_of(name)
+    val = units / dt / scale
+    print(json.dumps({
+        "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"],
+        "data": "synthetic", "config": {"workload": w["desc"]},
+        "cpu_baseline": {"value": val, "unit": unit, "cores": used, "kind": "reference",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def metric_of(name):
+    if name.startswith("mvt"):
+        return "HBM GB/s of the raised mat-vec pair", "GB/s", 1e9
+    return "GFLOP/s per raised op", "GFLOP/s", 1e9
+
+
+def cpu_baseline(w, name, budget_s=12.0):
+    """Bounded CPU sample on rank 0: the compiled reference kernel when present
+    (kind 'reference'), else this repository's C restatement (kind 'port')."""
+    import concurrent.futures as cf
+
+    import numpy as np
+
+    from oracle import pbo, ref
+    have_ref = ref.available()
+    cores = os.cpu_count() or 1
+    np_dt = np.float64 if w["dtype"] == "f64" else np.float32
+    metric, unit, scale = metric_of(name)
+    if name.startswith("mvt"):
+        n = 4096
+        A = pbo.fill(n, n, np_dt, SEED, 1, w["lo"], w["hi"])
+        v = [pbo.fill_vec(n, np_dt, SEED, 2 + k, w["lo"], w["hi"]) for k in range(4)]
+        t0 = time.perf_counter()
+        reps = 0
+        while reps < 3 or time.perf_counter() - t0 < 2.0:
+            if have_ref:
+                ref.kernel_mvt(n, v[0], v[1], v[2], v[3], A)
+            else:
+                pbo.mvt(v[0], v[1], v[2], v[3], A)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": (n * n * 8 + 6 * n * 8) / dt / scale, "unit": unit, "cores": 1,
+                "kind": "reference" if have_ref else "port",
+                "sample": f"kernel_mvt at N={n}, {reps} runs, sequential nests"}
+    if name == "chain2mm":
+        K, N = w["nk"], w["nj"]
+    else:
+        K, N = w["K"], w["N"]
+    rows_per = 16
+    B = pbo.fill(K, N, np_dt, SEED, 2, w["lo"], w["hi"])
+    As = [pbo.fill(rows_per, K, np_dt, SEED, 1, w["lo"], w["hi"], row0=t * rows_per) for t in range(cores)]
+    Cs = [pbo.fill(rows_per, N, np_dt, SEED, 3, w["lo"], w["hi"], row0=t * rows_per) for t in range(cores)]
+
+    def one(t):
+        if have_ref:
+            ref.kernel_gemm(rows_per, N, K, ALPHA, BETA, Cs[t], As[t], B)
+        else:
+            pbo.gemm(ALPHA, BETA, Cs[t], As[t], B)
+
+    with cf.ThreadPoolExecutor(max_workers=cores) as pool:
+        list(pool.map(one, range(cores)))  # warm-up
+        t0 = time.perf_counter()
+        reps = 0
+        while reps < 2 or time.perf_counter() - t0 < min(budget_s, 6.0):
+            list(pool.map(one, range(cores)))
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+    return {"value": 2 * rows_per * cores * N * K / dt / scale, "unit": unit, "cores": cores,
+            "kind": "reference" if have_ref else "port",
+            "sample": f"kernel_gemm on {cores} independent {rows_per}-row slabs of the "
+                      f"{K}x{N} problem, {reps} runs"}
+
+
+# ----------------------------------------------------------------------------- pgb200 arm
+def run_pgb200(args, w, name):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import polygeist_b200 as pgb
+    from polygeist_b200 import partition, polybench
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; libpgb200 has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pgb.init()
+    tdt = torch.float64 if w["dtype"] == "f64" else torch.float32
+    metric, unit, scale = metric_of(name)
+    units = algorithmic_work(name, w)
+
+    def filled(rows, cols, aid, row0=0):
+        t = torch.empty((rows, cols), dtype=tdt, device=dev)
+        pgb.fill_uniform(t, SEED, aid, w["lo"], w["hi"], row0=row0)
+        return t
+
+    # ---- operands resident in HBM ----
+    if name.startswith("mvt"):
+        n = w["N"]
+        A = filled(n, n, 1)
+        vec = [filled(1, n, 2 + k).reshape(n) for k in range(4)]
+
+        def step():
+            pgb.mvt(A, vec[2], vec[3], vec[0], vec[1])
+    elif name == "chain2mm":
+        A = filled(w["ni"], w["nk"], 1)
+        B = filled(w["nk"], w["nj"], 2)
+        Cc = filled(w["nj"], w["nl"], 3)
+        D = filled(w["ni"], w["nl"], 4)
+        tmp = torch.empty((w["ni"], w["nj"]), dtype=tdt, device=dev)
+
+        def step():
+            pgb.gemm(ALPHA, A, B, 0.0, tmp)
+            pgb.gemm(1.0, tmp, Cc, BETA, D)
+    else:
+        M, N, K = w["M"], w["N"], w["K"]
+        A = filled(M, K, 1, row0=rank * M)          # this rank's row block
+        Cm = filled(M, N, 3, row0=rank * M)
+        B = filled(K, N, 2) if rank == 0 else torch.empty((K, N), dtype=tdt, device=dev)
+        if world > 1:
+            plan = partition.PartitionedGemm(dist, pgb.gemm, src=0, chunk=max(256, K // 4))
+
+            def step():
+                plan.run(ALPHA, A, B, BETA, Cm)
+        else:
+            def step():
+                pgb.gemm(ALPHA, A, B, BETA, Cm)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = None
+    if rank == 0:
+        sampler = NvmlSampler(local)
+        if not sampler.ok:
+            sampler = ClockSampler(local)
+        sampler.start()
+    stream = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = pgb.launch_count()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    launches = pgb.launch_count() - l0
+    clocks = sampler.stop() if sampler else None
+    pgb.poll_device_status()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = units * world / (ms_per_step * 1e-3) / scale
+
+    # ---- dominant-kernel roofline (one kernel per step for the GEMMs) ----
+    roof = None
+    if rank == 0:
+        if name.startswith("mvt"):
+            peaks = {}
+            try:
+                peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+            except OSError:
+                pass
+            peak = peaks.get("hbm_gbs", 6650.0)
+            src = "of measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "of fallback"
+            ach = units / (ms_per_step * 1e-3) / 1e9
+            roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
+                    "frac": ach / peak, "traffic": None, "peak_source": src}
+        elif w["dtype"] == "f64":
+            peak = pgb.probe_peak(pgb.PEAK_DMMA) / 1e3
+            ach = units / (ms_per_step * 1e-3) / 1e12
+            roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+                    "frac": ach / peak, "traffic": None,
+                    "peak_source": "fp64 tensor (mma.sync .f64) issue-rate probe measured in this "
+                                   "run; MEASURED_PEAKS.json has no fp64 figure"}
+        else:
+            roof = None  # filled by the tcgen05 path's own probe when present
+
+    # ---- end to end through the reference-facing drop-in, host arrays ----
+    e2e = None
+    if name in ("dgemm4096", "sgemm1024", "sgemm8192") and not args.kernel_only:
+        M, N, K = w["M"], w["N"], w["K"]
+        np_dt = np.float64 if w["dtype"] == "f64" else np.float32
+
+        def pinned(t):
+            h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            h.copy_(t)
+            return h.numpy()
+        hA, hB, hC = pinned(A), pinned(B if rank == 0 or world == 1 else B), pinned(Cm)
+        isz = np.dtype(np_dt).itemsize
+        h2d, d2h = (M * K + K * N + M * N) * isz, M * N * isz
+        reps = max(3, min(args.steps, 10))
+        polybench.kernel_gemm(M, N, K, ALPHA, BETA, hC, hA, hB)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            polybench.kernel_gemm(M, N, K, ALPHA, BETA, hC, hA, hB)
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / reps
+        if world > 1:
+            t = torch.tensor([dt], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        e2e = {"value": units * world / dt / scale, "unit": unit, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h}
+    elif name.startswith("mvt"):
+        n = min(8192, w["N"])  # host-array drop-in on a bounded sample (0.5 GB): PCIe-bound
+        hAm = torch.empty((n, n), dtype=tdt, pin_memory=True)
+        hAm.copy_(A[:n, :n])
+        hv = [torch.empty(n, dtype=tdt, pin_memory=True).copy_(v[:n]).numpy() for v in vec]
+        hAn = hAm.numpy()
+        polybench.kernel_mvt(n, hv[0], hv[1], hv[2], hv[3], hAn)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            polybench.kernel_mvt(n, hv[0], hv[1], hv[2], hv[3], hAn)
+        dt = (time.perf_counter() - t0) / 3
+        e2e = {"value": (n * n * 8 + 6 * n * 8) / dt / scale, "unit": unit,
+               "h2d_bytes_per_step": n * n * 8 + 4 * n * 8, "d2h_bytes_per_step": 2 * n * 8,
+               "note": f"kernel_mvt drop-in at N={n}"}
+
+    if rank == 0:
+        cpu = cpu_baseline(w, name) if (world == 1 and not args.kernel_only) else None
+        line = {
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": w["desc"],
+                       "l2": "operands (>= 384 MiB) exceed the 126 MB L2; no flush between steps",
+                       "parallelism": ("single GPU" if world == 1 else
+                                       f"{world} row blocks of 4096 rows, B broadcast by NCCL each step")},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roof,
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="pgb200", choices=["pgb200", "reference"])
+    ap.add_argument("--workload", default="dgemm4096", choices=sorted(WORKLOADS))
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU-baseline legs (profiling runs)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "pgb200" else args.warmup
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        if args.steps > 5:
+            args.steps = 5
+        run_reference(args, w, args.workload)
+    else:
+        run_pgb200(args, w, args.workload)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,67 @@
+"""CPU tests of the drop-in boundary: the shared library loads, exports every
+symbol include/pgb200.h declares, and fails loudly (never computes on the CPU)
+when there is no GPU."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+import polygeist_b200 as pgb
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "pgb200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(pgb200\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_typed():
+    lib = pgb.load()
+    names = _declared_symbols()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in pgb200.h but not exported"
+        assert n in pgb.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(pgb.SIGNATURES) == set(names)
+
+
+def test_version_and_error_string():
+    lib = pgb.load()
+    assert lib.pgb200Version() >= 100
+    assert isinstance(lib.pgb200GetLastErrorString(), bytes)
+
+
+def _no_gpu():
+    import torch
+    return not torch.cuda.is_available()
+
+
+@pytest.mark.skipif(not _no_gpu(), reason="only meaningful without a GPU")
+def test_no_cpu_fallback_without_gpu():
+    """Without a device the compute entry points return an error status and
+    leave the output untouched - there is no silent host path."""
+    lib = pgb.load()
+    A = np.ones((4, 4))
+    B = np.ones((4, 4))
+    Cm = np.full((4, 4), 3.0)
+    st = lib.pgb200Dgemm(None, 4, 4, 4, 1.0, A.ctypes.data, 4, B.ctypes.data, 4, 0.0,
+                         Cm.ctypes.data, 4)
+    assert st in (pgb.ERR_CUDA, pgb.ERR_UNSUPPORTED)
+    assert np.all(Cm == 3.0)
+    assert lib.pgb200GetLastErrorString() != b""
+    with pytest.raises(pgb.PGB200Error):
+        from polygeist_b200 import polybench
+        polybench.kernel_gemm(4, 4, 4, 1.0, 0.0, Cm, A, B)
+
+
+def test_polybench_mirror_rejects_wrong_extents():
+    from polygeist_b200 import polybench
+    with pytest.raises(ValueError):
+        polybench.kernel_gemm(4, 4, 4, 1.0, 0.0, np.zeros((4, 5)), np.zeros((4, 4)), np.zeros((4, 4)))
+    with pytest.raises(ValueError):
+        polybench.kernel_mvt(4, np.zeros(4), np.zeros(4), np.zeros(4), np.zeros(4),
+                             np.zeros((4, 4), dtype=np.float32))

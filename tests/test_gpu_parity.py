@@ -1,0 +1,319 @@
+"""GPU parity tests: every call goes through the C ABI of libpgb200 and is
+checked against the CPU oracle on the same seeded inputs.
+
+Gates (the tolerances BASELINE.json states, made precise):
+  fp64, signed inputs  : max|d| / max|ref| <= 1e-12, and componentwise backward
+                         error |d| / (|a||A||B| + |b||C|) <= 1e-13
+  fp64, inputs in [0,1): element-wise relative error <= 1e-12
+  fp32                 : element-wise relative error <= 1e-5 against the fp64-
+                         accumulated evaluation of the same fp32 inputs, and
+                         against the sequential fp32 loop nest where K <= 8192
+"""
+import numpy as np
+import pytest
+import torch
+
+import polygeist_b200 as pgb
+from helpers import (MINI, SEED, assert_dump_equal, backward_gemm, elementwise_rel, init_2mm,
+                     init_gemm, init_mvt, init_syrk, normwise, read_dump)
+from oracle import pbo
+from polygeist_b200 import polybench
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev_fill(rows, cols, dtype, aid, lo, hi, ld=None):
+    ld = cols if ld is None else ld
+    buf = torch.full((rows, ld), float("nan"), dtype=dtype, device=DEV)
+    view = buf[:, :cols]
+    pgb.fill_uniform(view, SEED, aid, lo, hi)
+    return view
+
+
+def sync_ok():
+    torch.cuda.synchronize()
+    pgb.poll_device_status()
+
+
+# --------------------------------------------------------------------------- generator
+@pytest.mark.parametrize("dtype,np_dtype", [(torch.float64, np.float64), (torch.float32, np.float32)])
+def test_device_generator_is_bit_identical_to_host(dtype, np_dtype):
+    d = dev_fill(33, 47, dtype, 3, -1.0, 1.0, ld=52)
+    h = pbo.fill(33, 47, np_dtype, SEED, 3, -1.0, 1.0)
+    assert np.array_equal(d.cpu().numpy(), h)
+    part = torch.empty((5, 47), dtype=dtype, device=DEV)
+    pgb.fill_uniform(part, SEED, 3, -1.0, 1.0, row0=11)
+    assert np.array_equal(part.cpu().numpy(), h[11:16])
+
+
+# --------------------------------------------------------------------------- dgemm
+DGEMM_SHAPES = [
+    # (M, N, K, lda_pad, ldb_pad, ldc_pad, expect fast path)
+    (128, 128, 64, 0, 0, 0, True),
+    (256, 384, 512, 0, 0, 0, True),
+    (200, 152, 100, 0, 0, 0, True),      # ragged tiles, K not a multiple of 16
+    (1, 4, 4, 0, 0, 0, True),
+    (130, 260, 36, 6, 2, 4, True),       # padded leading dimensions
+    (97, 61, 45, 0, 0, 0, False),        # odd sizes -> SIMT path
+    (64, 64, 64, 1, 0, 0, False),        # odd lda -> SIMT path
+    (17, 33, 1, 0, 0, 0, False),
+]
+
+
+@pytest.mark.parametrize("M,N,K,pa,pb,pc,fast", DGEMM_SHAPES)
+@pytest.mark.parametrize("beta", [1.2, 0.0])
+def test_dgemm_matches_oracle(M, N, K, pa, pb, pc, fast, beta):
+    A = dev_fill(M, K, torch.float64, 1, -1.0, 1.0, ld=K + pa)
+    B = dev_fill(K, N, torch.float64, 2, -1.0, 1.0, ld=N + pb)
+    Cm = dev_fill(M, N, torch.float64, 3, -1.0, 1.0, ld=N + pc)
+    hA, hB, hC = A.cpu().numpy(), B.cpu().numpy(), Cm.cpu().numpy()
+    C0 = hC.copy()
+    if beta == 0.0:
+        Cm.fill_(float("nan"))  # beta == 0 must not read C
+    pgb.gemm(1.5, A, B, beta, Cm)
+    sync_ok()
+    assert pgb.last_path() == (pgb.PATH_DMMA if fast else pgb.PATH_SIMT)
+    ref = pbo.gemm(1.5, beta, np.ascontiguousarray(hC), np.ascontiguousarray(hA),
+                   np.ascontiguousarray(hB))
+    got = Cm.cpu().numpy()
+    assert normwise(got, ref) <= 1e-12
+    assert backward_gemm(got, ref, 1.5, beta, hA, hB, C0) <= 1e-13
+    if pc:
+        assert torch.isnan(Cm._base[:, N:]).all(), "padding columns must keep their NaN fill"
+
+
+def test_dgemm_empty_and_k0():
+    A = torch.zeros((4, 0), dtype=torch.float64, device=DEV)
+    B = torch.zeros((0, 8), dtype=torch.float64, device=DEV)
+    Cm = dev_fill(4, 8, torch.float64, 1, -1.0, 1.0)
+    C0 = Cm.clone()
+    pgb.gemm(1.5, A, B, 1.2, Cm)  # K == 0: C *= beta
+    sync_ok()
+    assert torch.equal(Cm, C0 * 1.2)
+    lib = pgb.load()
+    assert lib.pgb200Dgemm(None, 0, 8, 4, 1.0, None, 4, None, 8, 0.0, None, 8) == pgb.OK
+    assert lib.pgb200Dgemm(None, 4, 8, 4, 1.0, Cm.data_ptr(), 2, Cm.data_ptr(), 8, 0.0,
+                           Cm.data_ptr(), 8) == pgb.ERR_INVALID  # lda < K
+    assert lib.pgb200Dgemm(None, -1, 8, 4, 1.0, None, 4, None, 8, 0.0, None, 8) == pgb.ERR_INVALID
+
+
+def test_dgemm_full_size_rows_and_freivalds():
+    """configs[1]: M=N=K=4096, inputs uniform [-1,1).  Oracle on a pseudo-random
+    row subset (rows are independent in the loop nest) plus a Freivalds check of
+    the whole product."""
+    n = 4096
+    A = dev_fill(n, n, torch.float64, 1, -1.0, 1.0)
+    B = dev_fill(n, n, torch.float64, 2, -1.0, 1.0)
+    Cm = dev_fill(n, n, torch.float64, 3, -1.0, 1.0)
+    C0 = Cm.clone()
+    pgb.gemm(1.5, A, B, 1.2, Cm)
+    sync_ok()
+    assert pgb.last_path() == pgb.PATH_DMMA
+    rows = np.sort(np.random.default_rng(SEED).choice(n, 24, replace=False))
+    rows = np.unique(np.concatenate([rows, [0, 127, 128, n - 1]]))
+    hB = pbo.fill(n, n, np.float64, SEED, 2, -1.0, 1.0)
+    for r in rows:
+        hA = pbo.fill(1, n, np.float64, SEED, 1, -1.0, 1.0, row0=int(r))
+        hC = pbo.fill(1, n, np.float64, SEED, 3, -1.0, 1.0, row0=int(r))
+        ref = pbo.gemm(1.5, 1.2, hC, hA, hB)
+        got = Cm[int(r)].cpu().numpy()[None, :]
+        assert normwise(got, ref) <= 1e-12
+    v = dev_fill(n, 1, torch.float64, 9, -1.0, 1.0)
+    lhs = Cm @ v
+    rhs = 1.5 * (A @ (B @ v)) + 1.2 * (C0 @ v)
+    assert float((lhs - rhs).abs().max() / rhs.abs().max()) <= 1e-12
+
+
+# --------------------------------------------------------------------------- 2mm
+def test_chained_gemm_matches_2mm_oracle():
+    ni, nj, nk, nl = 192, 160, 224, 256
+    A = dev_fill(ni, nk, torch.float64, 1, -1.0, 1.0)
+    B = dev_fill(nk, nj, torch.float64, 2, -1.0, 1.0)
+    Cc = dev_fill(nj, nl, torch.float64, 3, -1.0, 1.0)
+    D = dev_fill(ni, nl, torch.float64, 4, -1.0, 1.0)
+    hA, hB, hC, hD = (t.cpu().numpy() for t in (A, B, Cc, D))
+    tmp = torch.full((ni, nj), float("nan"), dtype=torch.float64, device=DEV)
+    pgb.gemm(1.5, A, B, 0.0, tmp)       # nest 1: tmp = alpha*A*B
+    pgb.gemm(1.0, tmp, Cc, 1.2, D)      # nest 2: D = tmp*C + beta*D
+    sync_ok()
+    htmp = np.zeros((ni, nj))
+    ref = pbo.mm2(1.5, 1.2, htmp, hA, hB, hC, hD.copy())
+    assert normwise(tmp.cpu().numpy(), htmp) <= 1e-12
+    assert normwise(D.cpu().numpy(), ref) <= 1e-12
+
+
+# --------------------------------------------------------------------------- mat-vec
+@pytest.mark.parametrize("n,pad", [(1, 0), (2, 0), (7, 0), (40, 0), (129, 0), (256, 0), (258, 6),
+                                    (1000, 0), (1537, 3), (4096, 0)])
+def test_mvt_matches_oracle(n, pad):
+    A = dev_fill(n, n, torch.float64, 1, 0.0, 1.0, ld=n + pad)
+    vec = [dev_fill(1, n, torch.float64, 2 + k, 0.0, 1.0).reshape(n).contiguous() for k in range(4)]
+    x1, x2, y1, y2 = vec
+    h = [t.cpu().numpy().copy() for t in vec]
+    hA = np.ascontiguousarray(A.cpu().numpy())
+    pgb.mvt(A, y1, y2, x1, x2)
+    sync_ok()
+    assert pgb.last_path() == pgb.PATH_STREAM
+    pbo.mvt(h[0], h[1], h[2], h[3], hA)
+    assert elementwise_rel(x1.cpu().numpy(), h[0]) <= 1e-12
+    assert elementwise_rel(x2.cpu().numpy(), h[1]) <= 1e-12
+
+
+@pytest.mark.parametrize("M,N", [(300, 200), (64, 1025), (1, 9), (513, 2)])
+@pytest.mark.parametrize("trans", [0, 1])
+def test_dgemv_matches_numpy(M, N, trans):
+    A = dev_fill(M, N, torch.float64, 1, -1.0, 1.0)
+    x = dev_fill(1, M if trans else N, torch.float64, 2, -1.0, 1.0).reshape(-1).contiguous()
+    y = dev_fill(1, N if trans else M, torch.float64, 3, -1.0, 1.0).reshape(-1).contiguous()
+    hA, hx, hy = A.cpu().numpy(), x.cpu().numpy(), y.cpu().numpy()
+    pgb.gemv(trans, 1.5, A, x, 1.2, y)
+    sync_ok()
+    ref = 1.5 * ((hA.T if trans else hA) @ hx) + 1.2 * hy
+    assert normwise(y.cpu().numpy(), ref) <= 1e-12
+    y.fill_(float("nan"))
+    pgb.gemv(trans, 1.0, A, x, 0.0, y)  # beta == 0 must not read y
+    sync_ok()
+    assert normwise(y.cpu().numpy(), (hA.T if trans else hA) @ hx) <= 1e-12
+
+
+def test_mvt_large_row_subset():
+    n = 8192
+    A = dev_fill(n, n, torch.float64, 1, 0.0, 1.0)
+    vec = [dev_fill(1, n, torch.float64, 2 + k, 0.0, 1.0).reshape(n).contiguous() for k in range(4)]
+    x1, x2, y1, y2 = vec
+    h = [t.cpu().numpy().copy() for t in vec]
+    x1_before = x1.clone()
+    pgb.mvt(A, y1, y2, x1, x2)
+    sync_ok()
+    hA = pbo.fill(n, n, np.float64, SEED, 1, 0.0, 1.0)
+    pbo.mvt(h[0], h[1], h[2], h[3], hA, 1000, 1064)
+    assert elementwise_rel(x1.cpu().numpy()[1000:1064], h[0][1000:1064]) <= 1e-12
+    assert elementwise_rel(x2.cpu().numpy()[1000:1064], h[1][1000:1064]) <= 1e-12
+    # whole-vector property: 1^T(A y1) == (A^T 1)^T y1
+    ones = torch.ones(n, dtype=torch.float64, device=DEV)
+    lhs = float((x1 - x1_before).sum())
+    rhs = float(((A.T @ ones) * y1).sum())
+    assert abs(lhs - rhs) <= 1e-11 * abs(rhs)
+
+
+# --------------------------------------------------------------------------- syrk
+@pytest.mark.parametrize("n,k,pa,pc", [(128, 64, 0, 0), (300, 100, 0, 0), (257, 36, 2, 4),
+                                        (45, 33, 0, 0), (1, 4, 0, 0)])
+def test_dsyrk_matches_oracle(n, k, pa, pc):
+    A = dev_fill(n, k, torch.float64, 1, -1.0, 1.0, ld=k + pa)
+    Cm = dev_fill(n, n, torch.float64, 2, -1.0, 1.0, ld=n + pc)
+    hA, hC = np.ascontiguousarray(A.cpu().numpy()), np.ascontiguousarray(Cm.cpu().numpy())
+    C0 = hC.copy()
+    pgb.syrk(1.5, A, 1.2, Cm)
+    sync_ok()
+    ref = pbo.syrk(1.5, 1.2, hC, hA)
+    got = Cm.cpu().numpy()
+    il = np.tril_indices(n)
+    assert normwise(got[il], ref[il]) <= 1e-12
+    iu = np.triu_indices(n, 1)
+    assert np.array_equal(got[iu], C0[iu]), "strict upper triangle must stay untouched"
+
+
+# --------------------------------------------------------------------------- fp32 (path-agnostic gates)
+def _sgemm_case(M, N, K, beta=1.2):
+    A = dev_fill(M, K, torch.float32, 1, 0.0, 1.0)
+    B = dev_fill(K, N, torch.float32, 2, 0.0, 1.0)
+    Cm = dev_fill(M, N, torch.float32, 3, 0.0, 1.0)
+    hA, hB, hC = (np.ascontiguousarray(t.cpu().numpy()) for t in (A, B, Cm))
+    pgb.gemm(1.5, A, B, beta, Cm)
+    sync_ok()
+    got = Cm.cpu().numpy()
+    truth = pbo.gemm_acc64(1.5, beta, hC, hA, hB)
+    seq = pbo.gemm(1.5, beta, hC.copy(), hA, hB)
+    return got, truth, seq
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 1024), (200, 136, 100), (97, 61, 45),
+                                    (1, 4, 4), (384, 256, 4096)])
+def test_sgemm_matches_oracle(M, N, K):
+    got, truth, seq = _sgemm_case(M, N, K)
+    assert elementwise_rel(got, truth) <= 1e-5
+    assert elementwise_rel(got, seq) <= 1e-5
+
+
+def test_sgemm_config0_1024():
+    """configs[0]: fp32 M=N=K=1024, uniform [0,1), alpha=1.5, beta=1.2."""
+    got, truth, seq = _sgemm_case(1024, 1024, 1024)
+    assert elementwise_rel(got, truth) <= 1e-5
+    assert elementwise_rel(got, seq) <= 1e-5
+
+
+@pytest.mark.parametrize("n,k", [(128, 64), (300, 100), (45, 33), (512, 1024)])
+def test_ssyrk_matches_oracle(n, k):
+    A = dev_fill(n, k, torch.float32, 1, 0.0, 1.0)
+    Cm = dev_fill(n, n, torch.float32, 2, 0.0, 1.0)
+    hA, hC = np.ascontiguousarray(A.cpu().numpy()), np.ascontiguousarray(Cm.cpu().numpy())
+    C0 = hC.copy()
+    pgb.syrk(1.5, A, 1.2, Cm)
+    sync_ok()
+    got = Cm.cpu().numpy()
+    truth = pbo.syrk_acc64(1.5, 1.2, hC, hA)
+    seq = pbo.syrk(1.5, 1.2, hC.copy(), hA)
+    il = np.tril_indices(n)
+    assert elementwise_rel(got[il], truth[il]) <= 1e-5
+    assert elementwise_rel(got[il], seq[il]) <= 1e-5
+    iu = np.triu_indices(n, 1)
+    assert np.array_equal(got[iu], C0[iu])
+
+
+def test_ssyrk_row_block_equals_rows_of_full_update():
+    n, k = 384, 128
+    A = dev_fill(n, k, torch.float32, 1, 0.0, 1.0)
+    C1 = dev_fill(n, n, torch.float32, 2, 0.0, 1.0)
+    C2 = C1.clone()
+    pgb.syrk(1.5, A, 1.2, C1)
+    for r0, r1 in [(0, 100), (100, 256), (256, 384)]:
+        pgb.syrk(1.5, A, 1.2, C2, rows=(r0, r1))
+    sync_ok()
+    il = np.tril_indices(n)
+    assert elementwise_rel(C2.cpu().numpy()[il], C1.cpu().numpy()[il]) <= 1e-6
+
+
+# --------------------------------------------------------------------------- reference-style drop-ins (host arrays)
+@pytest.mark.parametrize("tname,dtype", [("f64", np.float64), ("f32", np.float32)])
+def test_kernel_gemm_dropin_reproduces_golden_dump(tname, dtype):
+    ni, nj, nk = MINI["gemm"]
+    alpha, beta, Cm, A, B = init_gemm(ni, nj, nk, dtype)
+    polybench.kernel_gemm(ni, nj, nk, alpha, beta, Cm, A, B)
+    assert_dump_equal(read_dump("gemm", tname)["C"], Cm, slack_ulps=1)
+
+
+def test_kernel_2mm_dropin_reproduces_golden_dump():
+    ni, nj, nk, nl = MINI["2mm"]
+    alpha, beta, tmp, A, B, Cm, D = init_2mm(ni, nj, nk, nl, np.float64)
+    polybench.kernel_2mm(ni, nj, nk, nl, alpha, beta, tmp, A, B, Cm, D)
+    assert_dump_equal(read_dump("2mm", "f64")["D"], D, slack_ulps=1)
+    assert normwise(tmp, 1.5 * (A @ B)) <= 1e-12
+
+
+def test_kernel_mvt_dropin_reproduces_golden_dump():
+    (n,) = MINI["mvt"]
+    x1, x2, y1, y2, A = init_mvt(n, np.float64)
+    polybench.kernel_mvt(n, x1, x2, y1, y2, A)
+    d = read_dump("mvt", "f64")
+    assert_dump_equal(d["x1"], x1, slack_ulps=1)
+    assert_dump_equal(d["x2"], x2, slack_ulps=1)
+
+
+@pytest.mark.parametrize("tname,dtype", [("f64", np.float64), ("f32", np.float32)])
+def test_kernel_syrk_dropin_reproduces_golden_dump(tname, dtype):
+    n, m = MINI["syrk"]
+    alpha, beta, Cm, A = init_syrk(n, m, dtype)
+    polybench.kernel_syrk(n, m, alpha, beta, Cm, A)
+    assert_dump_equal(read_dump("syrk", tname)["C"], Cm, slack_ulps=1)
+
+
+def test_host_and_device_operands_can_be_mixed():
+    M, N, K = 96, 64, 48
+    A = dev_fill(M, K, torch.float64, 1, -1.0, 1.0)
+    hB = pbo.fill(K, N, np.float64, SEED, 2, -1.0, 1.0)
+    hC = pbo.fill(M, N, np.float64, SEED, 3, -1.0, 1.0)
+    ref = pbo.gemm(1.5, 1.2, hC.copy(), np.ascontiguousarray(A.cpu().numpy()), hB)
+    pgb.gemm(1.5, A, hB, 1.2, hC)  # returns after the copy-back
+    assert normwise(hC, ref) <= 1e-12
