@@ -146,8 +146,9 @@ int32_t pgb200PollDeviceStatus(void);
 /* Measured peak of the current GPU, the denominators of the fp64 rooflines:
  * kind 0 = fp64 tensor (best of the mma.sync .f64 shapes; 10/11/12/13 select
  * m16n8k4 / k8 / k16 / m8n8k4), 1 = fp64 FMA, in GFLOP/s from register-only
- * issue loops; 2 = read-only HBM sweep over 2 GiB in GB/s.  Synchronises the
- * stream.  No counterpart in the reference. */
+ * issue loops; 2 = read-only HBM sweep over 2 GiB in GB/s; 3 = dense TF32
+ * tensor rate (tcgen05.mma kind::tf32 issue loop) in GFLOP/s, of which the
+ * 3xTF32 fp32 path can deliver at most a third.  Synchronises the stream.  No counterpart in the reference. */
 int32_t pgb200ProbePeak(void *stream, int32_t kind, double *out);
 
 /* How many of this library's kernels this thread has launched so far. */

@@ -111,6 +111,9 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
                     const float *A, int64_t lda, const float *B, int64_t ldb, bool transB,
                     float beta, float *C, int64_t ldc, bool lower, int64_t row0);
 
+// kind::tf32 tensor-pipe issue-rate probe (dense GFLOP/s).
+int32_t tf32_peak_probe(cudaStream_t s, double *gflops);
+
 // HBM-streaming mat-vec: y1 = beta*y1 + alpha*A*x1 (if y1) and
 // y2 = beta*y2 + alpha*A^T*x2 (if y2) in one pass over A[MxN].
 int32_t stream_matvec(cudaStream_t s, int64_t M, int64_t N, const double *A, int64_t lda,

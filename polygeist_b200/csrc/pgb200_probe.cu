@@ -164,6 +164,7 @@ extern "C" int32_t pgb200ProbePeak(void *stream, int32_t kind, double *out) {
     *out = (double)(bytes - 4096) / (ms * 1e-3) * 1e-9;
     return PGB200_OK;
   }
+  if (kind == 3) return tf32_peak_probe(s, out);
   set_error("ProbePeak: unknown kind %d", kind);
   return PGB200_ERR_INVALID;
 }

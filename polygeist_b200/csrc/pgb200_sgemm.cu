@@ -1,9 +1,616 @@
-// placeholder until the tcgen05 path lands: reports UNSUPPORTED so that the
-// caller takes the SIMT kernels.
+// fp32 GEMM / SYRK on the 5th-generation tensor cores (tcgen05 + tensor memory)
+// with an error-compensated 3xTF32 split.
+//
+//   a = a_hi + a_lo,  a_hi = tf32(a),  a_lo = tf32(a - a_hi)     (same for b)
+//   a*b ~= a_lo*b_hi + a_hi*b_lo + a_hi*b_hi                      (a_lo*b_lo dropped)
+//
+// Two launches per call:
+//   1. split kernels write the hi/lo planes of both operands to scratch memory,
+//      K-major ([rows][Kp] with Kp a multiple of 32, so every plane row is
+//      16-byte aligned whatever the caller's leading dimension was).  A row-major
+//      B[K][N] is transposed on the way, so the tensor cores only ever see the
+//      plain K-major / 64-byte-swizzle operand layout.
+//   2. a persistent, warp-specialised GEMM over the planes:
+//        warp 0    TMA producer: four 2-D tile loads per K-block into a 4-stage
+//                  shared-memory ring (mbarrier transaction counts);
+//        warp 1    one elected thread issues tcgen05.mma kind::tf32 (M=128,
+//                  N=256, K=8), six per K-block of 16, accumulating in tensor
+//                  memory; tcgen05.commit releases ring stages and publishes
+//                  accumulators;
+//        warps 2-9 drain warps: tcgen05.ld the 128x256 fp32 accumulator
+//                  (each thread one row x 128 columns), add it into fp32
+//                  registers, and at the end of a tile apply alpha/beta and store.
+//      Tensor memory holds two 256-column accumulators, so the tensor cores work
+//      on chunk c+1 (or the next tile) while chunk c is drained.
+//
+// Why chunks.  The tensor core adds each K=8 partial product into the fp32
+// accumulator with truncation, which biases long all-positive sums; draining
+// every `chunk_kblocks` K-blocks and adding the chunks in round-to-nearest fp32
+// registers bounds that bias independently of K.
+//
+// Every wait is time-bounded: on expiry the kernel records a code in the
+// host-visible status word, leaves its loops, frees its tensor memory and
+// returns.
 #include "pgb200_internal.h"
+
 namespace pgb200 {
-int32_t tf32x3_gemm(cudaStream_t, int64_t, int64_t, int64_t, float, const float *, int64_t,
-                    const float *, int64_t, bool, float, float *, int64_t, bool, int64_t) {
-  return PGB200_ERR_UNSUPPORTED;
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 4;                      // 8 KiB per plane tile
+constexpr int B_BYTES = BN * BK * 4;                      // 16 KiB per plane tile
+constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;    // 48 KiB
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 32 * (2 + EPI_WARPS);
+constexpr int TMEM_COLS = 512;
+constexpr long long WAIT_CYCLES = 4000000000ll;           // ~2 s
+constexpr int DEFAULT_CHUNK_KBLOCKS = 32;                 // 512 K-elements
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Time-bounded wait: false when ~2 s of SM cycles passed without completion.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 64; i++)
+      if (mbar_try(bar, parity)) return true;
+    if (clock64() - t0 > WAIT_CYCLES) return false;
+  }
+}
+__device__ __forceinline__ void report_status(int32_t *status, int32_t code, int32_t detail) {
+  volatile int32_t *s = status;
+  s[1] = detail;
+  s[0] = code;
+  __threadfence_system();
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are one 64-byte
+// swizzle span (16 fp32): 8-row groups are 512 bytes apart (stride byte offset),
+// the leading byte offset is unused for swizzled K-major layouts, descriptor
+// version 1 (sm_100), layout type 4 = 64-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);        // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                          // leading byte offset (ignored)
+  d |= (uint64_t)((8 * BK * 4) >> 4) << 32;        // stride byte offset = 512 B
+  d |= (uint64_t)1 << 46;                          // descriptor version
+  d |= (uint64_t)4 << 61;                          // SWIZZLE_64B
+  return d;
+}
+
+// kind::tf32 instruction descriptor: fp32 accumulator, tf32 A and B, both
+// K-major, N=256, M=128.
+constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                           ((uint32_t)(BM >> 4) << 24);
+
+struct Tiles {
+  int64_t tiles_m, tiles_n, total;
+  int64_t row0;  // absolute row of local row 0 (lower only)
+  int lower;
+};
+
+// Columns tiles of tile-row tm that intersect j <= i (lower) or all of them.
+__device__ __forceinline__ int64_t row_tiles(const Tiles &t, int64_t tm) {
+  if (!t.lower) return t.tiles_n;
+  const int64_t last_col = t.row0 + tm * BM + BM - 1;  // largest j of the tile row
+  const int64_t c = last_col / BN + 1;
+  return c < t.tiles_n ? c : t.tiles_n;
+}
+
+// Walks the valid tiles in row-major order; each role keeps its own cursor and
+// advances it monotonically (tile indices only grow within a CTA).
+struct TileCursor {
+  int64_t tm = 0, before = 0;  // tiles in rows < tm
+  __device__ __forceinline__ void seek(const Tiles &t, int64_t idx, int64_t *otm, int64_t *otn) {
+    if (!t.lower) {
+      // Full product: walk groups of 16 tile-rows column by column, so the
+      // ~148 tiles in flight form a 16 x 9 patch that shares 16 A panels and
+      // 9 B panels through L2 instead of streaming every B panel per wave.
+      constexpr int64_t G = 16;
+      const int64_t per_group = G * t.tiles_n;
+      const int64_t grp = idx / per_group;
+      const int64_t first = grp * G;
+      const int64_t rows = (t.tiles_m - first < G) ? (t.tiles_m - first) : G;
+      const int64_t in = idx - grp * per_group;
+      *otm = first + in % rows;
+      *otn = in / rows;
+      return;
+    }
+    for (;;) {
+      const int64_t c = row_tiles(t, tm);
+      if (idx < before + c) break;
+      before += c;
+      tm++;
+    }
+    *otm = tm;
+    *otn = idx - before;
+  }
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
+                   const __grid_constant__ CUtensorMap mapAlo,
+                   const __grid_constant__ CUtensorMap mapBhi,
+                   const __grid_constant__ CUtensorMap mapBlo, int64_t M, int64_t N, int64_t K,
+                   float alpha, float beta, float *__restrict__ C, int64_t ldc, Tiles tiles,
+                   int chunk_kblocks, int32_t *status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ uint32_t tmem_slot;
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+  const uint32_t accf0 = smem_u32(&bars[2 * STAGES]), acce0 = smem_u32(&bars[2 * STAGES + 2]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(accf0 + 8 * b, 1);
+      mbar_init(acce0 + 8 * b, EPI_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  const int64_t nkb = (K + BK - 1) / BK;
+  const int64_t nchunks = (nkb + chunk_kblocks - 1) / chunk_kblocks;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      TileCursor cur;
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < tiles.total && ok; t += gridDim.x) {
+        int64_t tm, tn;
+        cur.seek(tiles, t, &tm, &tn);
+        for (int64_t kb = 0; kb < nkb; kb++) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) {
+            report_status(status, 11, (int32_t)blockIdx.x);
+            ok = false;
+            break;
+          }
+          const uint32_t dst = ring + stage * STAGE_BYTES;
+          const uint32_t bar = full0 + 8 * stage;
+          mbar_expect_tx(bar, STAGE_BYTES);
+          const int k0 = (int)(kb * BK);
+          tma_load_2d(dst, &mapAhi, bar, k0, (int)(tm * BM));
+          tma_load_2d(dst + A_BYTES, &mapAlo, bar, k0, (int)(tm * BM));
+          tma_load_2d(dst + 2 * A_BYTES, &mapBhi, bar, k0, (int)(tn * BN));
+          tma_load_2d(dst + 2 * A_BYTES + B_BYTES, &mapBlo, bar, k0, (int)(tn * BN));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      int64_t cc = 0;  // chunks issued by this CTA so far
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < tiles.total && ok; t += gridDim.x) {
+        for (int64_t ch = 0; ch < nchunks && ok; ch++, cc++) {
+          const uint32_t buf = (uint32_t)(cc & 1);
+          const uint32_t use = (uint32_t)((cc >> 1) & 1);
+          if (!mbar_wait(acce0 + 8 * buf, use ^ 1)) {
+            report_status(status, 12, (int32_t)blockIdx.x);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + buf * BN;
+          const int64_t kb_end = (ch + 1) * chunk_kblocks < nkb ? (ch + 1) * chunk_kblocks : nkb;
+          for (int64_t kb = ch * chunk_kblocks; kb < kb_end; kb++) {
+            if (!mbar_wait(full0 + 8 * stage, phase)) {
+              report_status(status, 13, (int32_t)blockIdx.x);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t sa = ring + stage * STAGE_BYTES;
+            const uint64_t ahi = smem_desc_sw64(sa), alo = smem_desc_sw64(sa + A_BYTES);
+            const uint64_t bhi = smem_desc_sw64(sa + 2 * A_BYTES);
+            const uint64_t blo = smem_desc_sw64(sa + 2 * A_BYTES + B_BYTES);
+            const bool first = (kb == ch * chunk_kblocks);
+#pragma unroll
+            for (int ks = 0; ks < BK / 8; ks++) {
+              // +32 bytes per K=8 step inside the swizzled row (encoded >> 4).
+              const uint64_t ko = (uint64_t)(ks * 2);
+              tc_mma_tf32(tmem_d, alo + ko, bhi + ko, IDESC, (first && ks == 0) ? 0u : 1u);
+              tc_mma_tf32(tmem_d, ahi + ko, blo + ko, IDESC, 1u);
+              tc_mma_tf32(tmem_d, ahi + ko, bhi + ko, IDESC, 1u);
+            }
+            tc_commit(empty0 + 8 * stage);  // stage reusable once these MMAs retire
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+          if (ok) tc_commit(accf0 + 8 * buf);  // accumulator complete
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- drain warps
+    const int ew = warp - 2;
+    const int quarter = warp & 3;      // tensor-memory lane quarter this warp may read
+    const int half = ew >> 2;          // which 128 columns of the 256
+    TileCursor cur;
+    int64_t cc = 0;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; t < tiles.total && ok; t += gridDim.x) {
+      int64_t tm, tn;
+      cur.seek(tiles, t, &tm, &tn);
+      float acc[128];
+#pragma unroll
+      for (int i = 0; i < 128; i++) acc[i] = 0.0f;
+      for (int64_t ch = 0; ch < nchunks && ok; ch++, cc++) {
+        const uint32_t buf = (uint32_t)(cc & 1);
+        const uint32_t use = (uint32_t)((cc >> 1) & 1);
+        if (!mbar_wait(accf0 + 8 * buf, use)) {
+          if (lane == 0) report_status(status, 14, (int32_t)blockIdx.x);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr =
+            tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + (uint32_t)(half * 128);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          uint32_t v[32];
+          tc_ld32(taddr + j * 32, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i++) acc[j * 32 + i] += __uint_as_float(v[i]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acce0 + 8 * buf);
+      }
+      if (!ok) break;
+      // alpha/beta epilogue: this thread owns row r, columns [cb, cb+128).
+      const int64_t r = tm * BM + quarter * 32 + lane;
+      const int64_t cb = tn * BN + half * 128;
+      if (r < M && cb < N) {
+        int64_t lim = N - 1;
+        if (tiles.lower && r + tiles.row0 < lim) lim = r + tiles.row0;
+        float *crow = C + r * ldc;
+        const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+#pragma unroll
+        for (int j = 0; j < 128; j += 4) {
+          const int64_t c = cb + j;
+          if (c > lim) break;
+          if (vec_ok && c + 3 <= lim) {
+            float4 o;
+            o.x = alpha * acc[j];
+            o.y = alpha * acc[j + 1];
+            o.z = alpha * acc[j + 2];
+            o.w = alpha * acc[j + 3];
+            if (beta != 0.0f) {
+              const float4 old = *reinterpret_cast<const float4 *>(crow + c);
+              o.x = fmaf(beta, old.x, o.x);
+              o.y = fmaf(beta, old.y, o.y);
+              o.z = fmaf(beta, old.z, o.z);
+              o.w = fmaf(beta, old.w, o.w);
+            }
+            *reinterpret_cast<float4 *>(crow + c) = o;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              if (c + e <= lim) {
+                float o = alpha * acc[j + e];
+                if (beta != 0.0f) o = fmaf(beta, crow[c + e], o);
+                crow[c + e] = o;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ split kernels
+__device__ __forceinline__ void split_tf32(float a, float *hi, float *lo) {
+  uint32_t h, l;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
+  const float hf = __uint_as_float(h);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(a - hf));
+  *hi = hf;
+  *lo = __uint_as_float(l);
+}
+
+// src[rows][K] (ld) -> hi/lo[rows][Kp]; columns K..Kp-1 are zero-filled.
+__global__ void split_rows_kernel(const float *__restrict__ src, int64_t ld, int64_t rows,
+                                  int64_t K, int64_t Kp, float *__restrict__ hi,
+                                  float *__restrict__ lo) {
+  const int64_t total = rows * Kp;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / Kp, k = i - r * Kp;
+    float h = 0.0f, l = 0.0f;
+    if (k < K) split_tf32(src[r * ld + k], &h, &l);
+    hi[i] = h;
+    lo[i] = l;
+  }
+}
+
+// src[K][N] (ld) -> hi/lo[N][Kp] (transposed through a 32x33 shared tile).
+__global__ void split_transpose_kernel(const float *__restrict__ src, int64_t ld, int64_t K,
+                                       int64_t N, int64_t Kp, float *__restrict__ hi,
+                                       float *__restrict__ lo, int64_t tiles_k) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int64_t tk = blockIdx.x % tiles_k, tn = blockIdx.x / tiles_k;
+  const int64_t k0 = tk * 32, n0 = tn * 32;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int64_t k = k0 + ty + 8 * i, n = n0 + tx;
+    tile[ty + 8 * i][tx] = (k < K && n < N) ? src[k * ld + n] : 0.0f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int64_t n = n0 + ty + 8 * i, k = k0 + tx;
+    if (n < N && k < Kp) {
+      float h, l;
+      split_tf32(tile[tx][ty + 8 * i], &h, &l);
+      hi[n * Kp + k] = h;
+      lo[n * Kp + k] = l;
+    }
+  }
+}
+
+int32_t make_plane_map(CUtensorMap *map, const float *base, int64_t rows, int64_t K, int64_t Kp,
+                       int box_rows) {
+  const uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows};
+  const uint64_t str[1] = {(uint64_t)Kp * 4};
+  const uint32_t box[2] = {BK, (uint32_t)box_rows};
+  return encode_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, str, box,
+                           CU_TENSOR_MAP_SWIZZLE_64B);
+}
+
+
+// Tensor-pipe peak probe: every CTA issues `iters` back-to-back kind::tf32 MMAs
+// (M=128, N=256, K=8) on whatever its shared memory holds and waits for them.
+__global__ void __launch_bounds__(128, 1) tf32_probe_kernel(int iters, int32_t *status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // Finite operand data so that the accumulators stay finite.
+  for (int i = threadIdx.x; i < (A_BYTES + B_BYTES) / 4; i += blockDim.x)
+    reinterpret_cast<float *>(smem_raw + (base - smem_u32(smem_raw)))[i] = 1.0f / (float)(1 + (i & 7));
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  if (warp == 0 && lane == 0) {
+    const uint64_t a = smem_desc_sw64(base), b = smem_desc_sw64(base + A_BYTES);
+    for (int i = 0; i < iters; i++)
+      tc_mma_tf32(tmem_base + (uint32_t)((i & 1) * BN), a + (uint64_t)((i & 1) * 2),
+                  b + (uint64_t)((i & 1) * 2), IDESC, i < 2 ? 0u : 1u);
+    tc_commit(smem_u32(&bar));
+    if (!mbar_wait(smem_u32(&bar), 0)) report_status(status, 21, (int32_t)blockIdx.x);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+}  // namespace
+
+int32_t tf32_peak_probe(cudaStream_t s, double *gflops) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  const int iters = 8192, smem = A_BYTES + B_BYTES + 1024;
+  PGB_CUDA(cudaFuncSetAttribute(tf32_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                smem));
+  cudaEvent_t e0, e1;
+  PGB_CUDA(cudaEventCreate(&e0));
+  PGB_CUDA(cudaEventCreate(&e1));
+  float best = 1e30f;
+  for (int r = 0; r < 5; r++) {
+    PGB_CUDA(cudaEventRecord(e0, s));
+    tf32_probe_kernel<<<rt->num_sms, 128, smem, s>>>(iters, rt->status_dev);
+    PGB_CUDA(cudaEventRecord(e1, s));
+    PGB_CUDA(cudaEventSynchronize(e1));
+    float ms = 0;
+    PGB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    if (r >= 1 && ms < best) best = ms;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  PGB_CUDA(cudaGetLastError());
+  *gflops = 2.0 * BM * BN * 8 * (double)iters * rt->num_sms / (best * 1e-3) * 1e-9;
+  return PGB200_OK;
+}
+
+int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha, const float *A,
+                    int64_t lda, const float *B, int64_t ldb, bool transB, float beta, float *C,
+                    int64_t ldc, bool lower, int64_t row0) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  if (K == 0) return PGB200_ERR_UNSUPPORTED;  // nothing to contract: SIMT path scales C
+  if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31))
+    return PGB200_ERR_UNSUPPORTED;
+  const int64_t Kp = (K + 31) / 32 * 32;
+  // For the rank-k update both operands are rows of the same matrix: when B
+  // starts at A's row 0 (or is A itself) one pair of planes serves both.
+  const bool shared_planes = transB && (ldb == lda) && (B <= A) &&
+                             ((A - B) % lda == 0) && ((A - B) / lda + M <= N);
+  const int64_t a_off_rows = shared_planes ? (A - B) / lda : 0;
+  const size_t plane_a = (size_t)M * Kp, plane_b = (size_t)N * Kp;
+  const size_t floats = shared_planes ? 2 * plane_b : 2 * plane_a + 2 * plane_b;
+  void *ws = nullptr;
+  PGB_TRY(get_workspace(s, floats * sizeof(float), &ws));
+  float *Bhi = static_cast<float *>(ws), *Blo = Bhi + plane_b;
+  float *Ahi = shared_planes ? Bhi + a_off_rows * Kp : Blo + plane_b;
+  float *Alo = shared_planes ? Blo + a_off_rows * Kp : Ahi + plane_a;
+
+  const int64_t cap = (int64_t)rt->num_sms * 8;
+  auto grid_for = [&](int64_t total) {
+    int64_t g = (total + 255) / 256;
+    return (unsigned)(g < 1 ? 1 : (g > cap ? cap : g));
+  };
+  if (transB) {
+    split_rows_kernel<<<grid_for(N * Kp), 256, 0, s>>>(B, ldb, N, K, Kp, Bhi, Blo);
+  } else {
+    const int64_t tk = Kp / 32, tn = (N + 31) / 32;
+    PGB_REQUIRE(tk * tn < (int64_t(1) << 31), "tf32x3_gemm: operand too large");
+    split_transpose_kernel<<<(unsigned)(tk * tn), 256, 0, s>>>(B, ldb, K, N, Kp, Bhi, Blo, tk);
+  }
+  note_launch(PATH_TCGEN05);
+  if (!shared_planes) {
+    split_rows_kernel<<<grid_for(M * Kp), 256, 0, s>>>(A, lda, M, K, Kp, Ahi, Alo);
+    note_launch(PATH_TCGEN05);
+  }
+  PGB_CUDA(cudaGetLastError());
+
+  CUtensorMap mAhi, mAlo, mBhi, mBlo;
+  PGB_TRY(make_plane_map(&mAhi, Ahi, M, K, Kp, BM));
+  PGB_TRY(make_plane_map(&mAlo, Alo, M, K, Kp, BM));
+  PGB_TRY(make_plane_map(&mBhi, Bhi, N, K, Kp, BN));
+  PGB_TRY(make_plane_map(&mBlo, Blo, N, K, Kp, BN));
+
+  Tiles tiles;
+  tiles.tiles_m = (M + BM - 1) / BM;
+  tiles.tiles_n = (N + BN - 1) / BN;
+  tiles.row0 = row0;
+  tiles.lower = lower ? 1 : 0;
+  if (lower) {
+    int64_t total = 0;
+    for (int64_t tm = 0; tm < tiles.tiles_m; tm++) {
+      const int64_t c = (row0 + tm * BM + BM - 1) / BN + 1;
+      total += c < tiles.tiles_n ? c : tiles.tiles_n;
+    }
+    tiles.total = total;
+  } else {
+    tiles.total = tiles.tiles_m * tiles.tiles_n;
+  }
+  int chunk = rt->cfg.sgemm_chunk_kblocks > 0 ? rt->cfg.sgemm_chunk_kblocks : DEFAULT_CHUNK_KBLOCKS;
+  const unsigned grid = (unsigned)(tiles.total < rt->num_sms ? tiles.total : rt->num_sms);
+  PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                SMEM_BYTES));
+  tf32x3_gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(mAhi, mAlo, mBhi, mBlo, M, N, K, alpha, beta,
+                                                        C, ldc, tiles, chunk, rt->status_dev);
+  note_launch(PATH_TCGEN05);
+  PGB_CUDA(cudaGetLastError());
+  return PGB200_OK;
+}
+
 }  // namespace pgb200
