@@ -37,6 +37,8 @@ WORKLOADS = {
                       desc="configs[1]: fp64 GEMM 4096^3, uniform [-1,1), alpha=1.5 beta=1.2"),
     "sgemm1024": dict(dtype="f32", M=1024, N=1024, K=1024, lo=0.0, hi=1.0,
                       desc="configs[0]: fp32 GEMM 1024^3, uniform [0,1), alpha=1.5 beta=1.2"),
+    "sgemm4096": dict(dtype="f32", M=4096, N=4096, K=4096, lo=0.0, hi=1.0,
+                      desc="fp32 GEMM 4096^3 (3xTF32), uniform [0,1); profiling-size case"),
     "sgemm8192": dict(dtype="f32", M=8192, N=8192, K=8192, lo=0.0, hi=1.0,
                       desc="fp32 GEMM 8192^3 (3xTF32), uniform [0,1)"),
     "mvt16384": dict(dtype="f64", N=16384, lo=0.0, hi=1.0,
@@ -409,11 +411,19 @@ def run_pgb200(args, w, name):
                     "peak_source": "fp64 tensor (mma.sync .f64) issue-rate probe measured in this "
                                    "run; MEASURED_PEAKS.json has no fp64 figure"}
         else:
-            roof = None  # filled by the tcgen05 path's own probe when present
+            # 3xTF32: every useful FMA costs three tensor-core FMAs, so the
+            # tensor pipe does 3 * 2MNK flop per step; compare with dense TF32.
+            peak = pgb.probe_peak(pgb.PEAK_TF32) / 1e3
+            ach = 3 * units / (ms_per_step * 1e-3) / 1e12
+            roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+                    "frac": ach / peak, "traffic": None,
+                    "peak_source": "dense TF32 tcgen05.mma issue-rate probe measured in this run "
+                                   "(MEASURED_PEAKS.json has no TF32 figure); achieved counts the "
+                                   "3 tensor products per useful product (useful = achieved/3)"}
 
     # ---- end to end through the reference-facing drop-in, host arrays ----
     e2e = None
-    if name in ("dgemm4096", "sgemm1024", "sgemm8192") and not args.kernel_only:
+    if name in ("dgemm4096", "sgemm1024", "sgemm4096", "sgemm8192") and not args.kernel_only:
         M, N, K = w["M"], w["N"], w["K"]
         np_dt = np.float64 if w["dtype"] == "f64" else np.float32
 

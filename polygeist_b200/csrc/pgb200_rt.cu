@@ -68,6 +68,16 @@ int32_t get_runtime(Runtime **out) {
               prop.major, prop.minor);
     return PGB200_ERR_UNSUPPORTED;
   }
+  {
+    // Keep staging buffers of the host-array path cached in the stream-ordered
+    // pool instead of returning them to the driver at every synchronisation.
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+      uint64_t keep = UINT64_MAX;
+      cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    cudaGetLastError();
+  }
   Runtime *rt = new Runtime();
   rt->cfg = g_cfg;
   rt->num_sms = prop.multiProcessorCount;
@@ -168,18 +178,28 @@ int32_t stage(cudaStream_t s, const T *p, int64_t rows, int64_t cols, int64_t ld
   void *d = nullptr;
   PGB_CUDA(cudaMallocAsync(&d, (size_t)rows * st->ld * sizeof(T), s));
   st->dev = static_cast<T *>(d);
-  if (in)
-    PGB_CUDA(cudaMemcpy2DAsync(st->dev, st->ld * sizeof(T), p, ld * sizeof(T), cols * sizeof(T),
-                               rows, cudaMemcpyHostToDevice, s));
+  if (in) {
+    if (st->ld == ld)
+      PGB_CUDA(cudaMemcpyAsync(st->dev, p, (size_t)rows * ld * sizeof(T), cudaMemcpyHostToDevice,
+                               s));
+    else
+      PGB_CUDA(cudaMemcpy2DAsync(st->dev, st->ld * sizeof(T), p, ld * sizeof(T), cols * sizeof(T),
+                                 rows, cudaMemcpyHostToDevice, s));
+  }
   return PGB200_OK;
 }
 
 template <typename T>
 int32_t finish(cudaStream_t s, Staged<T> *st) {
   if (!st->host) return PGB200_OK;
-  if (st->copy_back)
-    PGB_CUDA(cudaMemcpy2DAsync(st->host, st->host_ld * sizeof(T), st->dev, st->ld * sizeof(T),
-                               st->cols * sizeof(T), st->rows, cudaMemcpyDeviceToHost, s));
+  if (st->copy_back) {
+    if (st->ld == st->host_ld && st->ld == st->cols)
+      PGB_CUDA(cudaMemcpyAsync(st->host, st->dev, (size_t)st->rows * st->ld * sizeof(T),
+                               cudaMemcpyDeviceToHost, s));
+    else
+      PGB_CUDA(cudaMemcpy2DAsync(st->host, st->host_ld * sizeof(T), st->dev, st->ld * sizeof(T),
+                                 st->cols * sizeof(T), st->rows, cudaMemcpyDeviceToHost, s));
+  }
   PGB_CUDA(cudaFreeAsync(st->dev, s));
   st->host = nullptr;
   return PGB200_OK;

@@ -47,7 +47,7 @@ constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 32 * (2 + EPI_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_CYCLES = 4000000000ll;           // ~2 s
-constexpr int DEFAULT_CHUNK_KBLOCKS = 32;                 // 512 K-elements
+constexpr int DEFAULT_CHUNK_KBLOCKS = 16;                 // 256 K-elements
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -81,6 +81,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (;;) {
     for (int i = 0; i < 64; i++)
       if (mbar_try(bar, parity)) return true;
+    if (clock64() - t0 > WAIT_CYCLES) return false;
+  }
+}
+// Same, for waits entered by whole warps: sleeps between polls so that the
+// spinning warps do not compete with the single MMA-issuing thread.
+__device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 16; i++) {
+      __nanosleep(64);
+      if (mbar_try(bar, parity)) return true;
+    }
     if (clock64() - t0 > WAIT_CYCLES) return false;
   }
 }
@@ -334,7 +347,7 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
       for (int64_t ch = 0; ch < nchunks && ok; ch++, cc++) {
         const uint32_t buf = (uint32_t)(cc & 1);
         const uint32_t use = (uint32_t)((cc >> 1) & 1);
-        if (!mbar_wait(accf0 + 8 * buf, use)) {
+        if (!mbar_wait_backoff(accf0 + 8 * buf, use)) {
           if (lane == 0) report_status(status, 14, (int32_t)blockIdx.x);
           ok = false;
           break;
@@ -343,12 +356,15 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
         const uint32_t taddr =
             tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + (uint32_t)(half * 128);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-          uint32_t v[32];
-          tc_ld32(taddr + j * 32, v);
+        for (int j = 0; j < 4; j += 2) {
+          uint32_t v0[32], v1[32];
+          tc_ld32(taddr + j * 32, v0);
+          tc_ld32(taddr + j * 32 + 32, v1);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; i++) acc[j * 32 + i] += __uint_as_float(v[i]);
+          for (int i = 0; i < 32; i++) acc[j * 32 + i] += __uint_as_float(v0[i]);
+#pragma unroll
+          for (int i = 0; i < 32; i++) acc[j * 32 + 32 + i] += __uint_as_float(v1[i]);
         }
         tc_fence_before();
         __syncwarp();
