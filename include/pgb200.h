@@ -113,6 +113,36 @@ int32_t pgb200Dgemv(void *stream, int32_t transA, int64_t M, int64_t N,
 int32_t pgb200Dmvt(void *stream, int64_t N, const double *A, int64_t lda,
                    const double *y1, const double *y2, double *x1, double *x2);
 
+/* The same fused pair, x1 += A*y1 and x2 += A^T*y2, for callers that are not
+ * allowed to allocate.  This entry point has no counterpart in the reference.
+ *
+ * Who needs it: a host program that hands all GPU memory to its own arena at
+ * start-up (any later cudaMalloc by a library would simply fail), and code in a
+ * latency-critical section, where cudaMalloc / cudaFree would stall every stream
+ * of the device.  pgb200Dmvt keeps its per-tile partial sums in a workspace that
+ * it grows on demand; this variant keeps them in a fixed 1 MiB array inside the
+ * library image, so the call reserves and releases nothing - no cudaMalloc, no
+ * cudaFree, no memory pool, no pinned host block.  Every GPU that loads the
+ * library holds that 1 MiB until the process exits.
+ *
+ * Limits and rules:
+ *  - N <= 4096 (what the fixed array can hold); larger N is rejected with
+ *    PGB200_ERR_INVALID and a message that names the limit.
+ *  - A, y1, y2, x1, x2 must all be device (or managed) memory: host arrays would
+ *    need a staging buffer, so they are rejected too.
+ *  - The first call on each device looks up the device address of the array
+ *    (once, with that device current).  Make that first call outside any
+ *    stream capture.
+ *  - All calls on a device share the one array.  It still holds the previous
+ *    call's partial sums when the next call starts; that is harmless because
+ *    each call overwrites every entry before reading it (nothing has to start
+ *    at zero).  Two calls that overlap on the GPU - different streams, or two
+ *    host threads - would overwrite each other's partial sums: serialise them.
+ * The result is the same as pgb200Dmvt's (same kernels, same summation order). */
+int32_t pgb200DmvtNoAlloc(void *stream, int64_t N, const double *A, int64_t lda,
+                          const double *y1, const double *y2, double *x1,
+                          double *x2);
+
 /* Counter-based uniform generator used by the test and benchmark harness
  * (device pointer only).  Element (r,c) of the logical rows x cols array, for
  * r in [row0,row0+rows), written at dst[(r-row0)*ld + c]:

@@ -52,6 +52,7 @@ SIGNATURES = {
     "pgb200SsyrkRows": (_i32, [_vp, _i64, _i64, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
     "pgb200Dgemv": (_i32, [_vp, _i32, _i64, _i64, _f64, _vp, _i64, _vp, _f64, _vp]),
     "pgb200Dmvt": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp]),
+    "pgb200DmvtNoAlloc": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp]),
     "pgb200FillUniformF64": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, C.c_uint64, C.c_uint32, _f64, _f64]),
     "pgb200FillUniformF32": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, C.c_uint64, C.c_uint32, _f32, _f32]),
     "pgb200LastPath": (_i32, []),

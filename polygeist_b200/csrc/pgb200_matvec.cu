@@ -13,6 +13,8 @@
 // bytes.  Row dots are reduced with shuffles once per row; column sums stay in
 // registers for all rows of the tile and are combined across the 8 warps
 // through shared memory at the end of the tile.
+#include <mutex>
+
 #include "pgb200_internal.h"
 
 namespace pgb200 {
@@ -192,3 +194,100 @@ int32_t stream_matvec(cudaStream_t s, int64_t M, int64_t N, const double *A, int
 }
 
 }  // namespace pgb200
+
+// ---------------------------------------------------------------------------
+// pgb200DmvtNoAlloc: the fused mat-vec pair for callers that must not allocate.
+//
+// Same two kernels as pgb200Dmvt, but the per-tile partial sums go to a fixed
+// array that is part of the library image instead of the grown-on-demand
+// workspace, and nothing in the call path reserves or releases memory (no
+// cudaMalloc / cudaFree / stream-ordered pool, no pinned host block).  Every
+// GPU that loads the library carries the array (1 MiB) until the process exits.
+// ---------------------------------------------------------------------------
+namespace pgb200 {
+namespace {
+
+constexpr int64_t NOALLOC_MAX_N = 4096;
+constexpr int64_t NOALLOC_TILES = (NOALLOC_MAX_N + MV_TC - 1) / MV_TC;
+constexpr size_t NOALLOC_DOUBLES = (size_t)2 * NOALLOC_TILES * NOALLOC_MAX_N;  // 1 MiB
+
+static __device__ __align__(256) double g_noalloc_scratch[NOALLOC_DOUBLES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+struct NoAllocDevice {
+  double *scratch = nullptr;  // device address of g_noalloc_scratch on this GPU
+  int num_sms = 0;
+};
+std::mutex g_noalloc_mu;
+NoAllocDevice g_noalloc_dev[NOALLOC_MAX_DEVICES];
+
+// One-time set-up for the current device.  In host code the name of a
+// __device__ array is only a handle; the address a kernel can use has to be
+// asked for, with the owning device current.
+int32_t noalloc_device(NoAllocDevice **out) {
+  int dev = 0;
+  PGB_CUDA(cudaGetDevice(&dev));
+  PGB_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "DmvtNoAlloc: device index %d out of range",
+              dev);
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  NoAllocDevice &d = g_noalloc_dev[dev];
+  if (!d.scratch) {
+    int major = 0, sms = 0;
+    PGB_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    PGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (major != 10) {
+      set_error("DmvtNoAlloc: device %d is not sm_100", dev);
+      return PGB200_ERR_UNSUPPORTED;
+    }
+    double *ptr = nullptr;
+    PGB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_scratch));
+    PGB_REQUIRE(ptr != nullptr, "DmvtNoAlloc: no device address for the static scratch array");
+    d.num_sms = sms;
+    d.scratch = ptr;
+  }
+  *out = &d;
+  return PGB200_OK;
+}
+
+}  // namespace
+}  // namespace pgb200
+
+extern "C" int32_t pgb200DmvtNoAlloc(void *stream, int64_t N, const double *A, int64_t lda,
+                                     const double *y1, const double *y2, double *x1, double *x2) {
+  using namespace pgb200;
+  PGB_REQUIRE(N >= 0, "DmvtNoAlloc: negative size");
+  if (N == 0) return PGB200_OK;
+  PGB_REQUIRE(N <= NOALLOC_MAX_N,
+              "DmvtNoAlloc: N = %lld exceeds the static scratch limit of %lld; use pgb200Dmvt",
+              (long long)N, (long long)NOALLOC_MAX_N);
+  PGB_REQUIRE(A && y1 && y2 && x1 && x2 && lda >= N,
+              "DmvtNoAlloc: null pointer or lda (%lld) < N (%lld)", (long long)lda, (long long)N);
+  // Host arrays would need a staging buffer, i.e. an allocation.
+  PGB_REQUIRE(!is_host_pointer(A) && !is_host_pointer(y1) && !is_host_pointer(y2) &&
+                  !is_host_pointer(x1) && !is_host_pointer(x2),
+              "DmvtNoAlloc: all arrays must be device memory (staging host arrays would allocate)");
+  NoAllocDevice *d = nullptr;
+  PGB_TRY(noalloc_device(&d));
+  cudaStream_t s = (cudaStream_t)stream;
+  const int64_t tiles_r = (N + MV_TR - 1) / MV_TR, tiles_c = (N + MV_TC - 1) / MV_TC;
+  // Every partial that the second pass reads is written by the first pass of
+  // the same call, so nothing left over from an earlier call is ever consumed
+  // and nothing needs clearing.
+  double *p1 = d->scratch;
+  double *p2 = d->scratch + (size_t)tiles_c * N;
+  const int64_t ntiles = tiles_r * tiles_c;
+  const int64_t cap = (int64_t)d->num_sms * 2;
+  const unsigned grid = (unsigned)(ntiles < cap ? ntiles : cap);
+  const bool vec = aligned16(A) && (lda % 2 == 0) && (N % 2 == 0);
+  if (vec)
+    matvec_tile_kernel<true><<<grid, MV_WARPS * 32, 0, s>>>(A, lda, N, N, y1, y2, p1, p2, tiles_r,
+                                                            tiles_c);
+  else
+    matvec_tile_kernel<false><<<grid, MV_WARPS * 32, 0, s>>>(A, lda, N, N, y1, y2, p1, p2,
+                                                             tiles_r, tiles_c);
+  matvec_reduce_kernel<<<(unsigned)((N + 255) / 256), 256, 0, s>>>(x1, p1, tiles_c, N, 1.0, 1.0);
+  matvec_reduce_kernel<<<(unsigned)((N + 255) / 256), 256, 0, s>>>(x2, p2, tiles_r, N, 1.0, 1.0);
+  note_launch(PATH_STREAM, 3);
+  PGB_CUDA(cudaGetLastError());
+  return PGB200_OK;
+}
