@@ -41,6 +41,12 @@ WORKLOADS = {
                       desc="fp32 GEMM 4096^3 (3xTF32), uniform [0,1); profiling-size case"),
     "sgemm8192": dict(dtype="f32", M=8192, N=8192, K=8192, lo=0.0, hi=1.0,
                       desc="fp32 GEMM 8192^3 (3xTF32), uniform [0,1)"),
+    "sgemm32768": dict(dtype="f32", M=32768, N=32768, K=32768, lo=0.0, hi=1.0, strong=True,
+                       desc="configs[4]b: fp32 GEMM 32768^3 (3xTF32), uniform [0,1), rows partitioned "
+                            "across the GPUs, B broadcast by NCCL"),
+    "ssyrk16384": dict(dtype="f32", N=16384, K=8192, lo=0.0, hi=1.0, strong=True,
+                       desc="configs[4]a: fp32 SYRK N=16384 K=8192 lower (3xTF32), uniform [0,1), rows "
+                            "partitioned by equal triangular area, A broadcast by NCCL"),
     "mvt16384": dict(dtype="f64", N=16384, lo=0.0, hi=1.0,
                      desc="fp64 mat-vec pair, N=16384 (2.1 GB; the profiling-size case of configs[2])"),
     "mvt32768": dict(dtype="f64", N=32768, lo=0.0, hi=1.0,
@@ -167,53 +173,91 @@ def algorithmic_work(name, w):
         return n * n * 8 + 6 * n * 8
     if name == "chain2mm":
         return 2 * w["ni"] * w["nj"] * w["nk"] + 2 * w["ni"] * w["nl"] * w["nj"]
+    if name.startswith("ssyrk"):
+        return w["N"] * (w["N"] + 1) * w["K"]
     return 2 * w["M"] * w["N"] * w["K"]
 
 
-# ----------------------------------------------------------------------------- reference arm
-def run_reference(args, w, name):
-    """The reference's own CPU implementation of the path (oracle/_ref: kernel_gemm
-    etc. compiled unmodified from the reference sources), all host cores, each
-    thread running the unmodified kernel on an independent slab of rows."""
+# ----------------------------------------------------------------------------- CPU legs
+def metric_of(name):
+    if name.startswith("mvt"):
+        return "HBM GB/s of the raised mat-vec pair", "GB/s", 1e9
+    return "GFLOP/s per raised op", "GFLOP/s", 1e9
+
+
+def cpu_sample(w, name):
+    """A bounded sample of the workload for the host cores.  Returns
+    (units_per_step, step_fn, threads_used, description, kind).
+
+    The kernels are the reference's own compiled kernel_* functions
+    (oracle/_ref, kind "reference") when present, else this repository's C
+    restatement (kind "port").  The loop nests are sequential, so all host
+    threads are used by running the unmodified kernel on independent row slabs
+    (gemm, 2mm: rows are independent) or on independent problem instances
+    (syrk: the j<=i bound ties a slab to its absolute rows)."""
     import concurrent.futures as cf
 
     import numpy as np
 
     from oracle import pbo, ref
-    if not ref.available():
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "oracle/_ref is not built and the reference tree is not mounted"}))
-        return
+    have_ref = ref.available()
+    kind = "reference" if have_ref else "port"
     cores = os.cpu_count() or 1
     np_dt = np.float64 if w["dtype"] == "f64" else np.float32
+    lo, hi = w["lo"], w["hi"]
     if name.startswith("mvt"):
-        n = 8192  # bounded sample: same nests on an 8192^2 matrix (0.5 GB)
-        A = pbo.fill(n, n, np_dt, SEED, 1, w["lo"], w["hi"])
-        v = [pbo.fill_vec(n, np_dt, SEED, 2 + k, w["lo"], w["hi"]) for k in range(4)]
-        sample = f"kernel_mvt at N={n} (1 thread: the nests are sequential)"
-        units = n * n * 8 + 6 * n * 8
-        used = 1
+        n = 4096
+        A = pbo.fill(n, n, np_dt, SEED, 1, lo, hi)
+        v = [pbo.fill_vec(n, np_dt, SEED, 2 + k, lo, hi) for k in range(4)]
 
         def step():
-            ref.kernel_mvt(n, v[0], v[1], v[2], v[3], A)
+            if have_ref:
+                ref.kernel_mvt(n, v[0], v[1], v[2], v[3], A)
+            else:
+                pbo.mvt(v[0], v[1], v[2], v[3], A)
+        return n * n * 8 + 6 * n * 8, step, 1, f"kernel_mvt at N={n}, one thread (sequential nests)", kind
+    pool = cf.ThreadPoolExecutor(max_workers=cores)
+    if name.startswith("ssyrk"):
+        n, m = 512, w["K"]
+        As = [pbo.fill(n, m, np_dt, SEED, 1, lo, hi, row0=t * n) for t in range(cores)]
+        Cs = [pbo.fill(n, n, np_dt, SEED, 3, lo, hi, row0=t * n) for t in range(cores)]
+
+        def one(t):
+            if have_ref:
+                ref.kernel_syrk(n, m, ALPHA, BETA, Cs[t], As[t])
+            else:
+                pbo.syrk(ALPHA, BETA, Cs[t], As[t])
+
+        def step():
+            list(pool.map(one, range(cores)))
+        return (cores * n * (n + 1) * m, step, cores,
+                f"{cores} independent kernel_syrk instances of n={n}, m={m}, one thread each", kind)
+    if name == "chain2mm":
+        K, N = w["nk"], w["nj"]
     else:
-        if name == "chain2mm":
-            K, N = w["nk"], w["nj"]
-        else:
-            K, N = w["K"], w["N"]
-        rows_per = 32 if name != "sgemm1024" else 1024 // cores
-        used = cores
-        B = pbo.fill(K, N, np_dt, SEED, 2, w["lo"], w["hi"])
-        As = [pbo.fill(rows_per, K, np_dt, SEED, 1, w["lo"], w["hi"], row0=t * rows_per) for t in range(used)]
-        Cs = [pbo.fill(rows_per, N, np_dt, SEED, 3, w["lo"], w["hi"], row0=t * rows_per) for t in range(used)]
-        sample = (f"kernel_gemm on {used} independent {rows_per}-row slabs of the {K}x{N} problem, "
-                  f"one thread each")
-        units = 2 * rows_per * used * N * K
-        pool = cf.ThreadPoolExecutor(max_workers=used)
+        K, N = w["K"], w["N"]
+    rows_per = 2 if name == "sgemm32768" else 16
+    B = pbo.fill(K, N, np_dt, SEED, 2, lo, hi)
+    As = [pbo.fill(rows_per, K, np_dt, SEED, 1, lo, hi, row0=t * rows_per) for t in range(cores)]
+    Cs = [pbo.fill(rows_per, N, np_dt, SEED, 3, lo, hi, row0=t * rows_per) for t in range(cores)]
 
-        def step():
-            list(pool.map(lambda t: ref.kernel_gemm(rows_per, N, K, ALPHA, BETA, Cs[t], As[t], B),
-                          range(used)))
+    def one(t):
+        if have_ref:
+            ref.kernel_gemm(rows_per, N, K, ALPHA, BETA, Cs[t], As[t], B)
+        else:
+            pbo.gemm(ALPHA, BETA, Cs[t], As[t], B)
+
+    def step():
+        list(pool.map(one, range(cores)))
+    return (2 * rows_per * cores * N * K, step, cores,
+            f"kernel_gemm on {cores} independent {rows_per}-row slabs of the {K}x{N} problem, "
+            f"one thread each", kind)
+
+
+def run_reference(args, w, name):
+    """`--impl reference`: the reference's CPU implementation of the path on
+    the host cores; each step is the bounded sample of cpu_sample()."""
+    units, step, used, sample, kind = cpu_sample(w, name)
     for _ in range(args.warmup):
         step()
     t0 = time.perf_counter()
@@ -225,75 +269,40 @@ def run_reference(args, w, name):
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"],
-        "data": "synthetic", "config": {"workload": w["desc"]},
-        "cpu_baseline": {"value": val, "unit": unit, "cores": used, "kind": "reference",
+        "higher_is_better": True, "scaling": "strong" if w.get("strong") else "weak",
+        "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": w["desc"]},
+        "cpu_baseline": {"value": val, "unit": unit, "cores": used, "kind": kind,
                          "sample": sample},
         "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
-def metric_of(name):
-    if name.startswith("mvt"):
-        return "HBM GB/s of the raised mat-vec pair", "GB/s", 1e9
-    return "GFLOP/s per raised op", "GFLOP/s", 1e9
+def cpu_baseline(w, name, budget_s=5.0):
+    """The same sample timed on rank 0 beside the GPU number."""
+    units, step, used, sample, kind = cpu_sample(w, name)
+    step()
+    t0 = time.perf_counter()
+    reps = 0
+    while reps < 2 or time.perf_counter() - t0 < budget_s:
+        step()
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    _, unit, scale = metric_of(name)
+    return {"value": units / dt / scale, "unit": unit, "cores": used, "kind": kind,
+            "sample": f"{sample}; {reps} runs"}
 
 
-def cpu_baseline(w, name, budget_s=12.0):
-    """Bounded CPU sample on rank 0: the compiled reference kernel when present
-    (kind 'reference'), else this repository's C restatement (kind 'port')."""
-    import concurrent.futures as cf
+class _OneRank:
+    """Stand-in for torch.distributed when there is a single rank."""
 
-    import numpy as np
+    @staticmethod
+    def get_world_size(group=None):
+        return 1
 
-    from oracle import pbo, ref
-    have_ref = ref.available()
-    cores = os.cpu_count() or 1
-    np_dt = np.float64 if w["dtype"] == "f64" else np.float32
-    metric, unit, scale = metric_of(name)
-    if name.startswith("mvt"):
-        n = 4096
-        A = pbo.fill(n, n, np_dt, SEED, 1, w["lo"], w["hi"])
-        v = [pbo.fill_vec(n, np_dt, SEED, 2 + k, w["lo"], w["hi"]) for k in range(4)]
-        t0 = time.perf_counter()
-        reps = 0
-        while reps < 3 or time.perf_counter() - t0 < 2.0:
-            if have_ref:
-                ref.kernel_mvt(n, v[0], v[1], v[2], v[3], A)
-            else:
-                pbo.mvt(v[0], v[1], v[2], v[3], A)
-            reps += 1
-        dt = (time.perf_counter() - t0) / reps
-        return {"value": (n * n * 8 + 6 * n * 8) / dt / scale, "unit": unit, "cores": 1,
-                "kind": "reference" if have_ref else "port",
-                "sample": f"kernel_mvt at N={n}, {reps} runs, sequential nests"}
-    if name == "chain2mm":
-        K, N = w["nk"], w["nj"]
-    else:
-        K, N = w["K"], w["N"]
-    rows_per = 16
-    B = pbo.fill(K, N, np_dt, SEED, 2, w["lo"], w["hi"])
-    As = [pbo.fill(rows_per, K, np_dt, SEED, 1, w["lo"], w["hi"], row0=t * rows_per) for t in range(cores)]
-    Cs = [pbo.fill(rows_per, N, np_dt, SEED, 3, w["lo"], w["hi"], row0=t * rows_per) for t in range(cores)]
-
-    def one(t):
-        if have_ref:
-            ref.kernel_gemm(rows_per, N, K, ALPHA, BETA, Cs[t], As[t], B)
-        else:
-            pbo.gemm(ALPHA, BETA, Cs[t], As[t], B)
-
-    with cf.ThreadPoolExecutor(max_workers=cores) as pool:
-        list(pool.map(one, range(cores)))  # warm-up
-        t0 = time.perf_counter()
-        reps = 0
-        while reps < 2 or time.perf_counter() - t0 < min(budget_s, 6.0):
-            list(pool.map(one, range(cores)))
-            reps += 1
-        dt = (time.perf_counter() - t0) / reps
-    return {"value": 2 * rows_per * cores * N * K / dt / scale, "unit": unit, "cores": cores,
-            "kind": "reference" if have_ref else "port",
-            "sample": f"kernel_gemm on {cores} independent {rows_per}-row slabs of the "
-                      f"{K}x{N} problem, {reps} runs"}
+    @staticmethod
+    def get_rank(group=None):
+        return 0
 
 
 # ----------------------------------------------------------------------------- pgb200 arm
@@ -342,6 +351,33 @@ def run_pgb200(args, w, name):
         def step():
             pgb.gemm(ALPHA, A, B, 0.0, tmp)
             pgb.gemm(1.0, tmp, Cc, BETA, D)
+    elif name.startswith("ssyrk"):
+        n, K = w["N"], w["K"]
+        sp = partition.PartitionedSyrk(
+            dist if world > 1 else _OneRank(), lambda al, Ar, be, Cb, rows: pgb.syrk_rows(
+                al, Ar, be, Cb, rows[0], rows[1]), src=0, chunk_rows=2048)
+        b = sp.blocks(n)
+        r0, r1 = b[rank], b[rank + 1]
+        A = filled(n, K, 1) if rank == 0 else torch.empty((n, K), dtype=tdt, device=dev)
+        Cm = filled(r1 - r0, n, 3, row0=r0)
+
+        def step():
+            sp.run(ALPHA, A, BETA, Cm)
+    elif w.get("strong"):
+        M, N, K = w["M"], w["N"], w["K"]
+        b = partition.row_blocks(M, world)
+        r0, r1 = b[rank], b[rank + 1]
+        A = filled(r1 - r0, K, 1, row0=r0)
+        Cm = filled(r1 - r0, N, 3, row0=r0)
+        B = filled(K, N, 2) if rank == 0 else torch.empty((K, N), dtype=tdt, device=dev)
+        if world > 1:
+            plan = partition.PartitionedGemm(dist, pgb.gemm, src=0, chunk=K // 8)
+
+            def step():
+                plan.run(ALPHA, A, B, BETA, Cm)
+        else:
+            def step():
+                pgb.gemm(ALPHA, A, B, BETA, Cm)
     else:
         M, N, K = w["M"], w["N"], w["K"]
         A = filled(M, K, 1, row0=rank * M)          # this rank's row block
@@ -387,7 +423,9 @@ def run_pgb200(args, w, name):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / args.steps
-    value = units * world / (ms_per_step * 1e-3) / scale
+    strong = bool(w.get("strong"))
+    total_units = units if strong else units * world
+    value = total_units / (ms_per_step * 1e-3) / scale
 
     # ---- dominant-kernel roofline (one kernel per step for the GEMMs) ----
     roof = None
@@ -414,7 +452,7 @@ def run_pgb200(args, w, name):
             # 3xTF32: every useful FMA costs three tensor-core FMAs, so the
             # tensor pipe does 3 * 2MNK flop per step; compare with dense TF32.
             peak = pgb.probe_peak(pgb.PEAK_TF32) / 1e3
-            ach = 3 * units / (ms_per_step * 1e-3) / 1e12
+            ach = 3 * (units / world if strong else units) / (ms_per_step * 1e-3) / 1e12
             roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                     "frac": ach / peak, "traffic": None,
                     "peak_source": "dense TF32 tcgen05.mma issue-rate probe measured in this run "
@@ -423,18 +461,20 @@ def run_pgb200(args, w, name):
 
     # ---- end to end through the reference-facing drop-in, host arrays ----
     e2e = None
-    if name in ("dgemm4096", "sgemm1024", "sgemm4096", "sgemm8192") and not args.kernel_only:
-        M, N, K = w["M"], w["N"], w["K"]
+    if name in ("dgemm4096", "sgemm1024", "sgemm4096", "sgemm8192", "sgemm32768") and not args.kernel_only:
+        M, N, K = A.shape[0], w["N"], w["K"]
         np_dt = np.float64 if w["dtype"] == "f64" else np.float32
 
         def pinned(t):
             h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
             h.copy_(t)
             return h.numpy()
-        hA, hB, hC = pinned(A), pinned(B if rank == 0 or world == 1 else B), pinned(Cm)
+        if world > 1:
+            dist.broadcast(B, src=0)  # every rank's host copy of the shared operand
+        hA, hB, hC = pinned(A), pinned(B), pinned(Cm)
         isz = np.dtype(np_dt).itemsize
         h2d, d2h = (M * K + K * N + M * N) * isz, M * N * isz
-        reps = max(3, min(args.steps, 10))
+        reps = max(3, min(args.steps, 10)) if name != "sgemm32768" else 1
         polybench.kernel_gemm(M, N, K, ALPHA, BETA, hC, hA, hB)
         barrier()
         t0 = time.perf_counter()
@@ -446,7 +486,7 @@ def run_pgb200(args, w, name):
             t = torch.tensor([dt], dtype=torch.float64, device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dt = float(t.item())
-        e2e = {"value": units * world / dt / scale, "unit": unit, "h2d_bytes_per_step": h2d,
+        e2e = {"value": total_units / dt / scale, "unit": unit, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h}
     elif name.startswith("mvt"):
         n = min(8192, w["N"])  # host-array drop-in on a bounded sample (0.5 GB): PCIe-bound
@@ -468,11 +508,12 @@ def run_pgb200(args, w, name):
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": w["dtype"],
+            "data": "synthetic",
             "config": {"workload": w["desc"],
-                       "l2": "operands (>= 384 MiB) exceed the 126 MB L2; no flush between steps",
+                       "l2": "operands exceed the 126 MB L2; no flush between steps",
                        "parallelism": ("single GPU" if world == 1 else
-                                       f"{world} row blocks of 4096 rows, B broadcast by NCCL each step")},
+                                       f"{world} row blocks, shared operand broadcast by NCCL each step")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roof,
             "cpu_baseline": cpu,
         }

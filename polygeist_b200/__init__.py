@@ -180,6 +180,20 @@ def syrk(alpha, A, beta, Cm, stream=None, rows=None):
     return Cm
 
 
+def syrk_rows(alpha, A, beta, C_block, r0, r1, stream=None):
+    """Rows [r0,r1) of the lower-triangular update when only that row block of C
+    is resident: `C_block` is the [r1-r0, N] slice, `A` holds rows [0,r1)."""
+    K = A.shape[1]
+    N = C_block.shape[1]
+    assert A.shape[0] >= r1 and C_block.shape[0] == r1 - r0 and not _is_f64(C_block)
+    ldc = _ld(C_block)
+    # The ABI takes the address of row 0 of C; only rows [r0,r1) are touched.
+    base = _ptr(C_block) - r0 * ldc * 4
+    s = _stream(stream) if stream is not None else current_stream_for(A, C_block)
+    check(load().pgb200SsyrkRows(s, N, K, r0, r1, alpha, _ptr(A), _ld(A), beta, base, ldc))
+    return C_block
+
+
 def gemv(trans, alpha, A, x, beta, y, stream=None):
     M, N = A.shape
     s = _stream(stream) if stream is not None else current_stream_for(A, x, y)

@@ -275,6 +275,72 @@ def test_ssyrk_row_block_equals_rows_of_full_update():
     assert elementwise_rel(C2.cpu().numpy()[il], C1.cpu().numpy()[il]) <= 1e-6
 
 
+def test_ssyrk_config4_full_size():
+    """configs[4]a: fp32 SYRK N=16384, K=8192, inputs uniform [0,1).  CPU oracle on
+    scattered rows; every lower-triangle entry against an fp64 evaluation on the
+    GPU; strict upper triangle untouched."""
+    n, k = 16384, 8192
+    A = dev_fill(n, k, torch.float32, 1, 0.0, 1.0)
+    Cm = dev_fill(n, n, torch.float32, 2, 0.0, 1.0)
+    C0 = Cm.clone()
+    pgb.syrk(1.5, A, 1.2, Cm)
+    sync_ok()
+    assert pgb.last_path() == pgb.PATH_TCGEN05
+    hA = pbo.fill(n, k, np.float32, SEED, 1, 0.0, 1.0)
+    for r in (0, 127, 128, 255, 256, 5000, 11111, n - 1):
+        hC = pbo.fill(1, n, np.float32, SEED, 2, 0.0, 1.0, row0=r)
+        truth = pbo.syrk_block(1.5, 1.2, hC, hA, r, acc64=True)[0, : r + 1]
+        seq = pbo.syrk_block(1.5, 1.2, hC.copy(), hA, r)[0, : r + 1]
+        got = Cm[r, : r + 1].cpu().numpy()
+        assert elementwise_rel(got, truth) <= 1e-5
+        assert elementwise_rel(got, seq) <= 1e-5
+    Ad = A.double()
+    worst = 0.0
+    for r0 in range(0, n, 2048):
+        t = 1.5 * (Ad[r0:r0 + 2048] @ Ad.T) + 1.2 * C0[r0:r0 + 2048].double()
+        g = Cm[r0:r0 + 2048].double()
+        rows = torch.arange(r0, r0 + 2048, device=DEV)[:, None]
+        cols = torch.arange(n, device=DEV)[None, :]
+        low = cols <= rows
+        worst = max(worst, float((((g - t).abs() / t.abs())[low]).max()))
+        assert torch.equal(Cm[r0:r0 + 2048][~low], C0[r0:r0 + 2048][~low])
+    assert worst <= 1e-5
+
+
+def test_sgemm_config4_full_size():
+    """configs[4]b: fp32 GEMM M=N=K=32768, inputs uniform [0,1).  K exceeds 8192, so
+    the gate is the fp64-accumulated evaluation of the same fp32 inputs (the
+    sequential fp32 nest is itself ~1e-5 from it at this K): CPU oracle on two
+    rows, GPU fp64 on 128 pseudo-random rows plus block-boundary rows, and a
+    Freivalds identity over the whole product."""
+    n = 32768
+    A = dev_fill(n, n, torch.float32, 1, 0.0, 1.0)
+    B = dev_fill(n, n, torch.float32, 2, 0.0, 1.0)
+    Cm = dev_fill(n, n, torch.float32, 3, 0.0, 1.0)
+    C0 = Cm.clone()
+    pgb.gemm(1.5, A, B, 1.2, Cm)
+    sync_ok()
+    assert pgb.last_path() == pgb.PATH_TCGEN05
+    rows = np.random.default_rng(SEED).choice(n, 128, replace=False)
+    rows = np.unique(np.concatenate([rows, [0, 127, 128, 4095, 4096, n // 2 - 1, n // 2, n - 1]]))
+    idx = torch.from_numpy(rows).to(DEV)
+    Bd = B.double()
+    truth = 1.5 * (A[idx].double() @ Bd) + 1.2 * C0[idx].double()
+    got = Cm[idx].double()
+    assert float(((got - truth).abs() / truth.abs()).max()) <= 1e-5
+    v = dev_fill(n, 1, torch.float64, 9, 0.0, 1.0)
+    lhs = Cm.double() @ v
+    rhs = 1.5 * (A.double() @ (Bd @ v)) + 1.2 * (C0.double() @ v)
+    assert float(((lhs - rhs).abs() / rhs.abs()).max()) <= 1e-5
+    del Bd, lhs, rhs, truth, got
+    hB = pbo.fill(n, n, np.float32, SEED, 2, 0.0, 1.0)
+    for r in (1, n - 2):
+        hA = pbo.fill(1, n, np.float32, SEED, 1, 0.0, 1.0, row0=r)
+        hC = pbo.fill(1, n, np.float32, SEED, 3, 0.0, 1.0, row0=r)
+        t = pbo.gemm_acc64(1.5, 1.2, hC, hA, hB)
+        assert elementwise_rel(Cm[r].cpu().numpy()[None, :], t) <= 1e-5
+
+
 # --------------------------------------------------------------------------- reference-style drop-ins (host arrays)
 @pytest.mark.parametrize("tname,dtype", [("f64", np.float64), ("f32", np.float32)])
 def test_kernel_gemm_dropin_reproduces_golden_dump(tname, dtype):

@@ -1,0 +1,109 @@
+"""CPU tests of the multi-GPU host logic: world-size-2 (and 3) `gloo` process
+groups run the same partition/broadcast plan that bench.py runs over NCCL,
+with numpy standing in for the GPU kernels."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from polygeist_b200 import partition
+
+
+def test_row_blocks_cover_and_align():
+    for M, P in [(4096, 8), (1000, 3), (128, 4), (5, 2)]:
+        b = partition.row_blocks(M, P, align=128)
+        assert b[0] == 0 and b[-1] == M and len(b) == P + 1
+        assert all(x <= y for x, y in zip(b, b[1:]))
+        assert all(x % 128 == 0 for x in b[1:-1])
+
+
+def test_syrk_blocks_balance_area():
+    N, P = 16384, 8
+    b = partition.syrk_row_blocks(N, P, align=128)
+    area = [(b[p + 1] * (b[p + 1] + 1) - b[p] * (b[p] + 1)) / 2 for p in range(P)]
+    assert b[0] == 0 and b[-1] == N
+    assert max(area) / min(area) < 1.16          # equal heights would give 15x
+    eq = partition.row_blocks(N, P, align=128)
+    area_eq = [(eq[p + 1] * (eq[p + 1] + 1) - eq[p] * (eq[p] + 1)) / 2 for p in range(P)]
+    assert max(area_eq) / min(area_eq) > 10
+
+
+def test_k_chunks():
+    assert partition.k_chunks(10, 4) == [(0, 4), (4, 8), (8, 10)]
+    assert partition.k_chunks(0, 4) == [(0, 0)]
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _np_gemm(alpha, A, B, beta, C):
+    C.copy_(torch.from_numpy(alpha * (A.numpy() @ B.numpy()) + beta * C.numpy()))
+
+
+def _np_syrk(alpha, A, beta, Cb, rows):
+    r0, r1 = rows
+    full = alpha * (A.numpy()[r0:r1] @ A.numpy().T) + beta * Cb.numpy()[:, :r1]
+    out = Cb.numpy()
+    for i in range(r1 - r0):
+        out[i, : r0 + i + 1] = full[i, : r0 + i + 1]
+
+
+def _worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(7)
+        M, N, K = 96, 40, 64
+        A = rng.uniform(-1, 1, (M, K))
+        B = rng.uniform(-1, 1, (K, N))
+        C = rng.uniform(-1, 1, (M, N))
+        ref = 1.5 * A @ B + 1.2 * C
+        b = partition.row_blocks(M, world, align=16)
+        r0, r1 = b[rank], b[rank + 1]
+        A_p = torch.from_numpy(A[r0:r1].copy())
+        C_p = torch.from_numpy(C[r0:r1].copy())
+        B_local = torch.from_numpy(B.copy()) if rank == 0 else torch.full((K, N), float("nan"), dtype=torch.float64)
+        plan = partition.PartitionedGemm(dist, _np_gemm, src=0, chunk=24)
+        plan.run(1.5, A_p, B_local, 1.2, C_p)
+        ok = np.allclose(C_p.numpy(), ref[r0:r1], rtol=1e-13, atol=1e-13)
+        ok = ok and np.array_equal(B_local.numpy(), B)       # every rank ends with all of B
+
+        Ns, Ks = 80, 24
+        As = rng.uniform(0, 1, (Ns, Ks))
+        Cs = rng.uniform(0, 1, (Ns, Ns))
+        refs = np.where(np.tril(np.ones((Ns, Ns), bool)), 1.5 * As @ As.T + 1.2 * Cs, Cs)
+        sp = partition.PartitionedSyrk(dist, _np_syrk, src=0, chunk_rows=32, align=8)
+        bs = sp.blocks(Ns)
+        s0, s1 = bs[rank], bs[rank + 1]
+        A_loc = torch.from_numpy(As.copy()) if rank == 0 else torch.full((Ns, Ks), float("nan"), dtype=torch.float64)
+        C_blk = torch.from_numpy(Cs[s0:s1].copy())
+        sp.run(1.5, A_loc, 1.2, C_blk)
+        ok = ok and np.allclose(C_blk.numpy(), refs[s0:s1], rtol=1e-13, atol=1e-13)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_partitioned_plans_over_gloo(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(res) == [(r, True) for r in range(world)]
