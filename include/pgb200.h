@@ -51,7 +51,8 @@ typedef struct pgb200Config {
                                  into fp32 registers; bounds the truncation
                                  bias of tensor-core accumulation             */
   int32_t force_generic;      /* 1: always take the plain SIMT kernels        */
-  int32_t reserved[5];
+  int32_t reserved[5];        /* [0] != 0: 3xTF32 path never reads an operand in
+                                 place (always writes both hi and lo planes)  */
 } pgb200Config;
 
 /* Runtime life cycle.  Replaces nothing in the reference one-to-one; plays the

@@ -95,8 +95,9 @@ def check(status):
         raise PGB200Error(status, load().pgb200GetLastErrorString().decode())
 
 
-def init(log_level=0, sgemm_chunk_kblocks=0, force_generic=0):
+def init(log_level=0, sgemm_chunk_kblocks=0, force_generic=0, sgemm_planes_only=0):
     cfg = Config(log_level, sgemm_chunk_kblocks, force_generic)
+    cfg.reserved[0] = sgemm_planes_only
     check(load().pgb200Init(C.byref(cfg)))
 
 

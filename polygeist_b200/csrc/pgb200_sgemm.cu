@@ -1,32 +1,34 @@
 // fp32 GEMM / SYRK on the 5th-generation tensor cores (tcgen05 + tensor memory)
 // with an error-compensated 3xTF32 split.
 //
-//   a = a_hi + a_lo,  a_hi = tf32(a),  a_lo = tf32(a - a_hi)     (same for b)
-//   a*b ~= a_lo*b_hi + a_hi*b_lo + a_hi*b_hi                      (a_lo*b_lo dropped)
+//   a = a_hi + a_lo,  a*b ~= a_lo*b_hi + a_hi*b_lo + a_hi*b_hi     (a_lo*b_lo dropped)
 //
-// Two launches per call:
-//   1. split kernels write the hi/lo planes of both operands to scratch memory,
-//      K-major ([rows][Kp] with Kp a multiple of 32, so every plane row is
-//      16-byte aligned whatever the caller's leading dimension was).  A row-major
-//      B[K][N] is transposed on the way, so the tensor cores only ever see the
-//      plain K-major / 64-byte-swizzle operand layout.
-//   2. a persistent, warp-specialised GEMM over the planes:
-//        warp 0    TMA producer: four 2-D tile loads per K-block into a 4-stage
-//                  shared-memory ring (mbarrier transaction counts);
-//        warp 1    one elected thread issues tcgen05.mma kind::tf32 (M=128,
-//                  N=256, K=8), six per K-block of 16, accumulating in tensor
-//                  memory; tcgen05.commit releases ring stages and publishes
-//                  accumulators;
-//        warps 2-9 drain warps: tcgen05.ld the 128x256 fp32 accumulator
-//                  (each thread one row x 128 columns), add it into fp32
-//                  registers, and at the end of a tile apply alpha/beta and store.
-//      Tensor memory holds two 256-column accumulators, so the tensor cores work
-//      on chunk c+1 (or the next tile) while chunk c is drained.
+// The tensor core reads an fp32 operand as TF32 by dropping the low 13 mantissa
+// bits, so an operand whose rows are 16-byte aligned is used IN PLACE as its own
+// hi part (a_hi = trunc_tf32(a), exact), and only a_lo = tf32(a - a_hi) is
+// written to scratch by a small element-wise pre-pass.  A row-major B[K][N] is
+// consumed as it lies (N-major operand, 128-byte swizzle with 32-byte atoms);
+// the rank-k update's B = A^T is K-major like A.  Operands that break a TMA
+// alignment rule get both planes written instead (B transposed on the way).
+//
+// The GEMM itself is one persistent, warp-specialised kernel (384 threads):
+//   warp 0     TMA producer: four tile loads per K-block of 16 into a 4-stage
+//              shared-memory ring (mbarrier transaction counts);
+//   warp 1     one elected thread issues tcgen05.mma kind::tf32 (M=128, N=256,
+//              K=8), six per K-block, accumulating in tensor memory;
+//              tcgen05.commit releases ring stages and publishes accumulators;
+//   warps 4-11 drain warps: tcgen05.ld the 128x256 fp32 accumulator (each thread
+//              one row x 128 columns), add it into fp32 registers, and at the end
+//              of a tile apply alpha/beta and store.
+// setmaxnreg moves registers from warps 0-3 (40 each) to the drain warps (232).
+// Tensor memory holds two 256-column accumulators, so the tensor cores work on
+// chunk c+1 (or the next tile) while chunk c is drained.
 //
 // Why chunks.  The tensor core adds each K=8 partial product into the fp32
-// accumulator with truncation, which biases long all-positive sums; draining
-// every `chunk_kblocks` K-blocks and adding the chunks in round-to-nearest fp32
-// registers bounds that bias independently of K.
+// accumulator with truncation, which biases long all-positive sums (measured:
+// -3.0e-4 relative at K=32768 in one accumulation).  Draining every
+// `chunk_kblocks` K-blocks and adding the chunks in round-to-nearest fp32
+// registers bounds that bias independently of K (about 3e-6 at the default 8).
 //
 // Every wait is time-bounded: on expiry the kernel records a code in the
 // host-visible status word, leaves its loops, frees its tensor memory and
@@ -44,10 +46,11 @@ constexpr int B_BYTES = BN * BK * 4;                      // 16 KiB per plane ti
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;    // 48 KiB
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
 constexpr int EPI_WARPS = 8;
-constexpr int THREADS = 32 * (2 + EPI_WARPS);
+constexpr int FIRST_EPI_WARP = 4;                         // warps 0-3: producer, MMA, 2 spare
+constexpr int THREADS = 32 * (FIRST_EPI_WARP + EPI_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_CYCLES = 4000000000ll;           // ~2 s
-constexpr int DEFAULT_CHUNK_KBLOCKS = 16;                 // 256 K-elements
+constexpr int DEFAULT_CHUNK_KBLOCKS = 8;                  // 128 K-elements
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -111,6 +114,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       "l"(map), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -162,10 +173,30 @@ __device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t saddr) {
   return d;
 }
 
-// kind::tf32 instruction descriptor: fp32 accumulator, tf32 A and B, both
-// K-major, N=256, M=128.
+// Descriptor of an N-major ("MN-major") B tile, i.e. a row-major B[K][N] used as
+// it lies: the tile is stored as 8 column blocks of 32 fp32 (one 128-byte
+// span), each block [BK k-rows][128 bytes].  For 32-bit operands the tensor
+// core takes N-major data only in the "128-byte swizzle with 32-byte atoms"
+// layout (descriptor layout type 1; TMA mode SWIZZLE_128B_ATOM_32B), whose atom
+// is 4 k-rows x 128 bytes.  Leading byte offset = distance between column
+// blocks (BK*128), stride byte offset = distance between groups of 4 k-rows
+// (512).  (Established with a one-tile probe: an identity-like A against
+// B = k and B = n reproduces B exactly for this combination only.)
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((BK * 128) >> 4) << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)1 << 61;
+  return d;
+}
+
+// kind::tf32 instruction descriptor: fp32 accumulator, tf32 A and B, A K-major,
+// B K-major (bit 16 clear) or N-major (bit 16 set), N=256, M=128.
 constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
                            ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t IDESC_BMN = IDESC | (1u << 16);
 
 struct Tiles {
   int64_t tiles_m, tiles_n, total;
@@ -211,13 +242,14 @@ struct TileCursor {
   }
 };
 
+template <bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
                    const __grid_constant__ CUtensorMap mapAlo,
                    const __grid_constant__ CUtensorMap mapBhi,
                    const __grid_constant__ CUtensorMap mapBlo, int64_t M, int64_t N, int64_t K,
                    float alpha, float beta, float *__restrict__ C, int64_t ldc, Tiles tiles,
-                   int chunk_kblocks, int32_t *status) {
+                   int chunk_kblocks, int bhi_blocked, int32_t *status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_slot;
@@ -249,9 +281,17 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
+  // Register re-partition between the warpgroups: the producer/MMA group keeps
+  // 40 registers per thread, the two drain groups (128 fp32 accumulators per
+  // thread plus tensor-memory load buffers) grow to 232.
   const int64_t nkb = (K + BK - 1) / BK;
   const int64_t nchunks = (nkb + chunk_kblocks - 1) / chunk_kblocks;
 
+  if (warp < FIRST_EPI_WARP) {
+  // Register re-partition between the warpgroups: the producer/MMA group gives
+  // registers back, the two drain groups (128 fp32 accumulators per thread plus
+  // tensor-memory load buffers) grow.
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -273,8 +313,23 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
           const int k0 = (int)(kb * BK);
           tma_load_2d(dst, &mapAhi, bar, k0, (int)(tm * BM));
           tma_load_2d(dst + A_BYTES, &mapAlo, bar, k0, (int)(tm * BM));
-          tma_load_2d(dst + 2 * A_BYTES, &mapBhi, bar, k0, (int)(tn * BN));
-          tma_load_2d(dst + 2 * A_BYTES + B_BYTES, &mapBlo, bar, k0, (int)(tn * BN));
+          if (B_MN) {
+            // Row-major B as it lies: eight [BK x 32] column blocks per plane,
+            // fetched by one 3-D copy (view (32, K, N/32)) when N allows it,
+            // else by eight 2-D copies (zero-filled past column N).
+            tma_load_3d(dst + 2 * A_BYTES + B_BYTES, &mapBlo, bar, 0, k0, (int)(tn * (BN / 32)));
+            if (bhi_blocked) {
+              tma_load_3d(dst + 2 * A_BYTES, &mapBhi, bar, 0, k0, (int)(tn * (BN / 32)));
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 32; j++)
+                tma_load_2d(dst + 2 * A_BYTES + j * (BK * 128), &mapBhi, bar,
+                            (int)(tn * BN) + 32 * j, k0);
+            }
+          } else {
+            tma_load_2d(dst + 2 * A_BYTES, &mapBhi, bar, k0, (int)(tn * BN));
+            tma_load_2d(dst + 2 * A_BYTES + B_BYTES, &mapBlo, bar, k0, (int)(tn * BN));
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -309,16 +364,21 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
             tc_fence_after();
             const uint32_t sa = ring + stage * STAGE_BYTES;
             const uint64_t ahi = smem_desc_sw64(sa), alo = smem_desc_sw64(sa + A_BYTES);
-            const uint64_t bhi = smem_desc_sw64(sa + 2 * A_BYTES);
-            const uint64_t blo = smem_desc_sw64(sa + 2 * A_BYTES + B_BYTES);
+            const uint64_t bhi = B_MN ? smem_desc_mn_sw128(sa + 2 * A_BYTES)
+                                      : smem_desc_sw64(sa + 2 * A_BYTES);
+            const uint64_t blo = B_MN ? smem_desc_mn_sw128(sa + 2 * A_BYTES + B_BYTES)
+                                      : smem_desc_sw64(sa + 2 * A_BYTES + B_BYTES);
+            constexpr uint32_t idesc = B_MN ? IDESC_BMN : IDESC;
             const bool first = (kb == ch * chunk_kblocks);
 #pragma unroll
             for (int ks = 0; ks < BK / 8; ks++) {
-              // +32 bytes per K=8 step inside the swizzled row (encoded >> 4).
+              // K=8 step: +32 bytes inside a K-major swizzled row; one group of
+              // 8 k-rows (+1024 bytes) in an N-major tile (both encoded >> 4).
               const uint64_t ko = (uint64_t)(ks * 2);
-              tc_mma_tf32(tmem_d, alo + ko, bhi + ko, IDESC, (first && ks == 0) ? 0u : 1u);
-              tc_mma_tf32(tmem_d, ahi + ko, blo + ko, IDESC, 1u);
-              tc_mma_tf32(tmem_d, ahi + ko, bhi + ko, IDESC, 1u);
+              const uint64_t kob = B_MN ? (uint64_t)(ks * 64) : ko;
+              tc_mma_tf32(tmem_d, alo + ko, bhi + kob, idesc, (first && ks == 0) ? 0u : 1u);
+              tc_mma_tf32(tmem_d, ahi + ko, blo + kob, idesc, 1u);
+              tc_mma_tf32(tmem_d, ahi + ko, bhi + kob, idesc, 1u);
             }
             tc_commit(empty0 + 8 * stage);  // stage reusable once these MMAs retire
             if (++stage == STAGES) {
@@ -330,9 +390,11 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
         }
       }
     }
+  }
   } else {
     // ------------------------------------------------------------- drain warps
-    const int ew = warp - 2;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int ew = warp - FIRST_EPI_WARP;
     const int quarter = warp & 3;      // tensor-memory lane quarter this warp may read
     const int half = ew >> 2;          // which 128 columns of the 256
     TileCursor cur;
@@ -344,6 +406,17 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
       float acc[128];
 #pragma unroll
       for (int i = 0; i < 128; i++) acc[i] = 0.0f;
+      if (beta != 0.0f) {
+        // Pull this thread's part of the C tile towards L2 while the tensor
+        // cores work, so the epilogue's loads do not wait on HBM.
+        const int64_t pr = tm * BM + quarter * 32 + lane, pc = tn * BN + half * 128;
+        if (pr < M) {
+#pragma unroll
+          for (int q = 0; q < 4; q++)
+            if (pc + q * 32 < N)
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(C + pr * ldc + pc + q * 32));
+        }
+      }
       for (int64_t ch = 0; ch < nchunks && ok; ch++, cc++) {
         const uint32_t buf = (uint32_t)(cc & 1);
         const uint32_t use = (uint32_t)((cc >> 1) & 1);
@@ -371,7 +444,10 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
         if (lane == 0) mbar_arrive(acce0 + 8 * buf);
       }
       if (!ok) break;
-      // alpha/beta epilogue: this thread owns row r, columns [cb, cb+128).
+
+      // alpha/beta epilogue: this thread owns row r, columns [cb, cb+128), as 32
+      // independent 16-byte accesses (the loads are hoisted ahead of the stores,
+      // so their latencies overlap).
       const int64_t r = tm * BM + quarter * 32 + lane;
       const int64_t cb = tn * BN + half * 128;
       if (r < M && cb < N) {
@@ -379,32 +455,41 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
         if (tiles.lower && r + tiles.row0 < lim) lim = r + tiles.row0;
         float *crow = C + r * ldc;
         const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        if (vec_ok && cb + 127 <= lim) {
 #pragma unroll
-        for (int j = 0; j < 128; j += 4) {
-          const int64_t c = cb + j;
-          if (c > lim) break;
-          if (vec_ok && c + 3 <= lim) {
-            float4 o;
-            o.x = alpha * acc[j];
-            o.y = alpha * acc[j + 1];
-            o.z = alpha * acc[j + 2];
-            o.w = alpha * acc[j + 3];
+          for (int h = 0; h < 2; h++) {
+            float4 old[16];
             if (beta != 0.0f) {
-              const float4 old = *reinterpret_cast<const float4 *>(crow + c);
-              o.x = fmaf(beta, old.x, o.x);
-              o.y = fmaf(beta, old.y, o.y);
-              o.z = fmaf(beta, old.z, o.z);
-              o.w = fmaf(beta, old.w, o.w);
-            }
-            *reinterpret_cast<float4 *>(crow + c) = o;
-          } else {
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-              if (c + e <= lim) {
-                float o = alpha * acc[j + e];
-                if (beta != 0.0f) o = fmaf(beta, crow[c + e], o);
-                crow[c + e] = o;
+              for (int q = 0; q < 16; q++)
+                old[q] = __ldcs(reinterpret_cast<const float4 *>(crow + cb + h * 64 + q * 4));
+            }
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+              const int j = h * 64 + q * 4;
+              float4 o;
+              o.x = alpha * acc[j];
+              o.y = alpha * acc[j + 1];
+              o.z = alpha * acc[j + 2];
+              o.w = alpha * acc[j + 3];
+              if (beta != 0.0f) {
+                o.x = fmaf(beta, old[q].x, o.x);
+                o.y = fmaf(beta, old[q].y, o.y);
+                o.z = fmaf(beta, old[q].z, o.z);
+                o.w = fmaf(beta, old[q].w, o.w);
               }
+              *reinterpret_cast<float4 *>(crow + cb + j) = o;
+            }
+          }
+        } else {
+          // Ragged edge, diagonal tile or unaligned C: element by element.
+#pragma unroll 4
+          for (int j = 0; j < 128; j++) {
+            const int64_t c = cb + j;
+            if (c <= lim) {
+              float o = alpha * acc[j];
+              if (beta != 0.0f) o = fmaf(beta, crow[c], o);
+              crow[c] = o;
             }
           }
         }
@@ -447,6 +532,38 @@ __global__ void split_rows_kernel(const float *__restrict__ src, int64_t ld, int
   }
 }
 
+// The tensor core reads an fp32 operand as TF32 by dropping the low 13 mantissa
+// bits, so an aligned operand can serve as its own "hi" plane: only
+// lo = tf32(a - trunc_tf32(a)) has to be written.  src[rows][cols] (ld) ->
+// lo[rows][colsP]; columns cols..colsP-1 are zero-filled.  Needs ld % 4 == 0
+// and a 16-byte aligned src (the condition for using src as the hi plane).
+__global__ void split_lo_kernel(const float *__restrict__ src, int64_t ld, int64_t rows,
+                                int64_t cols, int64_t colsP, float *__restrict__ lo) {
+  const int64_t q = colsP / 4;  // float4 groups per row
+  const int64_t total = rows * q;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / q, c = (i - r * q) * 4;
+    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (c + 3 < cols) {
+      const float4 x = *reinterpret_cast<const float4 *>(src + r * ld + c);
+      v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    } else {
+      for (int e = 0; e < 4; e++)
+        if (c + e < cols) v[e] = src[r * ld + c + e];
+    }
+    float o[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const float hi = __uint_as_float(__float_as_uint(v[e]) & 0xFFFFE000u);
+      uint32_t l;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(v[e] - hi));
+      o[e] = __uint_as_float(l);
+    }
+    *reinterpret_cast<float4 *>(lo + r * colsP + c) = make_float4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // src[K][N] (ld) -> hi/lo[N][Kp] (transposed through a 32x33 shared tile).
 __global__ void split_transpose_kernel(const float *__restrict__ src, int64_t ld, int64_t K,
                                        int64_t N, int64_t Kp, float *__restrict__ hi,
@@ -473,13 +590,35 @@ __global__ void split_transpose_kernel(const float *__restrict__ src, int64_t ld
   }
 }
 
-int32_t make_plane_map(CUtensorMap *map, const float *base, int64_t rows, int64_t K, int64_t Kp,
+// K-major operand [rows][K] with row pitch `ld`: box = BK x box_rows, 64-byte swizzle.
+int32_t make_plane_map(CUtensorMap *map, const float *base, int64_t rows, int64_t K, int64_t ld,
                        int box_rows) {
   const uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows};
-  const uint64_t str[1] = {(uint64_t)Kp * 4};
+  const uint64_t str[1] = {(uint64_t)ld * 4};
   const uint32_t box[2] = {BK, (uint32_t)box_rows};
   return encode_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, str, box,
                            CU_TENSOR_MAP_SWIZZLE_64B);
+}
+
+// N-major operand B[K][N] with row pitch `ld`: box = 32 columns x BK rows,
+// 128-byte swizzle with 32-byte atoms.
+int32_t make_nmajor_map(CUtensorMap *map, const float *base, int64_t K, int64_t N, int64_t ld) {
+  const uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+  const uint64_t str[1] = {(uint64_t)ld * 4};
+  const uint32_t box[2] = {32, BK};
+  return encode_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, str, box,
+                           CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+}
+
+// The same operand seen as (32, K, N/32) so that one copy fetches all eight
+// column blocks of a tile; needs N % 32 == 0 (every block inside the row).
+int32_t make_nmajor_map_blocked(CUtensorMap *map, const float *base, int64_t K, int64_t N,
+                                int64_t ld) {
+  const uint64_t dims[3] = {32, (uint64_t)K, (uint64_t)(N / 32)};
+  const uint64_t str[2] = {(uint64_t)ld * 4, 128};
+  const uint32_t box[3] = {32, BK, BN / 32};
+  return encode_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, str, box,
+                           CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
 }
 
 
@@ -564,44 +703,93 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   if (K == 0) return PGB200_ERR_UNSUPPORTED;  // nothing to contract: SIMT path scales C
   if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31))
     return PGB200_ERR_UNSUPPORTED;
-  const int64_t Kp = (K + 31) / 32 * 32;
-  // For the rank-k update both operands are rows of the same matrix: when B
-  // starts at A's row 0 (or is A itself) one pair of planes serves both.
-  const bool shared_planes = transB && (ldb == lda) && (B <= A) &&
-                             ((A - B) % lda == 0) && ((A - B) / lda + M <= N);
+  const int64_t Kp = (K + 31) / 32 * 32, Np = (N + 31) / 32 * 32;
+  const bool planes_only = rt->cfg.reserved[0] != 0;  // debugging aid: never use operands in place
+  // An operand whose rows are 16-byte aligned is used in place as its own "hi"
+  // plane (the tensor core truncates fp32 to TF32); only its "lo" plane is
+  // written.  Otherwise both planes are written (and B is transposed).
+  const bool a_raw = !planes_only && aligned16(A) && (lda % 4) == 0;
+  const bool b_raw = !planes_only && aligned16(B) && (ldb % 4) == 0;
+  // For the rank-k update both operands are rows of one matrix: when A's rows
+  // are a sub-range of B's rows the A planes are views into the B planes.
+  const bool shared_planes = transB && (ldb == lda) && (B <= A) && ((A - B) % lda == 0) &&
+                             ((A - B) / lda + M <= N);
   const int64_t a_off_rows = shared_planes ? (A - B) / lda : 0;
-  const size_t plane_a = (size_t)M * Kp, plane_b = (size_t)N * Kp;
-  const size_t floats = shared_planes ? 2 * plane_b : 2 * plane_a + 2 * plane_b;
+  const bool b_mn = !transB && b_raw;
+
+  // Scratch layout (floats): [B lo][B hi?][A lo?][A hi?]
+  const size_t b_lo_n = b_mn ? (size_t)K * Np : (size_t)N * Kp;
+  const size_t b_hi_n = b_raw ? 0 : (size_t)N * Kp;
+  const size_t a_lo_n = shared_planes ? 0 : (size_t)M * Kp;
+  const size_t a_hi_n = (shared_planes || a_raw) ? 0 : (size_t)M * Kp;
   void *ws = nullptr;
-  PGB_TRY(get_workspace(s, floats * sizeof(float), &ws));
-  float *Bhi = static_cast<float *>(ws), *Blo = Bhi + plane_b;
-  float *Ahi = shared_planes ? Bhi + a_off_rows * Kp : Blo + plane_b;
-  float *Alo = shared_planes ? Blo + a_off_rows * Kp : Ahi + plane_a;
+  PGB_TRY(get_workspace(s, (b_lo_n + b_hi_n + a_lo_n + a_hi_n) * sizeof(float), &ws));
+  float *Blo = static_cast<float *>(ws);
+  float *Bhi_pl = Blo + b_lo_n;
+  float *Alo_pl = Bhi_pl + b_hi_n;
+  float *Ahi_pl = Alo_pl + a_lo_n;
 
   const int64_t cap = (int64_t)rt->num_sms * 8;
   auto grid_for = [&](int64_t total) {
     int64_t g = (total + 255) / 256;
     return (unsigned)(g < 1 ? 1 : (g > cap ? cap : g));
   };
-  if (transB) {
-    split_rows_kernel<<<grid_for(N * Kp), 256, 0, s>>>(B, ldb, N, K, Kp, Bhi, Blo);
+  // ---- B ----
+  const float *Bhi = nullptr;
+  int64_t bhi_ld = Kp;
+  if (b_mn) {
+    split_lo_kernel<<<grid_for(K * (Np / 4)), 256, 0, s>>>(B, ldb, K, N, Np, Blo);
+    Bhi = B;
+    bhi_ld = ldb;
+  } else if (transB && b_raw) {
+    split_lo_kernel<<<grid_for(N * (Kp / 4)), 256, 0, s>>>(B, ldb, N, K, Kp, Blo);
+    Bhi = B;
+    bhi_ld = ldb;
+  } else if (transB) {
+    split_rows_kernel<<<grid_for(N * Kp), 256, 0, s>>>(B, ldb, N, K, Kp, Bhi_pl, Blo);
+    Bhi = Bhi_pl;
   } else {
     const int64_t tk = Kp / 32, tn = (N + 31) / 32;
     PGB_REQUIRE(tk * tn < (int64_t(1) << 31), "tf32x3_gemm: operand too large");
-    split_transpose_kernel<<<(unsigned)(tk * tn), 256, 0, s>>>(B, ldb, K, N, Kp, Bhi, Blo, tk);
+    split_transpose_kernel<<<(unsigned)(tk * tn), 256, 0, s>>>(B, ldb, K, N, Kp, Bhi_pl, Blo, tk);
+    Bhi = Bhi_pl;
   }
   note_launch(PATH_TCGEN05);
-  if (!shared_planes) {
-    split_rows_kernel<<<grid_for(M * Kp), 256, 0, s>>>(A, lda, M, K, Kp, Ahi, Alo);
+  // ---- A ----
+  const float *Ahi = nullptr, *Alo = nullptr;
+  int64_t ahi_ld = Kp;
+  if (shared_planes) {
+    Alo = Blo + a_off_rows * Kp;
+    Ahi = Bhi + a_off_rows * bhi_ld;
+    ahi_ld = bhi_ld;
+  } else if (a_raw) {
+    split_lo_kernel<<<grid_for(M * (Kp / 4)), 256, 0, s>>>(A, lda, M, K, Kp, Alo_pl);
     note_launch(PATH_TCGEN05);
+    Alo = Alo_pl;
+    Ahi = A;
+    ahi_ld = lda;
+  } else {
+    split_rows_kernel<<<grid_for(M * Kp), 256, 0, s>>>(A, lda, M, K, Kp, Ahi_pl, Alo_pl);
+    note_launch(PATH_TCGEN05);
+    Alo = Alo_pl;
+    Ahi = Ahi_pl;
   }
   PGB_CUDA(cudaGetLastError());
 
   CUtensorMap mAhi, mAlo, mBhi, mBlo;
-  PGB_TRY(make_plane_map(&mAhi, Ahi, M, K, Kp, BM));
+  PGB_TRY(make_plane_map(&mAhi, Ahi, M, K, ahi_ld, BM));
   PGB_TRY(make_plane_map(&mAlo, Alo, M, K, Kp, BM));
-  PGB_TRY(make_plane_map(&mBhi, Bhi, N, K, Kp, BN));
-  PGB_TRY(make_plane_map(&mBlo, Blo, N, K, Kp, BN));
+  const bool bhi_blocked = b_mn && (N % 32) == 0;
+  if (b_mn) {
+    if (bhi_blocked)
+      PGB_TRY(make_nmajor_map_blocked(&mBhi, Bhi, K, N, bhi_ld));
+    else
+      PGB_TRY(make_nmajor_map(&mBhi, Bhi, K, N, bhi_ld));
+    PGB_TRY(make_nmajor_map_blocked(&mBlo, Blo, K, Np, Np));
+  } else {
+    PGB_TRY(make_plane_map(&mBhi, Bhi, N, K, bhi_ld, BN));
+    PGB_TRY(make_plane_map(&mBlo, Blo, N, K, Kp, BN));
+  }
 
   Tiles tiles;
   tiles.tiles_m = (M + BM - 1) / BM;
@@ -620,10 +808,18 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   }
   int chunk = rt->cfg.sgemm_chunk_kblocks > 0 ? rt->cfg.sgemm_chunk_kblocks : DEFAULT_CHUNK_KBLOCKS;
   const unsigned grid = (unsigned)(tiles.total < rt->num_sms ? tiles.total : rt->num_sms);
-  PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                SMEM_BYTES));
-  tf32x3_gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(mAhi, mAlo, mBhi, mBlo, M, N, K, alpha, beta,
-                                                        C, ldc, tiles, chunk, rt->status_dev);
+  if (b_mn) {
+    PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_kernel<true>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    tf32x3_gemm_kernel<true><<<grid, THREADS, SMEM_BYTES, s>>>(
+        mAhi, mAlo, mBhi, mBlo, M, N, K, alpha, beta, C, ldc, tiles, chunk, bhi_blocked ? 1 : 0,
+        rt->status_dev);
+  } else {
+    PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_kernel<false>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    tf32x3_gemm_kernel<false><<<grid, THREADS, SMEM_BYTES, s>>>(
+        mAhi, mAlo, mBhi, mBlo, M, N, K, alpha, beta, C, ldc, tiles, chunk, 0, rt->status_dev);
+  }
   note_launch(PATH_TCGEN05);
   PGB_CUDA(cudaGetLastError());
   return PGB200_OK;
