@@ -31,6 +31,10 @@ sys.path.insert(0, ROOT)
 SEED = 20261125
 ALPHA, BETA = 1.5, 1.2
 
+# DRAM bytes (read + write) per launch of the dominant kernel from the ncu
+# captures summarised under profiles/ (mvt32768: the N=16384 capture x 4).
+TRAFFIC = {"dgemm4096": 1.1345e9, "mvt16384": 2.156e9, "mvt32768": 8.624e9, "sgemm4096": 7.64e8}
+
 WORKLOADS = {
     # name: (metric, unit, dtype, description)
     "dgemm4096": dict(dtype="f64", M=4096, N=4096, K=4096, lo=-1.0, hi=1.0,
@@ -321,9 +325,28 @@ def run_pgb200(args, w, name):
         raise SystemExit("bench.py: no CUDA device; libpgb200 has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    strong_mg = world > 1 and bool(w.get("strong"))
     if world > 1:
+        # The broadcast of the next operand chunk runs beside the GEMM of the
+        # current one: keep NCCL to a few CTAs and leave it as many SMs.
         dist.init_process_group("nccl", device_id=dev)
-    pgb.init()
+    pgb.init(reserve_sms=int(os.environ.get("PGB_BENCH_RESERVE_SMS", "0")) if strong_mg else 0)
+
+    def shared_operand(rows, cols, aid):
+        """The broadcast operand: a plain tensor for the NCCL broadcast (default:
+        fastest at 8 GPUs), or symmetric (peer-mapped) memory for the optional
+        copy-engine broadcast (PGB_BENCH_BCAST=p2p; faster at 2 GPUs)."""
+        mode = os.environ.get("PGB_BENCH_BCAST", "nccl")
+        if world > 1 and mode == "p2p":
+            import torch.distributed._symmetric_memory as symm_mem
+            t = symm_mem.empty((rows, cols), dtype=tdt, device=dev)
+            hdl = symm_mem.rendezvous(t, dist.group.WORLD)
+            if rank == 0:
+                pgb.fill_uniform(t, SEED, aid, w["lo"], w["hi"])
+            views = {r: hdl.get_buffer(r, (rows, cols), tdt) for r in range(world)}
+            return t, partition.PeerPullBroadcast(torch, dist, views, src=0)
+        t = filled(rows, cols, aid) if rank == 0 else torch.empty((rows, cols), dtype=tdt, device=dev)
+        return t, None
     tdt = torch.float64 if w["dtype"] == "f64" else torch.float32
     metric, unit, scale = metric_of(name)
     units = algorithmic_work(name, w)
@@ -369,9 +392,10 @@ def run_pgb200(args, w, name):
         r0, r1 = b[rank], b[rank + 1]
         A = filled(r1 - r0, K, 1, row0=r0)
         Cm = filled(r1 - r0, N, 3, row0=r0)
-        B = filled(K, N, 2) if rank == 0 else torch.empty((K, N), dtype=tdt, device=dev)
+        B, pb = shared_operand(K, N, 2)
         if world > 1:
-            plan = partition.PartitionedGemm(dist, pgb.gemm, src=0, chunk=K // 8)
+            plan = partition.PartitionedGemm(dist, pgb.gemm, src=0, peer_broadcast=pb,
+                                             chunk=int(os.environ.get("PGB_BENCH_KCHUNK", K // 8)))
 
             def step():
                 plan.run(ALPHA, A, B, BETA, Cm)
@@ -382,9 +406,12 @@ def run_pgb200(args, w, name):
         M, N, K = w["M"], w["N"], w["K"]
         A = filled(M, K, 1, row0=rank * M)          # this rank's row block
         Cm = filled(M, N, 3, row0=rank * M)
-        B = filled(K, N, 2) if rank == 0 else torch.empty((K, N), dtype=tdt, device=dev)
+        B, pb = shared_operand(K, N, 2)
         if world > 1:
-            plan = partition.PartitionedGemm(dist, pgb.gemm, src=0, chunk=max(256, K // 4))
+            # B is small here (128 MiB against 4 ms of compute): one chunk, the
+            # broadcast simply precedes the product.
+            plan = partition.PartitionedGemm(dist, pgb.gemm, src=0, peer_broadcast=pb,
+                                             chunk=int(os.environ.get("PGB_BENCH_KCHUNK", K)))
 
             def step():
                 plan.run(ALPHA, A, B, BETA, Cm)
@@ -397,6 +424,12 @@ def run_pgb200(args, w, name):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # Roofline denominators not in MEASURED_PEAKS.json are probed twice: here
+    # (GPU idle: burst clocks) and right after the timed region (the power/clock
+    # state the timed kernels actually ran in).
+    peak_cold = None
+    if rank == 0 and not name.startswith("mvt"):
+        peak_cold = pgb.probe_peak(pgb.PEAK_DMMA if w["dtype"] == "f64" else pgb.PEAK_TF32) / 1e3
     for _ in range(args.warmup):
         step()
     barrier()
@@ -440,24 +473,35 @@ def run_pgb200(args, w, name):
             src = "of measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "of fallback"
             ach = units / (ms_per_step * 1e-3) / 1e9
             roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
-                    "frac": ach / peak, "traffic": None, "peak_source": src}
+                    "frac": ach / peak, "traffic": TRAFFIC.get(name), "peak_source": src}
         elif w["dtype"] == "f64":
-            peak = pgb.probe_peak(pgb.PEAK_DMMA) / 1e3
+            peak_hot = pgb.probe_peak(pgb.PEAK_DMMA) / 1e3
+            peak = max(peak_cold, peak_hot)
             ach = units / (ms_per_step * 1e-3) / 1e12
             roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                    "frac": ach / peak, "traffic": None,
-                    "peak_source": "fp64 tensor (mma.sync .f64) issue-rate probe measured in this "
-                                   "run; MEASURED_PEAKS.json has no fp64 figure"}
+                    "frac": ach / peak, "traffic": TRAFFIC.get(name),
+                    "peak_burst": peak_cold, "peak_after_run": peak_hot,
+                    "peak_source": "fp64 tensor (mma.sync .f64) issue-rate probe of this library, "
+                                   "max of before/after the timed region (MEASURED_PEAKS.json has "
+                                   "no fp64 figure)"}
         else:
             # 3xTF32: every useful FMA costs three tensor-core FMAs, so the
             # tensor pipe does 3 * 2MNK flop per step; compare with dense TF32.
-            peak = pgb.probe_peak(pgb.PEAK_TF32) / 1e3
+            peak_hot = pgb.probe_peak(pgb.PEAK_TF32) / 1e3
+            # A step that runs for seconds settles at the power-capped clock:
+            # judge it against the probe taken in that state; short steps
+            # against the burst figure.
+            long_run = ms_per_step * args.steps > 1000.0
+            peak = peak_hot if long_run else max(peak_cold, peak_hot)
             ach = 3 * (units / world if strong else units) / (ms_per_step * 1e-3) / 1e12
             roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                    "frac": ach / peak, "traffic": None,
-                    "peak_source": "dense TF32 tcgen05.mma issue-rate probe measured in this run "
-                                   "(MEASURED_PEAKS.json has no TF32 figure); achieved counts the "
-                                   "3 tensor products per useful product (useful = achieved/3)"}
+                    "frac": ach / peak, "traffic": TRAFFIC.get(name),
+                    "peak_burst": peak_cold, "peak_after_run": peak_hot,
+                    "peak_source": "dense TF32 tcgen05.mma issue-rate probe of this library "
+                                   "(MEASURED_PEAKS.json has no TF32 figure): "
+                                   + ("sustained (after the timed region)" if long_run else
+                                      "burst (max of before/after)")
+                                   + "; achieved counts the 3 tensor products per useful product"}
 
     # ---- end to end through the reference-facing drop-in, host arrays ----
     e2e = None

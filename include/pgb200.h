@@ -51,8 +51,12 @@ typedef struct pgb200Config {
                                  into fp32 registers; bounds the truncation
                                  bias of tensor-core accumulation             */
   int32_t force_generic;      /* 1: always take the plain SIMT kernels        */
-  int32_t reserved[5];        /* [0] != 0: 3xTF32 path never reads an operand in
+  int32_t sgemm_planes_only;  /* 1: the 3xTF32 path never reads an operand in
                                  place (always writes both hi and lo planes)  */
+  int32_t reserve_sms;        /* SMs the persistent GEMM kernels leave free, so
+                                 that a concurrent collective (NCCL broadcast
+                                 of the next operand chunk) can run beside them */
+  int32_t reserved[3];
 } pgb200Config;
 
 /* Runtime life cycle.  Replaces nothing in the reference one-to-one; plays the

@@ -33,7 +33,8 @@ class PGB200Error(RuntimeError):
 
 class Config(C.Structure):
     _fields_ = [("log_level", C.c_int32), ("sgemm_chunk_kblocks", C.c_int32),
-                ("force_generic", C.c_int32), ("reserved", C.c_int32 * 5)]
+                ("force_generic", C.c_int32), ("sgemm_planes_only", C.c_int32),
+                ("reserve_sms", C.c_int32), ("reserved", C.c_int32 * 3)]
 
 
 _i32, _i64, _vp, _f64, _f32 = C.c_int32, C.c_int64, C.c_void_p, C.c_double, C.c_float
@@ -95,9 +96,8 @@ def check(status):
         raise PGB200Error(status, load().pgb200GetLastErrorString().decode())
 
 
-def init(log_level=0, sgemm_chunk_kblocks=0, force_generic=0, sgemm_planes_only=0):
-    cfg = Config(log_level, sgemm_chunk_kblocks, force_generic)
-    cfg.reserved[0] = sgemm_planes_only
+def init(log_level=0, sgemm_chunk_kblocks=0, force_generic=0, sgemm_planes_only=0, reserve_sms=0):
+    cfg = Config(log_level, sgemm_chunk_kblocks, force_generic, sgemm_planes_only, reserve_sms)
     check(load().pgb200Init(C.byref(cfg)))
 
 

@@ -313,7 +313,9 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
   } else {
     tiles.total = tiles.tiles_m * tiles.tiles_n;
   }
-  const unsigned grid = (unsigned)(tiles.total < rt->num_sms ? tiles.total : rt->num_sms);
+  int64_t ctas = rt->num_sms - (rt->cfg.reserve_sms > 0 ? rt->cfg.reserve_sms : 0);
+  if (ctas < 1) ctas = 1;
+  const unsigned grid = (unsigned)(tiles.total < ctas ? tiles.total : ctas);
   if (transB) {
     PGB_CUDA(cudaFuncSetAttribute(dmma_gemm_kernel<true>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));

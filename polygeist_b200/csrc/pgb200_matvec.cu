@@ -134,6 +134,35 @@ __global__ void matvec_reduce_kernel(double *__restrict__ y, const double *__res
   y[i] = v;
 }
 
+// Both results of the fused pair in one launch: blocks [0,blocks1) reduce the
+// row-dot partials into y1, the rest reduce the column-sum partials into y2.
+__global__ void matvec_reduce_pair_kernel(double *__restrict__ y1, const double *__restrict__ p1,
+                                          int64_t parts1, int64_t len1, int blocks1,
+                                          double *__restrict__ y2, const double *__restrict__ p2,
+                                          int64_t parts2, int64_t len2, double alpha,
+                                          double beta) {
+  const bool first = (int)blockIdx.x < blocks1;
+  double *y = first ? y1 : y2;
+  const double *part = first ? p1 : p2;
+  const int64_t nparts = first ? parts1 : parts2, len = first ? len1 : len2;
+  const int64_t i = (first ? blockIdx.x : blockIdx.x - blocks1) * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= len) return;
+  double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+  int64_t p = 0;
+  // Four independent partial sums keep four loads in flight; they are combined
+  // in a fixed order, so the result is still deterministic.
+  for (; p + 3 < nparts; p += 4) {
+    s0 += part[p * len + i];
+    s1 += part[(p + 1) * len + i];
+    s2 += part[(p + 2) * len + i];
+    s3 += part[(p + 3) * len + i];
+  }
+  for (; p < nparts; p++) s0 += part[p * len + i];
+  double v = alpha * ((s0 + s1) + (s2 + s3));
+  if (beta != 0.0) v = fma(beta, y[i], v);
+  y[i] = v;
+}
+
 __global__ void vec_scale_kernel(double *y, int64_t len, double beta) {
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (i < len) y[i] = (beta == 0.0) ? 0.0 : beta * y[i];
@@ -179,6 +208,14 @@ int32_t stream_matvec(cudaStream_t s, int64_t M, int64_t N, const double *A, int
                                                              y2 ? x2 : nullptr, p1, p2, tiles_r,
                                                              tiles_c);
   note_launch(PATH_STREAM);
+  if (y1 && y2) {
+    const int b1 = (int)((M + 255) / 256), b2 = (int)((N + 255) / 256);
+    matvec_reduce_pair_kernel<<<(unsigned)(b1 + b2), 256, 0, s>>>(y1, p1, tiles_c, M, b1, y2, p2,
+                                                                  tiles_r, N, alpha, beta);
+    note_launch(PATH_STREAM);
+    PGB_CUDA(cudaGetLastError());
+    return PGB200_OK;
+  }
   if (y1) {
     matvec_reduce_kernel<<<(unsigned)((M + 255) / 256), 256, 0, s>>>(y1, p1, tiles_c, M, alpha,
                                                                      beta);

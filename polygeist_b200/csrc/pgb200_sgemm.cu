@@ -704,7 +704,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31))
     return PGB200_ERR_UNSUPPORTED;
   const int64_t Kp = (K + 31) / 32 * 32, Np = (N + 31) / 32 * 32;
-  const bool planes_only = rt->cfg.reserved[0] != 0;  // debugging aid: never use operands in place
+  const bool planes_only = rt->cfg.sgemm_planes_only != 0;  // never use operands in place
   // An operand whose rows are 16-byte aligned is used in place as its own "hi"
   // plane (the tensor core truncates fp32 to TF32); only its "lo" plane is
   // written.  Otherwise both planes are written (and B is transposed).
@@ -807,7 +807,9 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     tiles.total = tiles.tiles_m * tiles.tiles_n;
   }
   int chunk = rt->cfg.sgemm_chunk_kblocks > 0 ? rt->cfg.sgemm_chunk_kblocks : DEFAULT_CHUNK_KBLOCKS;
-  const unsigned grid = (unsigned)(tiles.total < rt->num_sms ? tiles.total : rt->num_sms);
+  int64_t ctas = rt->num_sms - (rt->cfg.reserve_sms > 0 ? rt->cfg.reserve_sms : 0);
+  if (ctas < 1) ctas = 1;
+  const unsigned grid = (unsigned)(tiles.total < ctas ? tiles.total : ctas);
   if (b_mn) {
     PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_kernel<true>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));

@@ -45,6 +45,66 @@ def k_chunks(K, chunk):
     return [(k0, min(K, k0 + chunk)) for k0 in range(0, K, chunk)] or [(0, 0)]
 
 
+def pull_plan(rank, world, src, k0, k1):
+    """Copy-engine broadcast of rows [k0,k1) from `src`, as pulls by `rank`.
+
+    Returns (phase1, phase2): lists of (peer, r0, r1) meaning "copy rows
+    [r0,r1) from `peer`'s buffer into mine".  The rows are split into world-1
+    pieces, one per non-source rank.  Phase 1: every non-source rank pulls its
+    own piece from `src` (so `src` sends each row once).  Phase 2 (after all
+    ranks finished phase 1): it pulls every other piece from the rank that
+    owns it, so the remaining traffic is spread over all links.
+    """
+    others = [r for r in range(world) if r != src]
+    if rank == src or not others:
+        return [], []
+    n = len(others)
+    rows = k1 - k0
+    bounds = [k0 + (rows * j) // n for j in range(n + 1)]
+    piece = {r: (bounds[j], bounds[j + 1]) for j, r in enumerate(others)}
+    p1 = [(src,) + piece[rank]] if piece[rank][1] > piece[rank][0] else []
+    p2 = [(q,) + piece[q] for q in others if q != rank and piece[q][1] > piece[q][0]]
+    return p1, p2
+
+
+class PeerPullBroadcast:
+    """Broadcast of the shared operand by peer-to-peer copies (DMA engines, no
+    SMs), so the transfer does not compete with the persistent GEMM kernels the
+    way a collective kernel does.  `views[r]` is rank r's buffer mapped into
+    this process (torch symmetric memory); copies run on a private stream and
+    one event per K-chunk tells the compute stream when its rows have landed.
+    A one-element all-reduce on the same stream is the device-side barrier
+    between the two phases of pull_plan()."""
+
+    def __init__(self, torch, dist, views, src=0, group=None):
+        self.torch, self.dist, self.views, self.src, self.group = torch, dist, views, src, group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.stream = torch.cuda.Stream()
+        self.flag = torch.zeros(1, device=views[self.rank].device)
+
+    def start(self, chunks):
+        torch, dist = self.torch, self.dist
+        mine = self.views[self.rank]
+        self.stream.wait_stream(torch.cuda.current_stream())
+        events = []
+        with torch.cuda.stream(self.stream):
+            # Nobody overwrites its buffer while a peer may still be reading it.
+            dist.all_reduce(self.flag, group=self.group)
+            for k0, k1 in chunks:
+                p1, p2 = pull_plan(self.rank, self.world, self.src, k0, k1)
+                for peer, r0, r1 in p1:
+                    mine[r0:r1].copy_(self.views[peer][r0:r1], non_blocking=True)
+                if self.world > 2:
+                    dist.all_reduce(self.flag, group=self.group)
+                for peer, r0, r1 in p2:
+                    mine[r0:r1].copy_(self.views[peer][r0:r1], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.stream)
+                events.append(ev)
+        return events
+
+
 class PartitionedGemm:
     """C_p = alpha * A_p @ B + beta * C_p on every rank, B broadcast from `src`.
 
@@ -53,12 +113,13 @@ class PartitionedGemm:
     polygeist_b200.gemm, which enqueues on the current CUDA stream).
     """
 
-    def __init__(self, dist, compute, src=0, chunk=1024, group=None):
+    def __init__(self, dist, compute, src=0, chunk=1024, group=None, peer_broadcast=None):
         self.dist = dist
         self.compute = compute
         self.src = src
         self.chunk = chunk
         self.group = group
+        self.peer_broadcast = peer_broadcast  # PeerPullBroadcast, or None for NCCL
 
     def run(self, alpha, A_p, B_local, beta, C_p):
         """`B_local`: the full [K,N] buffer on every rank; only `src`'s copy
@@ -68,6 +129,15 @@ class PartitionedGemm:
         chunks = k_chunks(K, self.chunk)
         world = dist.get_world_size(self.group)
         works = []
+        if world > 1 and self.peer_broadcast is not None:
+            pb = self.peer_broadcast
+            events = pb.start(chunks)
+            first = True
+            for (k0, k1), ev in zip(chunks, events):
+                pb.torch.cuda.current_stream().wait_event(ev)
+                self.compute(alpha, A_p[:, k0:k1], B_local[k0:k1], beta if first else 1.0, C_p)
+                first = False
+            return C_p
         if world > 1:
             for k0, k1 in chunks:
                 if k1 > k0:

@@ -37,6 +37,25 @@ def test_k_chunks():
     assert partition.k_chunks(0, 4) == [(0, 0)]
 
 
+def test_pull_plan_covers_every_row_once():
+    for world, src in [(2, 0), (3, 1), (8, 0)]:
+        k0, k1 = 100, 100 + 37 * world
+        for rank in range(world):
+            p1, p2 = partition.pull_plan(rank, world, src, k0, k1)
+            if rank == src:
+                assert p1 == [] and p2 == []
+                continue
+            got = sorted((r0, r1) for _, r0, r1 in p1 + p2)
+            assert got[0][0] == k0 and got[-1][1] == k1
+            assert all(a[1] == b[0] for a, b in zip(got, got[1:]))       # contiguous, no overlap
+            assert all(peer == src for peer, _, _ in p1)                  # own piece straight from the source
+            assert all(peer not in (src, rank) for peer, _, _ in p2)      # the rest from its owners
+        # the source sends each row exactly once in phase 1
+        sent = sorted((r0, r1) for rank in range(world) if rank != src
+                      for _, r0, r1 in partition.pull_plan(rank, world, src, k0, k1)[0])
+        assert sent[0][0] == k0 and sent[-1][1] == k1 and all(a[1] == b[0] for a, b in zip(sent, sent[1:]))
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
