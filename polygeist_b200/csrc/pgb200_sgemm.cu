@@ -19,7 +19,9 @@
 //              tcgen05.commit releases ring stages and publishes accumulators;
 //   warps 4-11 drain warps: tcgen05.ld the 128x256 fp32 accumulator (each thread
 //              one row x 128 columns), add it into fp32 registers, and at the end
-//              of a tile apply alpha/beta and store.
+//              of a tile apply alpha/beta and store through a padded shared
+//              32x32 transpose, so every access to C is a full 128-byte row
+//              segment.
 // setmaxnreg moves registers from warps 0-3 (40 each) to the drain warps (232).
 // Tensor memory holds two 256-column accumulators, so the tensor cores work on
 // chunk c+1 (or the next tile) while chunk c is drained.
@@ -28,7 +30,8 @@
 // accumulator with truncation, which biases long all-positive sums (measured:
 // -3.0e-4 relative at K=32768 in one accumulation).  Draining every
 // `chunk_kblocks` K-blocks and adding the chunks in round-to-nearest fp32
-// registers bounds that bias independently of K (about 3e-6 at the default 8).
+// registers bounds that bias independently of K (about 2e-6 at the default 4;
+// the drain overlaps the next chunk, so short chunks cost nothing measurable).
 //
 // Every wait is time-bounded: on expiry the kernel records a code in the
 // host-visible status word, leaves its loops, frees its tensor memory and
@@ -50,7 +53,7 @@ constexpr int FIRST_EPI_WARP = 4;                         // warps 0-3: producer
 constexpr int THREADS = 32 * (FIRST_EPI_WARP + EPI_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_CYCLES = 4000000000ll;           // ~2 s
-constexpr int DEFAULT_CHUNK_KBLOCKS = 8;                  // 128 K-elements
+constexpr int DEFAULT_CHUNK_KBLOCKS = 4;                  // 64 K-elements
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -212,16 +215,19 @@ __device__ __forceinline__ int64_t row_tiles(const Tiles &t, int64_t tm) {
   return c < t.tiles_n ? c : t.tiles_n;
 }
 
-// Walks the valid tiles in row-major order; each role keeps its own cursor and
-// advances it monotonically (tile indices only grow within a CTA).
+// Maps a linear tile index to (tile row, tile column).  Tiles are walked in
+// bands of 16 tile-rows, column by column inside a band, so the ~148 tiles in
+// flight form a 16 x 9 patch that shares 16 A panels and 9 B panels through L2
+// instead of streaming every B panel in every wave.  For the triangular update
+// only tiles that intersect j <= i exist; the band walk is the same, with each
+// column holding only the rows that reach it.  Each role keeps its own cursor;
+// tile indices only grow within a CTA, so the band position advances
+// monotonically.
 struct TileCursor {
-  int64_t tm = 0, before = 0;  // tiles in rows < tm
+  static constexpr int64_t G = 16;
+  int64_t band = 0, before = 0;  // tiles in bands < band (lower only)
   __device__ __forceinline__ void seek(const Tiles &t, int64_t idx, int64_t *otm, int64_t *otn) {
     if (!t.lower) {
-      // Full product: walk groups of 16 tile-rows column by column, so the
-      // ~148 tiles in flight form a 16 x 9 patch that shares 16 A panels and
-      // 9 B panels through L2 instead of streaming every B panel per wave.
-      constexpr int64_t G = 16;
       const int64_t per_group = G * t.tiles_n;
       const int64_t grp = idx / per_group;
       const int64_t first = grp * G;
@@ -231,14 +237,32 @@ struct TileCursor {
       *otn = in / rows;
       return;
     }
+    int64_t first, last;
     for (;;) {
-      const int64_t c = row_tiles(t, tm);
-      if (idx < before + c) break;
-      before += c;
-      tm++;
+      first = band * G;
+      last = (first + G < t.tiles_m ? first + G : t.tiles_m) - 1;
+      int64_t cnt = 0;
+      for (int64_t r = first; r <= last; r++) cnt += row_tiles(t, r);
+      if (idx < before + cnt) break;
+      before += cnt;
+      band++;
     }
-    *otm = tm;
-    *otn = idx - before;
+    int64_t in = idx - before;
+    for (int64_t tn = 0;; tn++) {
+      // Smallest tile row whose last matrix row reaches column tile tn.
+      int64_t need = tn * BN - t.row0 - (BM - 1);
+      int64_t lo = need <= 0 ? 0 : (need + BM - 1) / BM;
+      if (lo < first) lo = first;
+      const int64_t c = last - lo + 1;
+      if (c > 0) {
+        if (in < c) {
+          *otm = lo + in;
+          *otn = tn;
+          return;
+        }
+        in -= c;
+      }
+    }
   }
 };
 
@@ -253,6 +277,7 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_slot;
+  __shared__ float epi_stage[EPI_WARPS][32][33];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
   const uint32_t accf0 = smem_u32(&bars[2 * STAGES]), acce0 = smem_u32(&bars[2 * STAGES + 2]);
@@ -429,15 +454,12 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
         const uint32_t taddr =
             tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + (uint32_t)(half * 128);
 #pragma unroll
-        for (int j = 0; j < 4; j += 2) {
-          uint32_t v0[32], v1[32];
-          tc_ld32(taddr + j * 32, v0);
-          tc_ld32(taddr + j * 32 + 32, v1);
+        for (int j = 0; j < 4; j++) {
+          uint32_t v[32];
+          tc_ld32(taddr + j * 32, v);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; i++) acc[j * 32 + i] += __uint_as_float(v0[i]);
-#pragma unroll
-          for (int i = 0; i < 32; i++) acc[j * 32 + 32 + i] += __uint_as_float(v1[i]);
+          for (int i = 0; i < 32; i++) acc[j * 32 + i] += __uint_as_float(v[i]);
         }
         tc_fence_before();
         __syncwarp();
@@ -445,51 +467,53 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
       }
       if (!ok) break;
 
-      // alpha/beta epilogue: this thread owns row r, columns [cb, cb+128), as 32
-      // independent 16-byte accesses (the loads are hoisted ahead of the stores,
-      // so their latencies overlap).
-      const int64_t r = tm * BM + quarter * 32 + lane;
+      // alpha/beta epilogue.  A thread holds one row x 128 columns of the tile;
+      // accessing C that way would touch 32 different rows per instruction.
+      // Each warp instead turns 32x32 blocks through a padded shared tile, so
+      // that a load/store instruction covers one full 128-byte row segment.
+      // The 32 loads of a block are all issued before their first use.
+      const int64_t r_base = tm * BM + quarter * 32;
       const int64_t cb = tn * BN + half * 128;
-      if (r < M && cb < N) {
-        int64_t lim = N - 1;
-        if (tiles.lower && r + tiles.row0 < lim) lim = r + tiles.row0;
-        float *crow = C + r * ldc;
-        const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
-        if (vec_ok && cb + 127 <= lim) {
+      float(*st)[33] = epi_stage[ew];
+#pragma unroll
+      for (int cc = 0; cc < 4; cc++) {
+        if (cb + cc * 32 >= N) break;
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 32; i++) st[lane][i] = alpha * acc[cc * 32 + i];
+        __syncwarp();
+        const int64_t c = cb + cc * 32 + lane;
+        float *cptr = C + r_base * ldc + c;
+        const int64_t c_last = cb + cc * 32 + 31;
+        const bool interior = (r_base + 31 < M) && (c_last < N) &&
+                              (!tiles.lower || c_last <= r_base + tiles.row0);
+        if (interior) {
+          // Whole 32x32 block inside the matrix (and below the diagonal): no
+          // per-element predicates, 16 loads in flight.
 #pragma unroll
           for (int h = 0; h < 2; h++) {
-            float4 old[16];
+            float old[16];
             if (beta != 0.0f) {
 #pragma unroll
-              for (int q = 0; q < 16; q++)
-                old[q] = __ldcs(reinterpret_cast<const float4 *>(crow + cb + h * 64 + q * 4));
+              for (int q = 0; q < 16; q++) old[q] = __ldcs(cptr + (h * 16 + q) * ldc);
+            } else {
+#pragma unroll
+              for (int q = 0; q < 16; q++) old[q] = 0.0f;
             }
 #pragma unroll
-            for (int q = 0; q < 16; q++) {
-              const int j = h * 64 + q * 4;
-              float4 o;
-              o.x = alpha * acc[j];
-              o.y = alpha * acc[j + 1];
-              o.z = alpha * acc[j + 2];
-              o.w = alpha * acc[j + 3];
-              if (beta != 0.0f) {
-                o.x = fmaf(beta, old[q].x, o.x);
-                o.y = fmaf(beta, old[q].y, o.y);
-                o.z = fmaf(beta, old[q].z, o.z);
-                o.w = fmaf(beta, old[q].w, o.w);
-              }
-              *reinterpret_cast<float4 *>(crow + cb + j) = o;
-            }
+            for (int q = 0; q < 16; q++)
+              cptr[(h * 16 + q) * ldc] = fmaf(beta, old[q], st[h * 16 + q][lane]);
           }
         } else {
-          // Ragged edge, diagonal tile or unaligned C: element by element.
+          // Ragged edge or diagonal block: element by element.
+          const bool col_ok = c < N;
 #pragma unroll 4
-          for (int j = 0; j < 128; j++) {
-            const int64_t c = cb + j;
-            if (c <= lim) {
-              float o = alpha * acc[j];
-              if (beta != 0.0f) o = fmaf(beta, crow[c], o);
-              crow[c] = o;
+          for (int rr = 0; rr < 32; rr++) {
+            const int64_t r = r_base + rr;
+            if (col_ok && r < M && (!tiles.lower || c <= r + tiles.row0)) {
+              float o = st[rr][lane];
+              if (beta != 0.0f) o = fmaf(beta, cptr[rr * ldc], o);
+              cptr[rr * ldc] = o;
             }
           }
         }
