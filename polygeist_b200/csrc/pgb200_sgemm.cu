@@ -23,8 +23,10 @@
 //              32x32 transpose, so every access to C is a full 128-byte row
 //              segment.
 // setmaxnreg moves registers from warps 0-3 (40 each) to the drain warps (232).
-// Tensor memory holds two 256-column accumulators, so the tensor cores work on
-// chunk c+1 (or the next tile) while chunk c is drained.
+// Tensor memory holds two accumulators, so the tensor cores work on chunk c+1
+// (or the next tile) while chunk c is drained.  Problems with too few 128x256
+// tiles to occupy the GPU run the same kernel with 128x64 tiles (N=64 MMAs,
+// eight ring stages).
 //
 // Why chunks.  The tensor core adds each K=8 partial product into the fp32
 // accumulator with truncation, which biases long all-positive sums (measured:
@@ -205,13 +207,14 @@ struct Tiles {
   int64_t tiles_m, tiles_n, total;
   int64_t row0;  // absolute row of local row 0 (lower only)
   int lower;
+  int bn;        // tile width in columns (256, or 64 for problems with few tiles)
 };
 
 // Columns tiles of tile-row tm that intersect j <= i (lower) or all of them.
 __device__ __forceinline__ int64_t row_tiles(const Tiles &t, int64_t tm) {
   if (!t.lower) return t.tiles_n;
   const int64_t last_col = t.row0 + tm * BM + BM - 1;  // largest j of the tile row
-  const int64_t c = last_col / BN + 1;
+  const int64_t c = last_col / t.bn + 1;
   return c < t.tiles_n ? c : t.tiles_n;
 }
 
@@ -250,7 +253,7 @@ struct TileCursor {
     int64_t in = idx - before;
     for (int64_t tn = 0;; tn++) {
       // Smallest tile row whose last matrix row reaches column tile tn.
-      int64_t need = tn * BN - t.row0 - (BM - 1);
+      int64_t need = tn * t.bn - t.row0 - (BM - 1);
       int64_t lo = need <= 0 ? 0 : (need + BM - 1) / BM;
       if (lo < first) lo = first;
       const int64_t c = last - lo + 1;
@@ -266,7 +269,7 @@ struct TileCursor {
   }
 };
 
-template <bool B_MN>
+template <bool B_MN, int TBN>
 __global__ void __launch_bounds__(THREADS, 1)
 tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
                    const __grid_constant__ CUtensorMap mapAlo,
@@ -274,6 +277,15 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
                    const __grid_constant__ CUtensorMap mapBlo, int64_t M, int64_t N, int64_t K,
                    float alpha, float beta, float *__restrict__ C, int64_t ldc, Tiles tiles,
                    int chunk_kblocks, int bhi_blocked, int32_t *status) {
+  // Tile-width dependent constants (these shadow the 256-wide defaults above).
+  constexpr int BN = TBN;
+  constexpr int B_BYTES = BN * BK * 4;
+  constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  constexpr int STAGES = (192 * 1024) / STAGE_BYTES;  // 4 (BN=256) or 8 (BN=64)
+  constexpr int COLS = BN / 2;                         // columns per drain thread
+  constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
+  constexpr uint32_t IDESC_BMN = IDESC | (1u << 16);
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_slot;
@@ -421,23 +433,23 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
     asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
     const int ew = warp - FIRST_EPI_WARP;
     const int quarter = warp & 3;      // tensor-memory lane quarter this warp may read
-    const int half = ew >> 2;          // which 128 columns of the 256
+    const int half = ew >> 2;          // which half of the tile's columns
     TileCursor cur;
     int64_t cc = 0;
     bool ok = true;
     for (int64_t t = blockIdx.x; t < tiles.total && ok; t += gridDim.x) {
       int64_t tm, tn;
       cur.seek(tiles, t, &tm, &tn);
-      float acc[128];
+      float acc[COLS];
 #pragma unroll
-      for (int i = 0; i < 128; i++) acc[i] = 0.0f;
+      for (int i = 0; i < COLS; i++) acc[i] = 0.0f;
       if (beta != 0.0f) {
         // Pull this thread's part of the C tile towards L2 while the tensor
         // cores work, so the epilogue's loads do not wait on HBM.
-        const int64_t pr = tm * BM + quarter * 32 + lane, pc = tn * BN + half * 128;
+        const int64_t pr = tm * BM + quarter * 32 + lane, pc = tn * BN + half * COLS;
         if (pr < M) {
 #pragma unroll
-          for (int q = 0; q < 4; q++)
+          for (int q = 0; q < COLS / 32; q++)
             if (pc + q * 32 < N)
               asm volatile("prefetch.global.L2 [%0];" ::"l"(C + pr * ldc + pc + q * 32));
         }
@@ -452,9 +464,9 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
         }
         tc_fence_after();
         const uint32_t taddr =
-            tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + (uint32_t)(half * 128);
+            tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + (uint32_t)(half * COLS);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
+        for (int j = 0; j < COLS / 32; j++) {
           uint32_t v[32];
           tc_ld32(taddr + j * 32, v);
           tc_wait_ld();
@@ -473,10 +485,10 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
       // that a load/store instruction covers one full 128-byte row segment.
       // The 32 loads of a block are all issued before their first use.
       const int64_t r_base = tm * BM + quarter * 32;
-      const int64_t cb = tn * BN + half * 128;
+      const int64_t cb = tn * BN + half * COLS;
       float(*st)[33] = epi_stage[ew];
 #pragma unroll
-      for (int cc = 0; cc < 4; cc++) {
+      for (int cc = 0; cc < COLS / 32; cc++) {
         if (cb + cc * 32 >= N) break;
         __syncwarp();
 #pragma unroll
@@ -561,12 +573,13 @@ __global__ void split_rows_kernel(const float *__restrict__ src, int64_t ld, int
 // lo = tf32(a - trunc_tf32(a)) has to be written.  src[rows][cols] (ld) ->
 // lo[rows][colsP]; columns cols..colsP-1 are zero-filled.  Needs ld % 4 == 0
 // and a 16-byte aligned src (the condition for using src as the hi plane).
-__global__ void split_lo_kernel(const float *__restrict__ src, int64_t ld, int64_t rows,
-                                int64_t cols, int64_t colsP, float *__restrict__ lo) {
+__device__ __forceinline__ void split_lo_range(const float *__restrict__ src, int64_t ld,
+                                               int64_t rows, int64_t cols, int64_t colsP,
+                                               float *__restrict__ lo, int64_t first,
+                                               int64_t stride) {
   const int64_t q = colsP / 4;  // float4 groups per row
   const int64_t total = rows * q;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
+  for (int64_t i = first; i < total; i += stride) {
     const int64_t r = i / q, c = (i - r * q) * 4;
     float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (c + 3 < cols) {
@@ -586,6 +599,27 @@ __global__ void split_lo_kernel(const float *__restrict__ src, int64_t ld, int64
     }
     *reinterpret_cast<float4 *>(lo + r * colsP + c) = make_float4(o[0], o[1], o[2], o[3]);
   }
+}
+
+__global__ void split_lo_kernel(const float *__restrict__ src, int64_t ld, int64_t rows,
+                                int64_t cols, int64_t colsP, float *__restrict__ lo) {
+  split_lo_range(src, ld, rows, cols, colsP, lo, blockIdx.x * (int64_t)blockDim.x + threadIdx.x,
+                 (int64_t)gridDim.x * blockDim.x);
+}
+
+// Both operands in one launch: blocks [0,blocks0) take the first, the rest the second.
+__global__ void split_lo_pair_kernel(const float *__restrict__ src0, int64_t ld0, int64_t rows0,
+                                     int64_t cols0, int64_t colsP0, float *__restrict__ lo0,
+                                     int blocks0, const float *__restrict__ src1, int64_t ld1,
+                                     int64_t rows1, int64_t cols1, int64_t colsP1,
+                                     float *__restrict__ lo1) {
+  if ((int)blockIdx.x < blocks0)
+    split_lo_range(src0, ld0, rows0, cols0, colsP0, lo0,
+                   blockIdx.x * (int64_t)blockDim.x + threadIdx.x, (int64_t)blocks0 * blockDim.x);
+  else
+    split_lo_range(src1, ld1, rows1, cols1, colsP1, lo1,
+                   (blockIdx.x - blocks0) * (int64_t)blockDim.x + threadIdx.x,
+                   (int64_t)(gridDim.x - blocks0) * blockDim.x);
 }
 
 // src[K][N] (ld) -> hi/lo[N][Kp] (transposed through a 32x33 shared tile).
@@ -637,10 +671,10 @@ int32_t make_nmajor_map(CUtensorMap *map, const float *base, int64_t K, int64_t 
 // The same operand seen as (32, K, N/32) so that one copy fetches all eight
 // column blocks of a tile; needs N % 32 == 0 (every block inside the row).
 int32_t make_nmajor_map_blocked(CUtensorMap *map, const float *base, int64_t K, int64_t N,
-                                int64_t ld) {
+                                int64_t ld, int bn) {
   const uint64_t dims[3] = {32, (uint64_t)K, (uint64_t)(N / 32)};
   const uint64_t str[2] = {(uint64_t)ld * 4, 128};
-  const uint32_t box[3] = {32, BK, BN / 32};
+  const uint32_t box[3] = {32, BK, (uint32_t)(bn / 32)};
   return encode_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, str, box,
                            CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
 }
@@ -761,7 +795,16 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   // ---- B ----
   const float *Bhi = nullptr;
   int64_t bhi_ld = Kp;
-  if (b_mn) {
+  // Both operands usable in place: their lo planes come from one launch.
+  const bool pair = b_raw && a_raw && !shared_planes;
+  if (pair) {
+    const int64_t b_rows = b_mn ? K : N, b_cols = b_mn ? N : K, b_colsP = b_mn ? Np : Kp;
+    const unsigned g0 = grid_for(b_rows * (b_colsP / 4)), g1 = grid_for(M * (Kp / 4));
+    split_lo_pair_kernel<<<g0 + g1, 256, 0, s>>>(B, ldb, b_rows, b_cols, b_colsP, Blo, (int)g0, A,
+                                                  lda, M, K, Kp, Alo_pl);
+    Bhi = B;
+    bhi_ld = ldb;
+  } else if (b_mn) {
     split_lo_kernel<<<grid_for(K * (Np / 4)), 256, 0, s>>>(B, ldb, K, N, Np, Blo);
     Bhi = B;
     bhi_ld = ldb;
@@ -787,8 +830,10 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     Ahi = Bhi + a_off_rows * bhi_ld;
     ahi_ld = bhi_ld;
   } else if (a_raw) {
-    split_lo_kernel<<<grid_for(M * (Kp / 4)), 256, 0, s>>>(A, lda, M, K, Kp, Alo_pl);
-    note_launch(PATH_TCGEN05);
+    if (!pair) {
+      split_lo_kernel<<<grid_for(M * (Kp / 4)), 256, 0, s>>>(A, lda, M, K, Kp, Alo_pl);
+      note_launch(PATH_TCGEN05);
+    }
     Alo = Alo_pl;
     Ahi = A;
     ahi_ld = lda;
@@ -803,27 +848,32 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   CUtensorMap mAhi, mAlo, mBhi, mBlo;
   PGB_TRY(make_plane_map(&mAhi, Ahi, M, K, ahi_ld, BM));
   PGB_TRY(make_plane_map(&mAlo, Alo, M, K, Kp, BM));
+  // Tile width: 256 columns normally; 64 when 256-wide tiles would leave more
+  // than half of the SMs without a tile.
+  const int64_t tiles256 = ((M + BM - 1) / BM) * ((N + 255) / 256);
+  const int bn = (tiles256 * 2 <= rt->num_sms) ? 64 : 256;
   const bool bhi_blocked = b_mn && (N % 32) == 0;
   if (b_mn) {
     if (bhi_blocked)
-      PGB_TRY(make_nmajor_map_blocked(&mBhi, Bhi, K, N, bhi_ld));
+      PGB_TRY(make_nmajor_map_blocked(&mBhi, Bhi, K, N, bhi_ld, bn));
     else
       PGB_TRY(make_nmajor_map(&mBhi, Bhi, K, N, bhi_ld));
-    PGB_TRY(make_nmajor_map_blocked(&mBlo, Blo, K, Np, Np));
+    PGB_TRY(make_nmajor_map_blocked(&mBlo, Blo, K, Np, Np, bn));
   } else {
-    PGB_TRY(make_plane_map(&mBhi, Bhi, N, K, bhi_ld, BN));
-    PGB_TRY(make_plane_map(&mBlo, Blo, N, K, Kp, BN));
+    PGB_TRY(make_plane_map(&mBhi, Bhi, N, K, bhi_ld, bn));
+    PGB_TRY(make_plane_map(&mBlo, Blo, N, K, Kp, bn));
   }
 
   Tiles tiles;
   tiles.tiles_m = (M + BM - 1) / BM;
-  tiles.tiles_n = (N + BN - 1) / BN;
+  tiles.tiles_n = (N + bn - 1) / bn;
+  tiles.bn = bn;
   tiles.row0 = row0;
   tiles.lower = lower ? 1 : 0;
   if (lower) {
     int64_t total = 0;
     for (int64_t tm = 0; tm < tiles.tiles_m; tm++) {
-      const int64_t c = (row0 + tm * BM + BM - 1) / BN + 1;
+      const int64_t c = (row0 + tm * BM + BM - 1) / bn + 1;
       total += c < tiles.tiles_n ? c : tiles.tiles_n;
     }
     tiles.total = total;
@@ -834,18 +884,16 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   int64_t ctas = rt->num_sms - (rt->cfg.reserve_sms > 0 ? rt->cfg.reserve_sms : 0);
   if (ctas < 1) ctas = 1;
   const unsigned grid = (unsigned)(tiles.total < ctas ? tiles.total : ctas);
-  if (b_mn) {
-    PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_kernel<true>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    tf32x3_gemm_kernel<true><<<grid, THREADS, SMEM_BYTES, s>>>(
-        mAhi, mAlo, mBhi, mBlo, M, N, K, alpha, beta, C, ldc, tiles, chunk, bhi_blocked ? 1 : 0,
-        rt->status_dev);
-  } else {
-    PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_kernel<false>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    tf32x3_gemm_kernel<false><<<grid, THREADS, SMEM_BYTES, s>>>(
-        mAhi, mAlo, mBhi, mBlo, M, N, K, alpha, beta, C, ldc, tiles, chunk, 0, rt->status_dev);
-  }
+  auto launch = [&](auto kernel, int bhi_blk) -> int32_t {
+    PGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    kernel<<<grid, THREADS, SMEM_BYTES, s>>>(mAhi, mAlo, mBhi, mBlo, M, N, K, alpha, beta, C, ldc,
+                                             tiles, chunk, bhi_blk, rt->status_dev);
+    return PGB200_OK;
+  };
+  if (b_mn && bn == 256) PGB_TRY(launch(tf32x3_gemm_kernel<true, 256>, bhi_blocked ? 1 : 0));
+  if (b_mn && bn == 64) PGB_TRY(launch(tf32x3_gemm_kernel<true, 64>, bhi_blocked ? 1 : 0));
+  if (!b_mn && bn == 256) PGB_TRY(launch(tf32x3_gemm_kernel<false, 256>, 0));
+  if (!b_mn && bn == 64) PGB_TRY(launch(tf32x3_gemm_kernel<false, 64>, 0));
   note_launch(PATH_TCGEN05);
   PGB_CUDA(cudaGetLastError());
   return PGB200_OK;
