@@ -113,6 +113,15 @@ int32_t pgb200Dgemv(void *stream, int32_t transA, int64_t M, int64_t N,
                     double alpha, const double *A, int64_t lda, const double *x,
                     double beta, double *y);
 
+/* y1[M] = alpha * A * x1 + beta * y1 and y2[N] = alpha * A^T * x2 + beta * y2
+ * with A[MxN] read ONCE for both results (beta == 0 never reads y1 / y2).
+ * Replaces the scop of kernel_bicg,
+ * tools/cgeist/Test/polybench/linear-algebra/kernels/bicg/bicg.c:97-108
+ * (s = A^T r and q = A p accumulated in the same i-j nest). */
+int32_t pgb200DgemvPair(void *stream, int64_t M, int64_t N, double alpha,
+                        const double *A, int64_t lda, const double *x1,
+                        const double *x2, double beta, double *y1, double *y2);
+
 /* x1 += A * y1 and x2 += A^T * y2 with A[NxN] read ONCE for both results.
  * Replaces the whole scop of kernel_mvt, mvt.c:102-109. */
 int32_t pgb200Dmvt(void *stream, int64_t N, const double *A, int64_t lda,
@@ -212,6 +221,23 @@ int32_t pgb200_kernel_syrk(int n, int m, double alpha, double beta, double *C,
                            const double *A);
 int32_t pgb200_kernel_syrk_f32(int n, int m, float alpha, float beta, float *C,
                                const float *A);
+/* Same-shaped nests served by the same kernels:
+ *   pgb200_kernel_3mm      <- kernel_3mm      kernels/3mm/3mm.c:87-127   (three GEMMs;
+ *                             E and F are live-out like G)
+ *   pgb200_kernel_atax     <- kernel_atax     kernels/atax/atax.c:80-102 (tmp = A x, then
+ *                             y = A^T tmp: two passes, the second depends on the first)
+ *   pgb200_kernel_bicg     <- kernel_bicg     kernels/bicg/bicg.c:86-111 (one fused pass)
+ *   pgb200_kernel_gesummv  <- kernel_gesummv  blas/gesummv/gesummv.c:86-112 */
+int32_t pgb200_kernel_3mm(int ni, int nj, int nk, int nl, int nm, double *E,
+                          const double *A, const double *B, double *F,
+                          const double *C, const double *D, double *G);
+int32_t pgb200_kernel_atax(int m, int n, const double *A, const double *x,
+                           double *y, double *tmp);
+int32_t pgb200_kernel_bicg(int m, int n, const double *A, double *s, double *q,
+                           const double *p, const double *r);
+int32_t pgb200_kernel_gesummv(int n, double alpha, double beta, const double *A,
+                              const double *B, double *tmp, const double *x,
+                              double *y);
 
 #ifdef __cplusplus
 }

@@ -30,6 +30,10 @@ KERNELS = {
     "2mm": "linear-algebra/kernels/2mm/2mm.c",
     "mvt": "linear-algebra/kernels/mvt/mvt.c",
     "syrk": "linear-algebra/blas/syrk/syrk.c",
+    "3mm": "linear-algebra/kernels/3mm/3mm.c",
+    "atax": "linear-algebra/kernels/atax/atax.c",
+    "bicg": "linear-algebra/kernels/bicg/bicg.c",
+    "gesummv": "linear-algebra/blas/gesummv/gesummv.c",
 }
 TYPES = {"f64": [], "f32": ["-DDATA_TYPE_IS_FLOAT"]}
 

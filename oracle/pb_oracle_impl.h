@@ -98,6 +98,83 @@ void FN(pbo_syrk)(int64_t n, int64_t m, T alpha, T beta, T *C, int64_t ldc,
   FN(pbo_syrk_range)(0, n, m, alpha, beta, C, ldc, A, lda);
 }
 
+/* linear-algebra/kernels/3mm/3mm.c:99-124
+ *   E = A*B ; F = C*D ; G = E*F, each as  X[i][j] = 0; for k X[i][j] += L[i][k]*R[k][j] */
+void FN(pbo_3mm)(int64_t ni, int64_t nj, int64_t nk, int64_t nl, int64_t nm, T *E,
+                 const T *A, const T *B, T *F, const T *C, const T *D, T *G)
+{
+  for (int64_t i = 0; i < ni; i++)
+    for (int64_t j = 0; j < nj; j++) {
+      E[i * nj + j] = (T)0.0;
+      for (int64_t k = 0; k < nk; ++k)
+        E[i * nj + j] += A[i * nk + k] * B[k * nj + j];
+    }
+  for (int64_t i = 0; i < nj; i++)
+    for (int64_t j = 0; j < nl; j++) {
+      F[i * nl + j] = (T)0.0;
+      for (int64_t k = 0; k < nm; ++k)
+        F[i * nl + j] += C[i * nm + k] * D[k * nl + j];
+    }
+  for (int64_t i = 0; i < ni; i++)
+    for (int64_t j = 0; j < nl; j++) {
+      G[i * nl + j] = (T)0.0;
+      for (int64_t k = 0; k < nj; ++k)
+        G[i * nl + j] += E[i * nj + k] * F[k * nl + j];
+    }
+}
+
+/* linear-algebra/kernels/atax/atax.c:89-99
+ *   y = 0; for i { tmp[i] = 0; for j tmp[i] += A[i][j]*x[j];
+ *                  for j y[j] += A[i][j]*tmp[i]; }          A is m x n */
+void FN(pbo_atax)(int64_t m, int64_t n, const T *A, int64_t lda, const T *x, T *y,
+                  T *tmp)
+{
+  for (int64_t i = 0; i < n; i++)
+    y[i] = 0;
+  for (int64_t i = 0; i < m; i++) {
+    tmp[i] = (T)0.0;
+    for (int64_t j = 0; j < n; j++)
+      tmp[i] = tmp[i] + A[i * lda + j] * x[j];
+    for (int64_t j = 0; j < n; j++)
+      y[j] = y[j] + A[i * lda + j] * tmp[i];
+  }
+}
+
+/* linear-algebra/kernels/bicg/bicg.c:97-108
+ *   s = 0; for i { q[i] = 0; for j { s[j] += r[i]*A[i][j]; q[i] += A[i][j]*p[j]; } }
+ *   A is n x m */
+void FN(pbo_bicg)(int64_t m, int64_t n, const T *A, int64_t lda, T *s, T *q,
+                  const T *p, const T *r)
+{
+  for (int64_t i = 0; i < m; i++)
+    s[i] = 0;
+  for (int64_t i = 0; i < n; i++) {
+    q[i] = (T)0.0;
+    for (int64_t j = 0; j < m; j++) {
+      s[j] = s[j] + r[i] * A[i * lda + j];
+      q[i] = q[i] + A[i * lda + j] * p[j];
+    }
+  }
+}
+
+/* linear-algebra/blas/gesummv/gesummv.c:99-109
+ *   for i { tmp[i] = 0; y[i] = 0;
+ *           for j { tmp[i] = A[i][j]*x[j] + tmp[i]; y[i] = B[i][j]*x[j] + y[i]; }
+ *           y[i] = alpha*tmp[i] + beta*y[i]; } */
+void FN(pbo_gesummv)(int64_t n, T alpha, T beta, const T *A, int64_t lda, const T *B,
+                     int64_t ldb, T *tmp, const T *x, T *y)
+{
+  for (int64_t i = 0; i < n; i++) {
+    tmp[i] = (T)0.0;
+    y[i] = (T)0.0;
+    for (int64_t j = 0; j < n; j++) {
+      tmp[i] = A[i * lda + j] * x[j] + tmp[i];
+      y[i] = B[i * ldb + j] * x[j] + y[i];
+    }
+    y[i] = alpha * tmp[i] + beta * y[i];
+  }
+}
+
 /* Same statements as pbo_gemm, but with a double accumulator per output and
  * the fp32 inputs promoted: the "truth" that fp32 results are also gated on
  * (the sequential fp32 sum itself drifts from it as K grows). */

@@ -52,6 +52,7 @@ SIGNATURES = {
     "pgb200Ssyrk": (_i32, [_vp, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
     "pgb200SsyrkRows": (_i32, [_vp, _i64, _i64, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
     "pgb200Dgemv": (_i32, [_vp, _i32, _i64, _i64, _f64, _vp, _i64, _vp, _f64, _vp]),
+    "pgb200DgemvPair": (_i32, [_vp, _i64, _i64, _f64, _vp, _i64, _vp, _vp, _f64, _vp, _vp]),
     "pgb200Dmvt": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp]),
     "pgb200DmvtNoAlloc": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp]),
     "pgb200FillUniformF64": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, C.c_uint64, C.c_uint32, _f64, _f64]),
@@ -66,6 +67,10 @@ SIGNATURES = {
     "pgb200_kernel_mvt": (_i32, [_int, _vp, _vp, _vp, _vp, _vp]),
     "pgb200_kernel_syrk": (_i32, [_int, _int, _f64, _f64, _vp, _vp]),
     "pgb200_kernel_syrk_f32": (_i32, [_int, _int, _f32, _f32, _vp, _vp]),
+    "pgb200_kernel_3mm": (_i32, [_int] * 5 + [_vp] * 7),
+    "pgb200_kernel_atax": (_i32, [_int, _int, _vp, _vp, _vp, _vp]),
+    "pgb200_kernel_bicg": (_i32, [_int, _int, _vp, _vp, _vp, _vp, _vp]),
+    "pgb200_kernel_gesummv": (_i32, [_int, _f64, _f64, _vp, _vp, _vp, _vp, _vp]),
 }
 
 _lib = None
@@ -201,6 +206,15 @@ def gemv(trans, alpha, A, x, beta, y, stream=None):
     check(load().pgb200Dgemv(s, 1 if trans else 0, M, N, alpha, _ptr(A), _ld(A), _ptr(x), beta,
                              _ptr(y)))
     return y
+
+
+def gemv_pair(alpha, A, x1, x2, beta, y1, y2, stream=None):
+    """y1 = alpha*A@x1 + beta*y1 ; y2 = alpha*A^T@x2 + beta*y2 in one pass over A."""
+    M, N = A.shape
+    s = _stream(stream) if stream is not None else current_stream_for(A, y1, y2)
+    check(load().pgb200DgemvPair(s, M, N, alpha, _ptr(A), _ld(A), _ptr(x1), _ptr(x2), beta,
+                                 _ptr(y1), _ptr(y2)))
+    return y1, y2
 
 
 def mvt(A, y1, y2, x1, x2, stream=None):

@@ -120,4 +120,8 @@ int32_t stream_matvec(cudaStream_t s, int64_t M, int64_t N, const double *A, int
                       double alpha, double beta, const double *x1, double *y1,
                       const double *x2, double *y2);
 
+// y = alpha*x + beta*y on n doubles (device pointers).
+int32_t stream_axpby(cudaStream_t s, int64_t n, double alpha, const double *x, double beta,
+                     double *y);
+
 }  // namespace pgb200

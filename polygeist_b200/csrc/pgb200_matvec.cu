@@ -232,6 +232,24 @@ int32_t stream_matvec(cudaStream_t s, int64_t M, int64_t N, const double *A, int
 
 }  // namespace pgb200
 
+namespace pgb200 {
+namespace {
+__global__ void vec_axpby_kernel(double *y, const double *x, int64_t n, double alpha, double beta) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i < n) y[i] = alpha * x[i] + beta * y[i];
+}
+}  // namespace
+
+int32_t stream_axpby(cudaStream_t s, int64_t n, double alpha, const double *x, double beta,
+                     double *y) {
+  if (n <= 0) return PGB200_OK;
+  vec_axpby_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, x, n, alpha, beta);
+  note_launch(PATH_STREAM);
+  PGB_CUDA(cudaGetLastError());
+  return PGB200_OK;
+}
+}  // namespace pgb200
+
 // ---------------------------------------------------------------------------
 // pgb200DmvtNoAlloc: the fused mat-vec pair for callers that must not allocate.
 //

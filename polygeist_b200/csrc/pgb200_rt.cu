@@ -503,6 +503,13 @@ int32_t pgb200Dgemv(void *stream, int32_t transA, int64_t M, int64_t N, double a
   return matvec_entry(stream, M, N, A, lda, alpha, beta, x, y, nullptr, nullptr);
 }
 
+int32_t pgb200DgemvPair(void *stream, int64_t M, int64_t N, double alpha, const double *A,
+                        int64_t lda, const double *x1, const double *x2, double beta, double *y1,
+                        double *y2) {
+  PGB_REQUIRE((y1 || M == 0) && (y2 || N == 0), "gemv pair: null output vector");
+  return matvec_entry(stream, M, N, A, lda, alpha, beta, x1, y1, x2, y2);
+}
+
 int32_t pgb200Dmvt(void *stream, int64_t N, const double *A, int64_t lda, const double *y1,
                    const double *y2, double *x1, double *x2) {
   PGB_REQUIRE(N == 0 || (x1 && x2 && y1 && y2), "mvt: null vector");
@@ -550,6 +557,91 @@ int32_t pgb200_kernel_2mm(int ni, int nj, int nk, int nl, double alpha, double b
 int32_t pgb200_kernel_mvt(int n, double *x1, double *x2, const double *y_1, const double *y_2,
                           const double *A) {
   return pgb200Dmvt(nullptr, n, A, n, y_1, y_2, x1, x2);
+}
+
+int32_t pgb200_kernel_3mm(int ni, int nj, int nk, int nl, int nm, double *E, const double *A,
+                          const double *B, double *F, const double *C, const double *D,
+                          double *G) {
+  // E = A*B and F = C*D stay in HBM for G = E*F; all three are copied back
+  // because the C source leaves them as live-out arrays.
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(ni >= 0 && nj >= 0 && nk >= 0 && nl >= 0 && nm >= 0, "kernel_3mm: negative size");
+  cudaStream_t s = nullptr;
+  Staged<double> sa, sb, sc, sd, se, sf, sg;
+  PGB_TRY(stage<double>(s, A, ni, nk, nk, true, false, &sa));
+  PGB_TRY(stage<double>(s, B, nk, nj, nj, true, false, &sb));
+  PGB_TRY(stage<double>(s, C, nj, nm, nm, true, false, &sc));
+  PGB_TRY(stage<double>(s, D, nm, nl, nl, true, false, &sd));
+  PGB_TRY(stage<double>(s, E, ni, nj, nj, false, true, &se));
+  PGB_TRY(stage<double>(s, F, nj, nl, nl, false, true, &sf));
+  PGB_TRY(stage<double>(s, G, ni, nl, nl, false, true, &sg));
+  int32_t r = pgb200Dgemm(s, ni, nj, nk, 1.0, sa.dev, sa.ld, sb.dev, sb.ld, 0.0, se.dev, se.ld);
+  if (r == PGB200_OK)
+    r = pgb200Dgemm(s, nj, nl, nm, 1.0, sc.dev, sc.ld, sd.dev, sd.ld, 0.0, sf.dev, sf.ld);
+  if (r == PGB200_OK)
+    r = pgb200Dgemm(s, ni, nl, nj, 1.0, se.dev, se.ld, sf.dev, sf.ld, 0.0, sg.dev, sg.ld);
+  PGB_TRY(finish(s, &sa));
+  PGB_TRY(finish(s, &sb));
+  PGB_TRY(finish(s, &sc));
+  PGB_TRY(finish(s, &sd));
+  PGB_TRY(finish(s, &se));
+  PGB_TRY(finish(s, &sf));
+  PGB_TRY(finish(s, &sg));
+  PGB_CUDA(cudaStreamSynchronize(s));
+  return r;
+}
+
+int32_t pgb200_kernel_atax(int m, int n, const double *A, const double *x, double *y,
+                           double *tmp) {
+  // tmp = A x, then y = A^T tmp.  A is staged once and read twice on the GPU.
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(m >= 0 && n >= 0, "kernel_atax: negative size");
+  cudaStream_t s = nullptr;
+  Staged<double> sa, sx, sy, st;
+  PGB_TRY(stage<double>(s, A, m, n, n, true, false, &sa));
+  PGB_TRY(stage<double>(s, x, 1, n, n, true, false, &sx));
+  PGB_TRY(stage<double>(s, y, 1, n, n, false, true, &sy));
+  PGB_TRY(stage<double>(s, tmp, 1, m, m, false, true, &st));
+  int32_t r = pgb200Dgemv(s, 0, m, n, 1.0, sa.dev, sa.ld, sx.dev, 0.0, st.dev);
+  if (r == PGB200_OK) r = pgb200Dgemv(s, 1, m, n, 1.0, sa.dev, sa.ld, st.dev, 0.0, sy.dev);
+  PGB_TRY(finish(s, &sa));
+  PGB_TRY(finish(s, &sx));
+  PGB_TRY(finish(s, &sy));
+  PGB_TRY(finish(s, &st));
+  PGB_CUDA(cudaStreamSynchronize(s));
+  return r;
+}
+
+int32_t pgb200_kernel_bicg(int m, int n, const double *A, double *s_out, double *q,
+                           const double *p, const double *r) {
+  // A is n x m: q = A p (n entries), s = A^T r (m entries), one pass.
+  return pgb200DgemvPair(nullptr, n, m, 1.0, A, m, p, r, 0.0, q, s_out);
+}
+
+int32_t pgb200_kernel_gesummv(int n, double alpha, double beta, const double *A, const double *B,
+                              double *tmp, const double *x, double *y) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(n >= 0, "kernel_gesummv: negative size");
+  cudaStream_t s = nullptr;
+  Staged<double> sa, sb, sx, sy, st;
+  PGB_TRY(stage<double>(s, A, n, n, n, true, false, &sa));
+  PGB_TRY(stage<double>(s, B, n, n, n, true, false, &sb));
+  PGB_TRY(stage<double>(s, x, 1, n, n, true, false, &sx));
+  PGB_TRY(stage<double>(s, y, 1, n, n, false, true, &sy));
+  PGB_TRY(stage<double>(s, tmp, 1, n, n, false, true, &st));
+  int32_t r = pgb200Dgemv(s, 0, n, n, 1.0, sa.dev, sa.ld, sx.dev, 0.0, st.dev);  // tmp = A x
+  if (r == PGB200_OK) r = pgb200Dgemv(s, 0, n, n, 1.0, sb.dev, sb.ld, sx.dev, 0.0, sy.dev);  // y = B x
+  if (r == PGB200_OK) r = stream_axpby(s, n, alpha, st.dev, beta, sy.dev);  // y = alpha*tmp + beta*y
+  PGB_TRY(finish(s, &sa));
+  PGB_TRY(finish(s, &sb));
+  PGB_TRY(finish(s, &sx));
+  PGB_TRY(finish(s, &sy));
+  PGB_TRY(finish(s, &st));
+  PGB_CUDA(cudaStreamSynchronize(s));
+  return r;
 }
 
 int32_t pgb200_kernel_syrk(int n, int m, double alpha, double beta, double *C, const double *A) {

@@ -5,6 +5,9 @@ Same names, argument order and in-place semantics as
   kernel_2mm   tools/cgeist/Test/polybench/linear-algebra/kernels/2mm/2mm.c:92-121
   kernel_mvt   tools/cgeist/Test/polybench/linear-algebra/kernels/mvt/mvt.c:93-111
   kernel_syrk  tools/cgeist/Test/polybench/linear-algebra/blas/syrk/syrk.c:83-108
+and of the same-shaped nests kernel_3mm (kernels/3mm/3mm.c:87-127), kernel_atax
+(kernels/atax/atax.c:80-102), kernel_bicg (kernels/bicg/bicg.c:86-111) and
+kernel_gesummv (blas/gesummv/gesummv.c:86-112).
 Arrays are C-contiguous numpy arrays in host memory with exactly the extents
 given by the size arguments (the C99-prototype form of the PolyBench
 signatures); float64 takes the DATA_TYPE=double build, float32 the
@@ -46,3 +49,34 @@ def kernel_mvt(n, x1, x2, y_1, y_2, A):
 def kernel_syrk(n, m, alpha, beta, C, A):
     f = load().pgb200_kernel_syrk if C.dtype == np.float64 else load().pgb200_kernel_syrk_f32
     check(f(n, m, alpha, beta, _req(C, (n, n)), _req(A, (n, m))))
+
+
+def _f64(*arrs):
+    for a in arrs:
+        if a.dtype != np.float64:
+            raise ValueError("float64 only")
+
+
+def kernel_3mm(ni, nj, nk, nl, nm, E, A, B, F, C, D, G):
+    _f64(E, A, B, F, C, D, G)
+    check(load().pgb200_kernel_3mm(ni, nj, nk, nl, nm, _req(E, (ni, nj)), _req(A, (ni, nk)),
+                                   _req(B, (nk, nj)), _req(F, (nj, nl)), _req(C, (nj, nm)),
+                                   _req(D, (nm, nl)), _req(G, (ni, nl))))
+
+
+def kernel_atax(m, n, A, x, y, tmp):
+    _f64(A, x, y, tmp)
+    check(load().pgb200_kernel_atax(m, n, _req(A, (m, n)), _req(x, (n,)), _req(y, (n,)),
+                                    _req(tmp, (m,))))
+
+
+def kernel_bicg(m, n, A, s, q, p, r):
+    _f64(A, s, q, p, r)
+    check(load().pgb200_kernel_bicg(m, n, _req(A, (n, m)), _req(s, (m,)), _req(q, (n,)),
+                                    _req(p, (m,)), _req(r, (n,))))
+
+
+def kernel_gesummv(n, alpha, beta, A, B, tmp, x, y):
+    _f64(A, B, tmp, x, y)
+    check(load().pgb200_kernel_gesummv(n, alpha, beta, _req(A, (n, n)), _req(B, (n, n)),
+                                       _req(tmp, (n,)), _req(x, (n,)), _req(y, (n,))))

@@ -65,7 +65,52 @@ def init_syrk(n, m, dtype):
     return dt(1.5), dt(1.2), C, A
 
 
-MINI = {"gemm": (20, 25, 30), "2mm": (16, 18, 22, 24), "mvt": (40,), "syrk": (30, 20)}  # syrk: (N, M)
+def init_3mm(ni, nj, nk, nl, nm, dtype):
+    """3mm.c:41-62"""
+    dt = np.dtype(dtype).type
+    i, j = _grid(ni, nk)
+    A = ((i * j + 1) % ni).astype(dtype) / dt(5 * ni)
+    i, j = _grid(nk, nj)
+    B = ((i * (j + 1) + 2) % nj).astype(dtype) / dt(5 * nj)
+    i, j = _grid(nj, nm)
+    C = (i * (j + 3) % nl).astype(dtype) / dt(5 * nl)
+    i, j = _grid(nm, nl)
+    D = ((i * (j + 2) + 2) % nk).astype(dtype) / dt(5 * nk)
+    E, F, G = (np.zeros(s, dtype=dtype) for s in ((ni, nj), (nj, nl), (ni, nl)))
+    return E, A, B, F, C, D, G
+
+
+def init_atax(m, n, dtype):
+    """atax.c:40-54"""
+    dt = np.dtype(dtype).type
+    x = dt(1) + np.arange(n).astype(dtype) / dt(n)
+    i, j = _grid(m, n)
+    A = ((i + j) % n).astype(dtype) / dt(5 * m)
+    return A, x.astype(dtype), np.zeros(n, dtype=dtype), np.zeros(m, dtype=dtype)
+
+
+def init_bicg(m, n, dtype):
+    """bicg.c:40-54 (A is n x m)"""
+    dt = np.dtype(dtype).type
+    p = (np.arange(m) % m).astype(dtype) / dt(m)
+    r = (np.arange(n) % n).astype(dtype) / dt(n)
+    i, j = _grid(n, m)
+    A = (i * (j + 1) % n).astype(dtype) / dt(n)
+    return A, np.zeros(m, dtype=dtype), np.zeros(n, dtype=dtype), p, r
+
+
+def init_gesummv(n, dtype):
+    """gesummv.c:40-58"""
+    dt = np.dtype(dtype).type
+    x = (np.arange(n) % n).astype(dtype) / dt(n)
+    i, j = _grid(n, n)
+    A = ((i * j + 1) % n).astype(dtype) / dt(n)
+    B = ((i * j + 2) % n).astype(dtype) / dt(n)
+    return dt(1.5), dt(1.2), A, B, np.zeros(n, dtype=dtype), x, np.zeros(n, dtype=dtype)
+
+
+MINI = {"3mm": (16, 18, 20, 22, 24), "atax": (38, 42), "bicg": (38, 42), "gesummv": (30,),
+        "gemm": (20, 25, 30), "2mm": (16, 18, 22, 24), "mvt": (40,), "syrk": (30, 20)}  # syrk: (N, M)
 
 
 def read_dump(kernel, tname):

@@ -15,7 +15,8 @@ import torch
 
 import polygeist_b200 as pgb
 from helpers import (MINI, SEED, assert_dump_equal, backward_gemm, elementwise_rel, init_2mm,
-                     init_gemm, init_mvt, init_syrk, normwise, read_dump)
+                     init_3mm, init_atax, init_bicg, init_gemm, init_gesummv, init_mvt, init_syrk,
+                     normwise, read_dump)
 from oracle import pbo
 from polygeist_b200 import polybench
 
@@ -373,6 +374,72 @@ def test_kernel_syrk_dropin_reproduces_golden_dump(tname, dtype):
     alpha, beta, Cm, A = init_syrk(n, m, dtype)
     polybench.kernel_syrk(n, m, alpha, beta, Cm, A)
     assert_dump_equal(read_dump("syrk", tname)["C"], Cm, slack_ulps=1)
+
+
+@pytest.mark.parametrize("M,N", [(300, 200), (42, 38), (1030, 517), (2048, 4096)])
+def test_gemv_pair_matches_bicg_oracle(M, N):
+    """bicg nest: A is M x N (PolyBench's n x m), q = A p, s = A^T r, one pass."""
+    A = dev_fill(M, N, torch.float64, 1, 0.0, 1.0)
+    p = dev_fill(1, N, torch.float64, 2, 0.0, 1.0).reshape(N).contiguous()
+    r = dev_fill(1, M, torch.float64, 3, 0.0, 1.0).reshape(M).contiguous()
+    q = torch.full((M,), float("nan"), dtype=torch.float64, device=DEV)
+    s = torch.full((N,), float("nan"), dtype=torch.float64, device=DEV)
+    pgb.gemv_pair(1.0, A, p, r, 0.0, q, s)
+    sync_ok()
+    hs, hq = np.zeros(N), np.zeros(M)
+    pbo.bicg(np.ascontiguousarray(A.cpu().numpy()), hs, hq, p.cpu().numpy(), r.cpu().numpy())
+    assert elementwise_rel(q.cpu().numpy(), hq) <= 1e-12
+    assert elementwise_rel(s.cpu().numpy(), hs) <= 1e-12
+
+
+def test_same_shaped_nests_reproduce_golden_dumps():
+    """3mm / atax / bicg / gesummv drop-ins on the reference's MINI inputs."""
+    ni, nj, nk, nl, nm = MINI["3mm"]
+    E, A, B, F, Cm, D, G = init_3mm(ni, nj, nk, nl, nm, np.float64)
+    polybench.kernel_3mm(ni, nj, nk, nl, nm, E, A, B, F, Cm, D, G)
+    assert_dump_equal(read_dump("3mm", "f64")["G"], G, slack_ulps=1)
+    assert normwise(E, A @ B) <= 1e-12 and normwise(F, Cm @ D) <= 1e-12
+    m, n = MINI["atax"]
+    A, x, y, tmp = init_atax(m, n, np.float64)
+    polybench.kernel_atax(m, n, A, x, y, tmp)
+    assert_dump_equal(read_dump("atax", "f64")["y"], y, slack_ulps=1)
+    assert normwise(tmp, A @ x) <= 1e-12
+    m, n = MINI["bicg"]
+    A, s, q, p, r = init_bicg(m, n, np.float64)
+    polybench.kernel_bicg(m, n, A, s, q, p, r)
+    d = read_dump("bicg", "f64")
+    assert_dump_equal(d["s"], s, slack_ulps=1)
+    assert_dump_equal(d["q"], q, slack_ulps=1)
+    (n,) = MINI["gesummv"]
+    alpha, beta, A, B, tmp, x, y = init_gesummv(n, np.float64)
+    polybench.kernel_gesummv(n, alpha, beta, A, B, tmp, x, y)
+    assert_dump_equal(read_dump("gesummv", "f64")["y"], y, slack_ulps=1)
+
+
+def test_same_shaped_nests_match_oracle_on_seeded_inputs():
+    ni, nj, nk, nl, nm = 160, 136, 200, 184, 96
+    h = [pbo.fill(r, c, np.float64, SEED, k, -1.0, 1.0) for k, (r, c) in
+         enumerate([(ni, nk), (nk, nj), (nj, nm), (nm, nl)], 1)]
+    E, F, G = np.zeros((ni, nj)), np.zeros((nj, nl)), np.zeros((ni, nl))
+    E2, F2, G2 = E.copy(), F.copy(), G.copy()
+    polybench.kernel_3mm(ni, nj, nk, nl, nm, E, h[0], h[1], F, h[2], h[3], G)
+    pbo.mm3(E2, h[0], h[1], F2, h[2], h[3], G2)
+    assert normwise(G, G2) <= 1e-12 and normwise(E, E2) <= 1e-12 and normwise(F, F2) <= 1e-12
+    m, n = 700, 500
+    A = pbo.fill(m, n, np.float64, SEED, 5, 0.0, 1.0)
+    x = pbo.fill_vec(n, np.float64, SEED, 6, 0.0, 1.0)
+    y, tmp, y2, tmp2 = np.zeros(n), np.zeros(m), np.zeros(n), np.zeros(m)
+    polybench.kernel_atax(m, n, A, x, y, tmp)
+    pbo.atax(A, x, y2, tmp2)
+    assert elementwise_rel(y, y2) <= 1e-12 and elementwise_rel(tmp, tmp2) <= 1e-12
+    n = 600
+    A = pbo.fill(n, n, np.float64, SEED, 7, 0.0, 1.0)
+    B = pbo.fill(n, n, np.float64, SEED, 8, 0.0, 1.0)
+    x = pbo.fill_vec(n, np.float64, SEED, 9, 0.0, 1.0)
+    y, tmp, y2, tmp2 = np.zeros(n), np.zeros(n), np.zeros(n), np.zeros(n)
+    polybench.kernel_gesummv(n, 1.5, 1.2, A, B, tmp, x, y)
+    pbo.gesummv(1.5, 1.2, A, B, tmp2, x, y2)
+    assert elementwise_rel(y, y2) <= 1e-12 and elementwise_rel(tmp, tmp2) <= 1e-12
 
 
 def test_host_and_device_operands_can_be_mixed():

@@ -4,8 +4,8 @@ for bit on seeded inputs."""
 import numpy as np
 import pytest
 
-from helpers import (MINI, SEED, assert_dump_equal, init_2mm, init_gemm, init_mvt, init_syrk,
-                     read_dump)
+from helpers import (MINI, SEED, assert_dump_equal, init_2mm, init_3mm, init_atax, init_bicg,
+                     init_gemm, init_gesummv, init_mvt, init_syrk, read_dump)
 from oracle import pbo, ref
 
 TYPES = [("f64", np.float64), ("f32", np.float32)]
@@ -46,6 +46,24 @@ def test_syrk_golden(tname, dtype):
     assert_dump_equal(read_dump("syrk", tname)["C"], C)
     iu = np.triu_indices(n, 1)
     assert np.array_equal(C[iu], C0[iu]), "strict upper triangle must stay untouched"
+
+
+@pytest.mark.parametrize("tname,dtype", TYPES)
+def test_3mm_atax_bicg_gesummv_golden(tname, dtype):
+    E, A, B, F, C, D, G = init_3mm(*MINI["3mm"], dtype)
+    pbo.mm3(E, A, B, F, C, D, G)
+    assert_dump_equal(read_dump("3mm", tname)["G"], G)
+    A, x, y, tmp = init_atax(*MINI["atax"], dtype)
+    pbo.atax(A, x, y, tmp)
+    assert_dump_equal(read_dump("atax", tname)["y"], y)
+    A, s, q, p, r = init_bicg(*MINI["bicg"], dtype)
+    pbo.bicg(A, s, q, p, r)
+    d = read_dump("bicg", tname)
+    assert_dump_equal(d["s"], s)
+    assert_dump_equal(d["q"], q)
+    alpha, beta, A, B, tmp, x, y = init_gesummv(*MINI["gesummv"], dtype)
+    pbo.gesummv(alpha, beta, A, B, tmp, x, y)
+    assert_dump_equal(read_dump("gesummv", tname)["y"], y)
 
 
 needs_ref = pytest.mark.skipif(not ref.available(), reason="compiled reference kernels absent")
