@@ -773,11 +773,17 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   const bool shared_planes = transB && (ldb == lda) && (B <= A) && ((A - B) % lda == 0) &&
                              ((A - B) / lda + M <= N);
   const int64_t a_off_rows = shared_planes ? (A - B) / lda : 0;
-  const bool b_mn = !transB && b_raw;
+  // A row-major B can be consumed as it lies (N-major operand), which saves the
+  // transposing pre-pass, but the tensor cores run the N-major 32-byte-atom
+  // layout several percent slower (measured: 398 vs 372 ms at 32768^3).  The
+  // pre-pass is paid once per call, the slowdown per row of A: for tall
+  // products transpose B once, otherwise use it in place.
+  const bool b_mn = !transB && b_raw && M < 12288;
 
   // Scratch layout (floats): [B lo][B hi?][A lo?][A hi?]
   const size_t b_lo_n = b_mn ? (size_t)K * Np : (size_t)N * Kp;
-  const size_t b_hi_n = b_raw ? 0 : (size_t)N * Kp;
+  const bool b_inplace = b_mn || (transB && b_raw);  // B serves as its own hi part
+  const size_t b_hi_n = b_inplace ? 0 : (size_t)N * Kp;
   const size_t a_lo_n = shared_planes ? 0 : (size_t)M * Kp;
   const size_t a_hi_n = (shared_planes || a_raw) ? 0 : (size_t)M * Kp;
   void *ws = nullptr;
@@ -796,7 +802,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   const float *Bhi = nullptr;
   int64_t bhi_ld = Kp;
   // Both operands usable in place: their lo planes come from one launch.
-  const bool pair = b_raw && a_raw && !shared_planes;
+  const bool pair = b_inplace && a_raw && !shared_planes;
   if (pair) {
     const int64_t b_rows = b_mn ? K : N, b_cols = b_mn ? N : K, b_colsP = b_mn ? Np : Kp;
     const unsigned g0 = grid_for(b_rows * (b_colsP / 4)), g1 = grid_for(M * (Kp / 4));
