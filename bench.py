@@ -378,7 +378,8 @@ def run_pgb200(args, w, name):
         n, K = w["N"], w["K"]
         sp = partition.PartitionedSyrk(
             dist if world > 1 else _OneRank(), lambda al, Ar, be, Cb, rows: pgb.syrk_rows(
-                al, Ar, be, Cb, rows[0], rows[1]), src=0, chunk_rows=2048)
+                al, Ar, be, Cb, rows[0], rows[1]), src=0,
+            kchunk=int(os.environ.get("PGB_BENCH_KCHUNK", 2048)))
         b = sp.blocks(n)
         r0, r1 = b[rank], b[rank + 1]
         A = filled(n, K, 1) if rank == 0 else torch.empty((n, K), dtype=tdt, device=dev)

@@ -86,6 +86,29 @@ int32_t pgb200Sgemm(void *stream, int64_t M, int64_t N, int64_t K, float alpha,
                     const float *A, int64_t lda, const float *B, int64_t ldb,
                     float beta, float *C, int64_t ldc);
 
+/* C[MxN] = alpha * A[MxK] * B[NxK]^T + beta * C: the product of two row-major
+ * arrays over their common inner dimension, the statement shape
+ * `C[i][j] += alpha*A[i][k]*B[j][k]` of the rank-k / rank-2k nests
+ * (tools/cgeist/Test/polybench/linear-algebra/blas/syrk/syrk.c:102-105 with two
+ * different arrays).  Also the unit a GPU computes per column block when the
+ * rows of a triangular update are partitioned across devices. */
+int32_t pgb200DgemmNT(void *stream, int64_t M, int64_t N, int64_t K, double alpha,
+                      const double *A, int64_t lda, const double *B, int64_t ldb,
+                      double beta, double *C, int64_t ldc);
+int32_t pgb200SgemmNT(void *stream, int64_t M, int64_t N, int64_t K, float alpha,
+                      const float *A, int64_t lda, const float *B, int64_t ldb,
+                      float beta, float *C, int64_t ldc);
+
+/* Lower triangle of C[NxN] = alpha * (A * B^T + B * A^T) + beta * C with A, B
+ * [NxK]; the strict upper triangle is untouched.  Replaces kernel_syr2k,
+ * tools/cgeist/Test/polybench/linear-algebra/blas/syr2k/syr2k.c:100-109. */
+int32_t pgb200Dsyr2k(void *stream, int64_t N, int64_t K, double alpha,
+                     const double *A, int64_t lda, const double *B, int64_t ldb,
+                     double beta, double *C, int64_t ldc);
+int32_t pgb200Ssyr2k(void *stream, int64_t N, int64_t K, float alpha,
+                     const float *A, int64_t lda, const float *B, int64_t ldb,
+                     float beta, float *C, int64_t ldc);
+
 /* Lower triangle of C[NxN] = alpha * A[NxK] * A^T + beta * C; the strict upper
  * triangle of C is neither read nor written.  Replaces kernel_syrk,
  * tools/cgeist/Test/polybench/linear-algebra/blas/syrk/syrk.c:97-106. */
@@ -121,6 +144,16 @@ int32_t pgb200Dgemv(void *stream, int32_t transA, int64_t M, int64_t N,
 int32_t pgb200DgemvPair(void *stream, int64_t M, int64_t N, double alpha,
                         const double *A, int64_t lda, const double *x1,
                         const double *x2, double beta, double *y1, double *y2);
+
+/* The four nests of kernel_gemver,
+ * tools/cgeist/Test/polybench/linear-algebra/blas/gemver/gemver.c:114-131:
+ *   A += u1 v1^T + u2 v2^T;  x += beta * A^T y;  x += z;  w += alpha * A x
+ * in two passes over A[NxN] instead of four (the rank-2 update is fused with
+ * the transposed product; A is updated in place like in the C source). */
+int32_t pgb200Dgemver(void *stream, int64_t N, double alpha, double beta,
+                      double *A, int64_t lda, const double *u1, const double *v1,
+                      const double *u2, const double *v2, double *w, double *x,
+                      const double *y, const double *z);
 
 /* x1 += A * y1 and x2 += A^T * y2 with A[NxN] read ONCE for both results.
  * Replaces the whole scop of kernel_mvt, mvt.c:102-109. */
@@ -228,6 +261,16 @@ int32_t pgb200_kernel_syrk_f32(int n, int m, float alpha, float beta, float *C,
  *                             y = A^T tmp: two passes, the second depends on the first)
  *   pgb200_kernel_bicg     <- kernel_bicg     kernels/bicg/bicg.c:86-111 (one fused pass)
  *   pgb200_kernel_gesummv  <- kernel_gesummv  blas/gesummv/gesummv.c:86-112 */
+/*   pgb200_kernel_syr2k    <- kernel_syr2k    blas/syr2k/syr2k.c:84-112
+ *   pgb200_kernel_gemver   <- kernel_gemver   blas/gemver/gemver.c:97-133 */
+int32_t pgb200_kernel_gemver(int n, double alpha, double beta, double *A,
+                             const double *u1, const double *v1, const double *u2,
+                             const double *v2, double *w, double *x,
+                             const double *y, const double *z);
+int32_t pgb200_kernel_syr2k(int n, int m, double alpha, double beta, double *C,
+                            const double *A, const double *B);
+int32_t pgb200_kernel_syr2k_f32(int n, int m, float alpha, float beta, float *C,
+                                const float *A, const float *B);
 int32_t pgb200_kernel_3mm(int ni, int nj, int nk, int nl, int nm, double *E,
                           const double *A, const double *B, double *F,
                           const double *C, const double *D, double *G);

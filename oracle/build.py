@@ -34,6 +34,8 @@ KERNELS = {
     "atax": "linear-algebra/kernels/atax/atax.c",
     "bicg": "linear-algebra/kernels/bicg/bicg.c",
     "gesummv": "linear-algebra/blas/gesummv/gesummv.c",
+    "syr2k": "linear-algebra/blas/syr2k/syr2k.c",
+    "gemver": "linear-algebra/blas/gemver/gemver.c",
 }
 TYPES = {"f64": [], "f32": ["-DDATA_TYPE_IS_FLOAT"]}
 

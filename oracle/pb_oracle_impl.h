@@ -175,6 +175,38 @@ void FN(pbo_gesummv)(int64_t n, T alpha, T beta, const T *A, int64_t lda, const 
   }
 }
 
+/* linear-algebra/blas/syr2k/syr2k.c:100-109
+ *   for i { for j<=i C[i][j] *= beta;
+ *           for k for j<=i C[i][j] += A[j][k]*alpha*B[i][k] + B[j][k]*alpha*A[i][k]; } */
+void FN(pbo_syr2k)(int64_t n, int64_t m, T alpha, T beta, T *C, int64_t ldc, const T *A,
+                   int64_t lda, const T *B, int64_t ldb)
+{
+  for (int64_t i = 0; i < n; i++) {
+    for (int64_t j = 0; j <= i; j++)
+      C[i * ldc + j] *= beta;
+    for (int64_t k = 0; k < m; k++)
+      for (int64_t j = 0; j <= i; j++)
+        C[i * ldc + j] += A[j * lda + k] * alpha * B[i * ldb + k] + B[j * ldb + k] * alpha * A[i * lda + k];
+  }
+}
+
+/* linear-algebra/blas/gemver/gemver.c:114-131 (four nests, in order) */
+void FN(pbo_gemver)(int64_t n, T alpha, T beta, T *A, int64_t lda, const T *u1, const T *v1,
+                    const T *u2, const T *v2, T *w, T *x, const T *y, const T *z)
+{
+  for (int64_t i = 0; i < n; i++)
+    for (int64_t j = 0; j < n; j++)
+      A[i * lda + j] = A[i * lda + j] + u1[i] * v1[j] + u2[i] * v2[j];
+  for (int64_t i = 0; i < n; i++)
+    for (int64_t j = 0; j < n; j++)
+      x[i] = x[i] + beta * A[j * lda + i] * y[j];
+  for (int64_t i = 0; i < n; i++)
+    x[i] = x[i] + z[i];
+  for (int64_t i = 0; i < n; i++)
+    for (int64_t j = 0; j < n; j++)
+      w[i] = w[i] + alpha * A[i * lda + j] * x[j];
+}
+
 /* Same statements as pbo_gemm, but with a double accumulator per output and
  * the fp32 inputs promoted: the "truth" that fp32 results are also gated on
  * (the sequential fp32 sum itself drifts from it as K grows). */

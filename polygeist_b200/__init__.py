@@ -48,11 +48,16 @@ SIGNATURES = {
     "pgb200Version": (_i32, []),
     "pgb200Dgemm": (_i32, [_vp, _i64, _i64, _i64, _f64, _vp, _i64, _vp, _i64, _f64, _vp, _i64]),
     "pgb200Sgemm": (_i32, [_vp, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64, _f32, _vp, _i64]),
+    "pgb200DgemmNT": (_i32, [_vp, _i64, _i64, _i64, _f64, _vp, _i64, _vp, _i64, _f64, _vp, _i64]),
+    "pgb200SgemmNT": (_i32, [_vp, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64, _f32, _vp, _i64]),
+    "pgb200Dsyr2k": (_i32, [_vp, _i64, _i64, _f64, _vp, _i64, _vp, _i64, _f64, _vp, _i64]),
+    "pgb200Ssyr2k": (_i32, [_vp, _i64, _i64, _f32, _vp, _i64, _vp, _i64, _f32, _vp, _i64]),
     "pgb200Dsyrk": (_i32, [_vp, _i64, _i64, _f64, _vp, _i64, _f64, _vp, _i64]),
     "pgb200Ssyrk": (_i32, [_vp, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
     "pgb200SsyrkRows": (_i32, [_vp, _i64, _i64, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
     "pgb200Dgemv": (_i32, [_vp, _i32, _i64, _i64, _f64, _vp, _i64, _vp, _f64, _vp]),
     "pgb200DgemvPair": (_i32, [_vp, _i64, _i64, _f64, _vp, _i64, _vp, _vp, _f64, _vp, _vp]),
+    "pgb200Dgemver": (_i32, [_vp, _i64, _f64, _f64, _vp, _i64] + [_vp] * 8),
     "pgb200Dmvt": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp]),
     "pgb200DmvtNoAlloc": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp]),
     "pgb200FillUniformF64": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, C.c_uint64, C.c_uint32, _f64, _f64]),
@@ -67,6 +72,9 @@ SIGNATURES = {
     "pgb200_kernel_mvt": (_i32, [_int, _vp, _vp, _vp, _vp, _vp]),
     "pgb200_kernel_syrk": (_i32, [_int, _int, _f64, _f64, _vp, _vp]),
     "pgb200_kernel_syrk_f32": (_i32, [_int, _int, _f32, _f32, _vp, _vp]),
+    "pgb200_kernel_syr2k": (_i32, [_int, _int, _f64, _f64, _vp, _vp, _vp]),
+    "pgb200_kernel_syr2k_f32": (_i32, [_int, _int, _f32, _f32, _vp, _vp, _vp]),
+    "pgb200_kernel_gemver": (_i32, [_int, _f64, _f64] + [_vp] * 9),
     "pgb200_kernel_3mm": (_i32, [_int] * 5 + [_vp] * 7),
     "pgb200_kernel_atax": (_i32, [_int, _int, _vp, _vp, _vp, _vp]),
     "pgb200_kernel_bicg": (_i32, [_int, _int, _vp, _vp, _vp, _vp, _vp]),
@@ -167,6 +175,27 @@ def gemm(alpha, A, B, beta, Cm, stream=None):
     s = _stream(stream) if stream is not None else current_stream_for(A, B, Cm)
     fn = load().pgb200Dgemm if _is_f64(Cm) else load().pgb200Sgemm
     check(fn(s, M, N, K, alpha, _ptr(A), _ld(A), _ptr(B), _ld(B), beta, _ptr(Cm), _ld(Cm)))
+    return Cm
+
+
+def gemm_nt(alpha, A, B, beta, Cm, stream=None):
+    """Cm = alpha*A@B^T + beta*Cm in place (A [M,K], B [N,K])."""
+    M, K = A.shape
+    N = B.shape[0]
+    assert B.shape[1] == K and tuple(Cm.shape) == (M, N)
+    s = _stream(stream) if stream is not None else current_stream_for(A, B, Cm)
+    fn = load().pgb200DgemmNT if _is_f64(Cm) else load().pgb200SgemmNT
+    check(fn(s, M, N, K, alpha, _ptr(A), _ld(A), _ptr(B), _ld(B), beta, _ptr(Cm), _ld(Cm)))
+    return Cm
+
+
+def syr2k(alpha, A, B, beta, Cm, stream=None):
+    """Lower triangle of Cm = alpha*(A@B^T + B@A^T) + beta*Cm in place."""
+    N, K = A.shape
+    assert tuple(B.shape) == (N, K) and tuple(Cm.shape) == (N, N)
+    s = _stream(stream) if stream is not None else current_stream_for(A, B, Cm)
+    fn = load().pgb200Dsyr2k if _is_f64(Cm) else load().pgb200Ssyr2k
+    check(fn(s, N, K, alpha, _ptr(A), _ld(A), _ptr(B), _ld(B), beta, _ptr(Cm), _ld(Cm)))
     return Cm
 
 

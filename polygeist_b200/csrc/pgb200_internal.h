@@ -120,6 +120,11 @@ int32_t stream_matvec(cudaStream_t s, int64_t M, int64_t N, const double *A, int
                       double alpha, double beta, const double *x1, double *y1,
                       const double *x2, double *y2);
 
+// gemver in two passes over A (device pointers; A is updated in place).
+int32_t stream_gemver(cudaStream_t s, int64_t N, double alpha, double beta, double *A, int64_t lda,
+                      const double *u1, const double *v1, const double *u2, const double *v2,
+                      double *w, double *x, const double *y, const double *z);
+
 // y = alpha*x + beta*y on n doubles (device pointers).
 int32_t stream_axpby(cudaStream_t s, int64_t n, double alpha, const double *x, double beta,
                      double *y);

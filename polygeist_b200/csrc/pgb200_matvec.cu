@@ -36,12 +36,22 @@ __device__ __forceinline__ double2 ldg_stream_v2(const double *p) {
   return v;
 }
 
-template <bool VEC>
+// Optional rank-2 update fused into the pass (gemver's first nest): when R2,
+// every element becomes A + u1[r]*v1[c] + u2[r]*v2[c] (each product and sum
+// rounded separately, like the C statement compiled without contraction), is
+// written back, and the updated value feeds the dot products.
+struct Rank2 {
+  double *Aw;
+  const double *u1, *v1, *u2, *v2;
+};
+
+template <bool VEC, bool R2 = false>
 __global__ void __launch_bounds__(MV_WARPS * 32, 2)
 matvec_tile_kernel(const double *__restrict__ A, int64_t lda, int64_t M, int64_t N,
                    const double *__restrict__ x1, const double *__restrict__ x2,
                    double *__restrict__ p1 /* [tiles_c][M] */,
-                   double *__restrict__ p2 /* [tiles_r][N] */, int64_t tiles_r, int64_t tiles_c) {
+                   double *__restrict__ p2 /* [tiles_r][N] */, int64_t tiles_r, int64_t tiles_c,
+                   Rank2 r2 = Rank2{nullptr, nullptr, nullptr, nullptr, nullptr}) {
   __shared__ double red[MV_WARPS][MV_TC];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t ntiles = tiles_r * tiles_c;
@@ -50,6 +60,7 @@ matvec_tile_kernel(const double *__restrict__ A, int64_t lda, int64_t M, int64_t
     const int64_t r0 = tr * MV_TR, c0 = tc * MV_TC;
     double xv[MV_Q][2];
     double colacc[MV_Q][2];
+    double v1v[MV_Q][2], v2v[MV_Q][2];
 #pragma unroll
     for (int q = 0; q < MV_Q; q++) {
       const int64_t c = c0 + 64 * q + 2 * lane;
@@ -57,6 +68,12 @@ matvec_tile_kernel(const double *__restrict__ A, int64_t lda, int64_t M, int64_t
       xv[q][1] = (x1 && c + 1 < N) ? x1[c + 1] : 0.0;
       colacc[q][0] = 0.0;
       colacc[q][1] = 0.0;
+      if (R2) {
+        v1v[q][0] = c < N ? r2.v1[c] : 0.0;
+        v1v[q][1] = c + 1 < N ? r2.v1[c + 1] : 0.0;
+        v2v[q][0] = c < N ? r2.v2[c] : 0.0;
+        v2v[q][1] = c + 1 < N ? r2.v2[c + 1] : 0.0;
+      }
     }
     for (int it = 0; it < MV_ROWS_PER_WARP / MV_RU; it++) {
       double a[MV_RU][MV_Q][2];
@@ -67,10 +84,24 @@ matvec_tile_kernel(const double *__restrict__ A, int64_t lda, int64_t M, int64_t
         const bool rok = r < M;
         w[u] = (x2 && rok) ? x2[r] : 0.0;
         const double *row = A + r * lda;
+        const double u1r = (R2 && rok) ? r2.u1[r] : 0.0, u2r = (R2 && rok) ? r2.u2[r] : 0.0;
 #pragma unroll
         for (int q = 0; q < MV_Q; q++) {
           const int64_t c = c0 + 64 * q + 2 * lane;
-          if (VEC) {
+          if (R2) {
+            // Read-modify-write of A: plain loads (the data is written back).
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+              if (rok && c + e < N) {
+                double v = row[c + e];
+                v = __dadd_rn(__dadd_rn(v, __dmul_rn(u1r, v1v[q][e])), __dmul_rn(u2r, v2v[q][e]));
+                r2.Aw[r * lda + c + e] = v;
+                a[u][q][e] = v;
+              } else {
+                a[u][q][e] = 0.0;
+              }
+            }
+          } else if (VEC) {
             if (rok && c < N) {  // N even on this path: c+1 < N too
               const double2 v = ldg_stream_v2(row + c);
               a[u][q][0] = v.x;
@@ -239,6 +270,31 @@ __global__ void vec_axpby_kernel(double *y, const double *x, int64_t n, double a
   if (i < n) y[i] = alpha * x[i] + beta * y[i];
 }
 }  // namespace
+
+// gemver (blas/gemver/gemver.c:114-131) in two passes over A instead of four:
+//   pass 1: A += u1 v1^T + u2 v2^T fused with x += beta * A^T y (then x += z)
+//   pass 2: w += alpha * A x
+int32_t stream_gemver(cudaStream_t s, int64_t N, double alpha, double beta, double *A, int64_t lda,
+                      const double *u1, const double *v1, const double *u2, const double *v2,
+                      double *w, double *x, const double *y, const double *z) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  if (N == 0) return PGB200_OK;
+  const int64_t tiles_r = (N + MV_TR - 1) / MV_TR, tiles_c = (N + MV_TC - 1) / MV_TC;
+  void *ws = nullptr;
+  PGB_TRY(get_workspace(s, (size_t)tiles_r * N * sizeof(double), &ws));
+  double *p2 = static_cast<double *>(ws);
+  const int64_t ntiles = tiles_r * tiles_c, cap = (int64_t)rt->num_sms * 2;
+  const unsigned grid = (unsigned)(ntiles < cap ? ntiles : cap);
+  Rank2 r2{A, u1, v1, u2, v2};
+  matvec_tile_kernel<false, true><<<grid, MV_WARPS * 32, 0, s>>>(A, lda, N, N, nullptr, y, nullptr,
+                                                                 p2, tiles_r, tiles_c, r2);
+  matvec_reduce_kernel<<<(unsigned)((N + 255) / 256), 256, 0, s>>>(x, p2, tiles_r, N, beta, 1.0);
+  note_launch(PATH_STREAM, 2);
+  PGB_CUDA(cudaGetLastError());
+  PGB_TRY(stream_axpby(s, N, 1.0, z, 1.0, x));
+  return stream_matvec(s, N, N, A, lda, alpha, 1.0, x, w, nullptr, nullptr);
+}
 
 int32_t stream_axpby(cudaStream_t s, int64_t n, double alpha, const double *x, double beta,
                      double *y) {

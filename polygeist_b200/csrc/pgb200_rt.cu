@@ -376,7 +376,8 @@ static int32_t gemm_device(cudaStream_t s, int64_t M, int64_t N, int64_t K, T al
 
 template <typename T>
 static int32_t gemm_entry(void *stream, int64_t M, int64_t N, int64_t K, T alpha, const T *A,
-                          int64_t lda, const T *B, int64_t ldb, T beta, T *C, int64_t ldc) {
+                          int64_t lda, const T *B, int64_t ldb, T beta, T *C, int64_t ldc,
+                          bool transB = false) {
   Runtime *rt = nullptr;
   PGB_TRY(get_runtime(&rt));
   PGB_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative size (M=%lld N=%lld K=%lld)",
@@ -384,16 +385,19 @@ static int32_t gemm_entry(void *stream, int64_t M, int64_t N, int64_t K, T alpha
   if (M == 0 || N == 0) return PGB200_OK;
   PGB_REQUIRE(C && ldc >= N, "gemm: C is null or ldc (%lld) < N (%lld)", (long long)ldc,
               (long long)N);
-  PGB_REQUIRE(K == 0 || (A && B && lda >= K && ldb >= N),
-              "gemm: A/B null or lda (%lld) < K (%lld) or ldb (%lld) < N (%lld)", (long long)lda,
-              (long long)K, (long long)ldb, (long long)N);
+  PGB_REQUIRE(K == 0 || (A && B && lda >= K && ldb >= (transB ? K : N)),
+              "gemm: A/B null or lda (%lld) < K (%lld) or ldb (%lld) too small for N (%lld)",
+              (long long)lda, (long long)K, (long long)ldb, (long long)N);
   cudaStream_t s = (cudaStream_t)stream;
   Staged<T> sa, sb, sc;
   PGB_TRY(stage<T>(s, A, M, K, lda, true, false, &sa));
-  PGB_TRY(stage<T>(s, B, K, N, ldb, true, false, &sb));
+  if (transB)
+    PGB_TRY(stage<T>(s, B, N, K, ldb, true, false, &sb));
+  else
+    PGB_TRY(stage<T>(s, B, K, N, ldb, true, false, &sb));
   PGB_TRY(stage<T>(s, C, M, N, ldc, beta != (T)0, true, &sc));
   const bool staged = sa.host || sb.host || sc.host;
-  int32_t st = gemm_device<T>(s, M, N, K, alpha, sa.dev, sa.ld, sb.dev, sb.ld, false, beta,
+  int32_t st = gemm_device<T>(s, M, N, K, alpha, sa.dev, sa.ld, sb.dev, sb.ld, transB, beta,
                               sc.dev, sc.ld, false, 0);
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
@@ -427,6 +431,36 @@ static int32_t syrk_entry(void *stream, int64_t N, int64_t K, int64_t row0, int6
   int32_t st = gemm_device<T>(s, row1 - row0, row1, K, alpha, sa.dev + row0 * sa.ld, sa.ld,
                               sa.dev, sa.ld, true, beta, sc.dev, sc.ld, true, row0);
   PGB_TRY(finish(s, &sa));
+  PGB_TRY(finish(s, &sc));
+  if (staged) PGB_CUDA(cudaStreamSynchronize(s));
+  return st;
+}
+
+// Lower triangle of C = alpha*(A*B^T + B*A^T) + beta*C: two masked NT products.
+template <typename T>
+static int32_t syr2k_entry(void *stream, int64_t N, int64_t K, T alpha, const T *A, int64_t lda,
+                           const T *B, int64_t ldb, T beta, T *C, int64_t ldc) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(N >= 0 && K >= 0, "syr2k: negative size");
+  if (N == 0) return PGB200_OK;
+  PGB_REQUIRE(C && ldc >= N, "syr2k: C is null or ldc (%lld) < N (%lld)", (long long)ldc,
+              (long long)N);
+  PGB_REQUIRE(K == 0 || (A && B && lda >= K && ldb >= K), "syr2k: A/B null or lda/ldb < K (%lld)",
+              (long long)K);
+  cudaStream_t s = (cudaStream_t)stream;
+  Staged<T> sa, sb, sc;
+  PGB_TRY(stage<T>(s, A, N, K, lda, true, false, &sa));
+  PGB_TRY(stage<T>(s, B, N, K, ldb, true, false, &sb));
+  PGB_TRY(stage<T>(s, C, N, N, ldc, true, true, &sc));
+  const bool staged = sa.host || sb.host || sc.host;
+  int32_t st = gemm_device<T>(s, N, N, K, alpha, sb.dev, sb.ld, sa.dev, sa.ld, true, beta, sc.dev,
+                              sc.ld, true, 0);
+  if (st == PGB200_OK)
+    st = gemm_device<T>(s, N, N, K, alpha, sa.dev, sa.ld, sb.dev, sb.ld, true, (T)1, sc.dev, sc.ld,
+                        true, 0);
+  PGB_TRY(finish(s, &sa));
+  PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sc));
   if (staged) PGB_CUDA(cudaStreamSynchronize(s));
   return st;
@@ -480,6 +514,29 @@ int32_t pgb200Sgemm(void *stream, int64_t M, int64_t N, int64_t K, float alpha, 
   return gemm_entry<float>(stream, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
 }
 
+int32_t pgb200DgemmNT(void *stream, int64_t M, int64_t N, int64_t K, double alpha,
+                      const double *A, int64_t lda, const double *B, int64_t ldb, double beta,
+                      double *C, int64_t ldc) {
+  return gemm_entry<double>(stream, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, true);
+}
+
+int32_t pgb200SgemmNT(void *stream, int64_t M, int64_t N, int64_t K, float alpha, const float *A,
+                      int64_t lda, const float *B, int64_t ldb, float beta, float *C,
+                      int64_t ldc) {
+  return gemm_entry<float>(stream, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, true);
+}
+
+int32_t pgb200Dsyr2k(void *stream, int64_t N, int64_t K, double alpha, const double *A,
+                     int64_t lda, const double *B, int64_t ldb, double beta, double *C,
+                     int64_t ldc) {
+  return syr2k_entry<double>(stream, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
+}
+
+int32_t pgb200Ssyr2k(void *stream, int64_t N, int64_t K, float alpha, const float *A, int64_t lda,
+                     const float *B, int64_t ldb, float beta, float *C, int64_t ldc) {
+  return syr2k_entry<float>(stream, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
+}
+
 int32_t pgb200Dsyrk(void *stream, int64_t N, int64_t K, double alpha, const double *A,
                     int64_t lda, double beta, double *C, int64_t ldc) {
   return syrk_entry<double>(stream, N, K, 0, N, alpha, A, lda, beta, C, ldc);
@@ -508,6 +565,43 @@ int32_t pgb200DgemvPair(void *stream, int64_t M, int64_t N, double alpha, const 
                         double *y2) {
   PGB_REQUIRE((y1 || M == 0) && (y2 || N == 0), "gemv pair: null output vector");
   return matvec_entry(stream, M, N, A, lda, alpha, beta, x1, y1, x2, y2);
+}
+
+int32_t pgb200Dgemver(void *stream, int64_t N, double alpha, double beta, double *A, int64_t lda,
+                      const double *u1, const double *v1, const double *u2, const double *v2,
+                      double *w, double *x, const double *y, const double *z) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(N >= 0, "gemver: negative size");
+  if (N == 0) return PGB200_OK;
+  PGB_REQUIRE(A && u1 && v1 && u2 && v2 && w && x && y && z && lda >= N,
+              "gemver: null pointer or lda (%lld) < N (%lld)", (long long)lda, (long long)N);
+  cudaStream_t s = (cudaStream_t)stream;
+  Staged<double> sa, su1, sv1, su2, sv2, sw, sx, sy, sz;
+  PGB_TRY(stage<double>(s, A, N, N, lda, true, true, &sa));
+  PGB_TRY(stage<double>(s, u1, 1, N, N, true, false, &su1));
+  PGB_TRY(stage<double>(s, v1, 1, N, N, true, false, &sv1));
+  PGB_TRY(stage<double>(s, u2, 1, N, N, true, false, &su2));
+  PGB_TRY(stage<double>(s, v2, 1, N, N, true, false, &sv2));
+  PGB_TRY(stage<double>(s, w, 1, N, N, true, true, &sw));
+  PGB_TRY(stage<double>(s, x, 1, N, N, true, true, &sx));
+  PGB_TRY(stage<double>(s, y, 1, N, N, true, false, &sy));
+  PGB_TRY(stage<double>(s, z, 1, N, N, true, false, &sz));
+  const bool staged = sa.host || su1.host || sv1.host || su2.host || sv2.host || sw.host ||
+                      sx.host || sy.host || sz.host;
+  int32_t st = stream_gemver(s, N, alpha, beta, sa.dev, sa.ld, su1.dev, sv1.dev, su2.dev, sv2.dev,
+                             sw.dev, sx.dev, sy.dev, sz.dev);
+  PGB_TRY(finish(s, &sa));
+  PGB_TRY(finish(s, &su1));
+  PGB_TRY(finish(s, &sv1));
+  PGB_TRY(finish(s, &su2));
+  PGB_TRY(finish(s, &sv2));
+  PGB_TRY(finish(s, &sw));
+  PGB_TRY(finish(s, &sx));
+  PGB_TRY(finish(s, &sy));
+  PGB_TRY(finish(s, &sz));
+  if (staged) PGB_CUDA(cudaStreamSynchronize(s));
+  return st;
 }
 
 int32_t pgb200Dmvt(void *stream, int64_t N, const double *A, int64_t lda, const double *y1,
@@ -646,6 +740,22 @@ int32_t pgb200_kernel_gesummv(int n, double alpha, double beta, const double *A,
 
 int32_t pgb200_kernel_syrk(int n, int m, double alpha, double beta, double *C, const double *A) {
   return pgb200Dsyrk(nullptr, n, m, alpha, A, m, beta, C, n);
+}
+
+int32_t pgb200_kernel_gemver(int n, double alpha, double beta, double *A, const double *u1,
+                             const double *v1, const double *u2, const double *v2, double *w,
+                             double *x, const double *y, const double *z) {
+  return pgb200Dgemver(nullptr, n, alpha, beta, A, n, u1, v1, u2, v2, w, x, y, z);
+}
+
+int32_t pgb200_kernel_syr2k(int n, int m, double alpha, double beta, double *C, const double *A,
+                            const double *B) {
+  return pgb200Dsyr2k(nullptr, n, m, alpha, A, m, B, m, beta, C, n);
+}
+
+int32_t pgb200_kernel_syr2k_f32(int n, int m, float alpha, float beta, float *C, const float *A,
+                                const float *B) {
+  return pgb200Ssyr2k(nullptr, n, m, alpha, A, m, B, m, beta, C, n);
 }
 
 int32_t pgb200_kernel_syrk_f32(int n, int m, float alpha, float beta, float *C, const float *A) {

@@ -157,45 +157,54 @@ class PartitionedGemm:
 class PartitionedSyrk:
     """Lower triangle of C = alpha*A@A^T + beta*C with the rows of C split over
     the ranks by equal triangular area.  Rank p owns rows [b[p], b[p+1]) of C
-    and needs rows [0, b[p+1]) of A, which lives on `src` and is broadcast in
-    row chunks; a rank starts computing as soon as the chunks it needs are in.
+    and needs rows [0, b[p+1]) of A, which lives on `src`.
+
+    A rank can only start once it holds its own rows of A, and with a row-wise
+    broadcast the last rank receives those last.  The operand is therefore sent
+    in K-slices: `src` packs the columns [k0,k1) of A into a contiguous
+    [N, k1-k0] block, broadcasts it, and every rank accumulates
+    C_p += alpha * A_p[:, k0:k1] @ A[0:r1, k0:k1]^T (beta applied with the first
+    slice) while the next slice is in flight.
 
     `compute(alpha, A_rows_0_to_r1, beta, C_block, rows)` must update rows
     `rows=(r0,r1)` of the triangular result in place, `C_block` being those
     rows of C (the product path wraps pgb200SsyrkRows).
     """
 
-    def __init__(self, dist, compute, src=0, chunk_rows=2048, group=None, align=128):
+    def __init__(self, dist, compute, src=0, kchunk=2048, group=None, align=128):
         self.dist = dist
         self.compute = compute
         self.src = src
-        self.chunk_rows = chunk_rows
+        self.kchunk = kchunk
         self.group = group
         self.align = align
+        self._packed = None
 
     def blocks(self, N):
         return syrk_row_blocks(N, self.dist.get_world_size(self.group), self.align)
 
     def run(self, alpha, A_local, beta, C_block):
         dist = self.dist
-        N = A_local.shape[0]
+        N, K = A_local.shape
         world = dist.get_world_size(self.group)
         rank = dist.get_rank(self.group)
         b = self.blocks(N)
         r0, r1 = b[rank], b[rank + 1]
+        if world == 1:
+            self.compute(alpha, A_local, beta, C_block, (r0, r1))
+            return C_block
+        chunks = k_chunks(K, self.kchunk)
+        if self._packed is None or len(self._packed) != len(chunks):
+            self._packed = [A_local.new_empty((N, k1 - k0)) for k0, k1 in chunks]
         works = []
-        if world > 1:
-            for c0, c1 in k_chunks(N, self.chunk_rows):
-                w = dist.broadcast(A_local[c0:c1], src=self.src, group=self.group, async_op=True)
-                works.append((c0, w))
-            for c0, w in works:
-                if c0 < r1:
-                    w.wait()
-        if r1 > r0:
-            self.compute(alpha, A_local[:r1], beta, C_block, (r0, r1))
-        # Transfers this rank did not need still have to finish before A_local
-        # may be reused.
-        for c0, w in works:
-            if c0 >= r1:
-                w.wait()
+        for (k0, k1), buf in zip(chunks, self._packed):
+            if rank == self.src:
+                buf.copy_(A_local[:, k0:k1])
+            works.append(dist.broadcast(buf, src=self.src, group=self.group, async_op=True))
+        first = True
+        for w, buf in zip(works, self._packed):
+            w.wait()
+            if r1 > r0:
+                self.compute(alpha, buf[:r1], beta if first else 1.0, C_block, (r0, r1))
+            first = False
         return C_block

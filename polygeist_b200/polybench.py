@@ -6,7 +6,7 @@ Same names, argument order and in-place semantics as
   kernel_mvt   tools/cgeist/Test/polybench/linear-algebra/kernels/mvt/mvt.c:93-111
   kernel_syrk  tools/cgeist/Test/polybench/linear-algebra/blas/syrk/syrk.c:83-108
 and of the same-shaped nests kernel_3mm (kernels/3mm/3mm.c:87-127), kernel_atax
-(kernels/atax/atax.c:80-102), kernel_bicg (kernels/bicg/bicg.c:86-111) and
+(kernels/atax/atax.c:80-102), kernel_syr2k (blas/syr2k/syr2k.c:84-112), kernel_gemver (blas/gemver/gemver.c:97-133), kernel_bicg (kernels/bicg/bicg.c:86-111) and
 kernel_gesummv (blas/gesummv/gesummv.c:86-112).
 Arrays are C-contiguous numpy arrays in host memory with exactly the extents
 given by the size arguments (the C99-prototype form of the PolyBench
@@ -80,3 +80,14 @@ def kernel_gesummv(n, alpha, beta, A, B, tmp, x, y):
     _f64(A, B, tmp, x, y)
     check(load().pgb200_kernel_gesummv(n, alpha, beta, _req(A, (n, n)), _req(B, (n, n)),
                                        _req(tmp, (n,)), _req(x, (n,)), _req(y, (n,))))
+
+
+def kernel_syr2k(n, m, alpha, beta, C, A, B):
+    f = load().pgb200_kernel_syr2k if C.dtype == np.float64 else load().pgb200_kernel_syr2k_f32
+    check(f(n, m, alpha, beta, _req(C, (n, n)), _req(A, (n, m)), _req(B, (n, m))))
+
+
+def kernel_gemver(n, alpha, beta, A, u1, v1, u2, v2, w, x, y, z):
+    _f64(A, u1, v1, u2, v2, w, x, y, z)
+    vecs = [_req(v, (n,)) for v in (u1, v1, u2, v2, w, x, y, z)]
+    check(load().pgb200_kernel_gemver(n, alpha, beta, _req(A, (n, n)), *vecs))

@@ -109,7 +109,31 @@ def init_gesummv(n, dtype):
     return dt(1.5), dt(1.2), A, B, np.zeros(n, dtype=dtype), x, np.zeros(n, dtype=dtype)
 
 
-MINI = {"3mm": (16, 18, 20, 22, 24), "atax": (38, 42), "bicg": (38, 42), "gesummv": (30,),
+def init_syr2k(n, m, dtype):
+    """syr2k.c:40-60"""
+    dt = np.dtype(dtype).type
+    i, j = _grid(n, m)
+    A = ((i * j + 1) % n).astype(dtype) / dt(n)
+    B = ((i * j + 2) % m).astype(dtype) / dt(m)
+    i, j = _grid(n, n)
+    C = ((i * j + 3) % n).astype(dtype) / dt(m)
+    return dt(1.5), dt(1.2), C, A, B
+
+
+def init_gemver(n, dtype):
+    """gemver.c:40-73"""
+    dt = np.dtype(dtype).type
+    i = np.arange(n)
+    f = (i + 1).astype(dtype) / dt(n)
+    u1 = i.astype(dtype)
+    u2, v1, v2, y, z = f / dt(2.0), f / dt(4.0), f / dt(6.0), f / dt(8.0), f / dt(9.0)
+    ii, jj = _grid(n, n)
+    A = (ii * jj % n).astype(dtype) / dt(n)
+    return (dt(1.5), dt(1.2), A, u1, v1.astype(dtype), u2.astype(dtype), v2.astype(dtype),
+            np.zeros(n, dtype=dtype), np.zeros(n, dtype=dtype), y.astype(dtype), z.astype(dtype))
+
+
+MINI = {"gemver": (40,), "syr2k": (30, 20), "3mm": (16, 18, 20, 22, 24), "atax": (38, 42), "bicg": (38, 42), "gesummv": (30,),
         "gemm": (20, 25, 30), "2mm": (16, 18, 22, 24), "mvt": (40,), "syrk": (30, 20)}  # syrk: (N, M)
 
 

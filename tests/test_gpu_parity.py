@@ -15,7 +15,9 @@ import torch
 
 import polygeist_b200 as pgb
 from helpers import (MINI, SEED, assert_dump_equal, backward_gemm, elementwise_rel, init_2mm,
-                     init_3mm, init_atax, init_bicg, init_gemm, init_gesummv, init_mvt, init_syrk,
+                     init_3mm, init_atax, init_bicg, init_gemm, init_gemver, init_gesummv, init_mvt,
+                     init_syr2k,
+                     init_syrk,
                      normwise, read_dump)
 from oracle import pbo
 from polygeist_b200 import polybench
@@ -440,6 +442,56 @@ def test_same_shaped_nests_match_oracle_on_seeded_inputs():
     polybench.kernel_gesummv(n, 1.5, 1.2, A, B, tmp, x, y)
     pbo.gesummv(1.5, 1.2, A, B, tmp2, x, y2)
     assert elementwise_rel(y, y2) <= 1e-12 and elementwise_rel(tmp, tmp2) <= 1e-12
+
+
+@pytest.mark.parametrize("dtype,np_dtype", [(torch.float64, np.float64), (torch.float32, np.float32)])
+@pytest.mark.parametrize("M,N,K", [(256, 384, 128), (200, 136, 100), (97, 61, 45)])
+def test_gemm_nt_matches_numpy(dtype, np_dtype, M, N, K):
+    lo = -1.0 if dtype == torch.float64 else 0.0
+    A = dev_fill(M, K, dtype, 1, lo, 1.0)
+    B = dev_fill(N, K, dtype, 2, lo, 1.0)
+    Cm = dev_fill(M, N, dtype, 3, lo, 1.0)
+    truth = 1.5 * (A.double() @ B.double().T) + 1.2 * Cm.double()
+    pgb.gemm_nt(1.5, A, B, 1.2, Cm)
+    sync_ok()
+    if dtype == torch.float64:
+        assert float((Cm - truth).abs().max() / truth.abs().max()) <= 1e-12
+    else:
+        assert float(((Cm.double() - truth).abs() / truth.abs()).max()) <= 1e-5
+
+
+@pytest.mark.parametrize("np_dtype,tname", [(np.float64, "f64"), (np.float32, "f32")])
+def test_syr2k_matches_oracle_and_golden(np_dtype, tname):
+    n, m = MINI["syr2k"]
+    alpha, beta, Cm, A, B = init_syr2k(n, m, np_dtype)
+    polybench.kernel_syr2k(n, m, alpha, beta, Cm, A, B)
+    assert_dump_equal(read_dump("syr2k", tname)["C"], Cm, slack_ulps=1)
+    n, k = 300, 136
+    A = pbo.fill(n, k, np_dtype, SEED, 1, 0.0, 1.0)
+    B = pbo.fill(n, k, np_dtype, SEED, 2, 0.0, 1.0)
+    C0 = pbo.fill(n, n, np_dtype, SEED, 3, 0.0, 1.0)
+    got = C0.copy()
+    polybench.kernel_syr2k(n, k, 1.5, 1.2, got, A, B)
+    ref = pbo.syr2k(1.5, 1.2, C0.copy(), A, B)
+    il, iu = np.tril_indices(n), np.triu_indices(n, 1)
+    assert elementwise_rel(got[il], ref[il]) <= (1e-12 if np_dtype == np.float64 else 1e-5)
+    assert np.array_equal(got[iu], C0[iu])
+
+
+def test_gemver_matches_oracle_and_golden():
+    (n,) = MINI["gemver"]
+    alpha, beta, A, u1, v1, u2, v2, w, x, y, z = init_gemver(n, np.float64)
+    polybench.kernel_gemver(n, alpha, beta, A, u1, v1, u2, v2, w, x, y, z)
+    assert_dump_equal(read_dump("gemver", "f64")["w"], w, slack_ulps=1)
+    for n in (700, 1030):
+        A = pbo.fill(n, n, np.float64, SEED, 1, 0.0, 1.0)
+        v = [pbo.fill_vec(n, np.float64, SEED, 2 + k, 0.0, 1.0) for k in range(8)]
+        A2, v2_ = A.copy(), [t.copy() for t in v]
+        polybench.kernel_gemver(n, 1.5, 1.2, A, *v)
+        pbo.gemver(1.5, 1.2, A2, *v2_)
+        assert np.array_equal(A, A2), "rank-2 update is rounded like the C statement"
+        assert elementwise_rel(v[5], v2_[5]) <= 1e-12      # x
+        assert elementwise_rel(v[4], v2_[4]) <= 1e-12      # w
 
 
 def test_host_and_device_operands_can_be_mixed():

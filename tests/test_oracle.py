@@ -5,7 +5,8 @@ import numpy as np
 import pytest
 
 from helpers import (MINI, SEED, assert_dump_equal, init_2mm, init_3mm, init_atax, init_bicg,
-                     init_gemm, init_gesummv, init_mvt, init_syrk, read_dump)
+                     init_gemm, init_gemver, init_gesummv, init_mvt, init_syr2k, init_syrk,
+                     read_dump)
 from oracle import pbo, ref
 
 TYPES = [("f64", np.float64), ("f32", np.float32)]
@@ -64,6 +65,12 @@ def test_3mm_atax_bicg_gesummv_golden(tname, dtype):
     alpha, beta, A, B, tmp, x, y = init_gesummv(*MINI["gesummv"], dtype)
     pbo.gesummv(alpha, beta, A, B, tmp, x, y)
     assert_dump_equal(read_dump("gesummv", tname)["y"], y)
+    alpha, beta, Cm, A, B = init_syr2k(*MINI["syr2k"], dtype)
+    pbo.syr2k(alpha, beta, Cm, A, B)
+    assert_dump_equal(read_dump("syr2k", tname)["C"], Cm)
+    alpha, beta, A, u1, v1, u2, v2, w, x, y, z = init_gemver(*MINI["gemver"], dtype)
+    pbo.gemver(alpha, beta, A, u1, v1, u2, v2, w, x, y, z)
+    assert_dump_equal(read_dump("gemver", tname)["w"], w)
 
 
 needs_ref = pytest.mark.skipif(not ref.available(), reason="compiled reference kernels absent")

@@ -101,7 +101,7 @@ def _worker(rank, world, port, q):
         As = rng.uniform(0, 1, (Ns, Ks))
         Cs = rng.uniform(0, 1, (Ns, Ns))
         refs = np.where(np.tril(np.ones((Ns, Ns), bool)), 1.5 * As @ As.T + 1.2 * Cs, Cs)
-        sp = partition.PartitionedSyrk(dist, _np_syrk, src=0, chunk_rows=32, align=8)
+        sp = partition.PartitionedSyrk(dist, _np_syrk, src=0, kchunk=10, align=8)
         bs = sp.blocks(Ns)
         s0, s1 = bs[rank], bs[rank + 1]
         A_loc = torch.from_numpy(As.copy()) if rank == 0 else torch.full((Ns, Ks), float("nan"), dtype=torch.float64)
