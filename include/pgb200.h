@@ -228,6 +228,14 @@ int32_t pgb200PollDeviceStatus(void);
  * 3xTF32 fp32 path can deliver at most a third.  Synchronises the stream.  No counterpart in the reference. */
 int32_t pgb200ProbePeak(void *stream, int32_t kind, double *out);
 
+/* Exercises that path without any fault: launches one CTA that waits on a
+ * barrier nothing ever signals, for at most `limit_cycles` SM cycles (clamped
+ * to about one second), after which it records a code and returns.  A
+ * following synchronise + pgb200PollDeviceStatus() must report
+ * PGB200_ERR_TIMEOUT, and the context stays usable.  No counterpart in the
+ * reference. */
+int32_t pgb200SelfTestWaitTimeout(void *stream, int64_t limit_cycles);
+
 /* How many of this library's kernels this thread has launched so far. */
 int64_t pgb200LaunchCount(void);
 

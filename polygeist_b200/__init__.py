@@ -64,6 +64,7 @@ SIGNATURES = {
     "pgb200FillUniformF32": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, C.c_uint64, C.c_uint32, _f32, _f32]),
     "pgb200LastPath": (_i32, []),
     "pgb200PollDeviceStatus": (_i32, []),
+    "pgb200SelfTestWaitTimeout": (_i32, [_vp, _i64]),
     "pgb200LaunchCount": (_i64, []),
     "pgb200ProbePeak": (_i32, [_vp, _i32, C.POINTER(_f64)]),
     "pgb200_kernel_gemm": (_i32, [_int, _int, _int, _f64, _f64, _vp, _vp, _vp]),

@@ -114,6 +114,10 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
 // kind::tf32 tensor-pipe issue-rate probe (dense GFLOP/s).
 int32_t tf32_peak_probe(cudaStream_t s, double *gflops);
 
+// Launches a one-CTA kernel whose wait can never be satisfied, bounded by
+// `limit_cycles`; it must record status code 99 and return.
+int32_t wait_timeout_selftest(cudaStream_t s, long long limit_cycles);
+
 // HBM-streaming mat-vec: y1 = beta*y1 + alpha*A*x1 (if y1) and
 // y2 = beta*y2 + alpha*A^T*x2 (if y2) in one pass over A[MxN].
 int32_t stream_matvec(cudaStream_t s, int64_t M, int64_t N, const double *A, int64_t lda,

@@ -310,6 +310,10 @@ int32_t pgb200PollDeviceStatus(void) {
   return PGB200_OK;
 }
 
+int32_t pgb200SelfTestWaitTimeout(void *stream, int64_t limit_cycles) {
+  return wait_timeout_selftest((cudaStream_t)stream, (long long)limit_cycles);
+}
+
 int32_t pgb200FillUniformF64(void *stream, double *dst, int64_t row0, int64_t rows, int64_t cols,
                              int64_t ld, uint64_t seed, uint32_t array_id, double lo, double hi) {
   Runtime *rt = nullptr;

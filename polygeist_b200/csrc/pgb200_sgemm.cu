@@ -727,6 +727,32 @@ __global__ void __launch_bounds__(128, 1) tf32_probe_kernel(int iters, int32_t *
 
 }  // namespace
 
+// Self-test of the bounded-wait machinery: one CTA waits on an mbarrier that
+// nothing ever arrives at, with a caller-chosen cycle limit, and must come back
+// with a status code instead of hanging.
+__global__ void wait_timeout_selftest_kernel(long long limit_cycles, int32_t *status) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const long long t0 = clock64();
+    bool done = false;
+    while (!done && clock64() - t0 <= limit_cycles) done = mbar_try(smem_u32(&bar), 0);
+    if (!done) report_status(status, 99, (int32_t)blockIdx.x);
+  }
+}
+
+int32_t wait_timeout_selftest(cudaStream_t s, long long limit_cycles) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  if (limit_cycles < 0) limit_cycles = 0;
+  if (limit_cycles > 2000000000ll) limit_cycles = 2000000000ll;  // never more than ~1 s
+  wait_timeout_selftest_kernel<<<1, 32, 0, s>>>(limit_cycles, rt->status_dev);
+  note_launch(PATH_TCGEN05);
+  PGB_CUDA(cudaGetLastError());
+  return PGB200_OK;
+}
+
 int32_t tf32_peak_probe(cudaStream_t s, double *gflops) {
   Runtime *rt = nullptr;
   PGB_TRY(get_runtime(&rt));

@@ -494,6 +494,23 @@ def test_gemver_matches_oracle_and_golden():
         assert elementwise_rel(v[4], v2_[4]) <= 1e-12      # w
 
 
+def test_bounded_wait_reports_timeout_and_context_survives():
+    """A device-side wait that can never be satisfied must end by itself, surface
+    as PGB200_ERR_TIMEOUT on the host, and leave the GPU usable."""
+    lib = pgb.load()
+    assert lib.pgb200SelfTestWaitTimeout(None, 2_000_000) == pgb.OK   # ~1 ms
+    torch.cuda.synchronize()
+    assert lib.pgb200PollDeviceStatus() == pgb.ERR_TIMEOUT
+    assert b"code 99" in lib.pgb200GetLastErrorString()
+    assert lib.pgb200PollDeviceStatus() == pgb.OK                      # cleared by the read
+    A = dev_fill(128, 64, torch.float64, 1, -1.0, 1.0)
+    B = dev_fill(64, 128, torch.float64, 2, -1.0, 1.0)
+    Cm = torch.zeros((128, 128), dtype=torch.float64, device=DEV)
+    pgb.gemm(1.0, A, B, 0.0, Cm)
+    sync_ok()
+    assert float((Cm - A @ B).abs().max()) <= 1e-12
+
+
 def test_host_and_device_operands_can_be_mixed():
     M, N, K = 96, 64, 48
     A = dev_fill(M, K, torch.float64, 1, -1.0, 1.0)
