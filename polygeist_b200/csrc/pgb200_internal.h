@@ -48,6 +48,9 @@ struct Runtime {
   // non-zero code there when a bounded wait expires.
   volatile int32_t *status_host;
   int32_t *status_dev;
+  // Side streams of the host-array path: uploads and downloads of row blocks
+  // run beside the products of the blocks already on the device.
+  cudaStream_t copy_in, copy_out;
 };
 
 // Lazily initialises the runtime for the current device; fails (no CPU

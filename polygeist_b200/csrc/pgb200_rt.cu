@@ -89,6 +89,8 @@ int32_t get_runtime(Runtime **out) {
   void *d = nullptr;
   PGB_CUDA(cudaHostGetDevicePointer(&d, h, 0));
   rt->status_dev = static_cast<int32_t *>(d);
+  PGB_CUDA(cudaStreamCreateWithFlags(&rt->copy_in, cudaStreamNonBlocking));
+  PGB_CUDA(cudaStreamCreateWithFlags(&rt->copy_out, cudaStreamNonBlocking));
   if (!g_encode) {
     void *fn = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -285,6 +287,8 @@ int32_t pgb200Shutdown(void) {
   for (auto &kv : g_rt) {
     cudaSetDevice(kv.first);
     cudaFreeHost(const_cast<int32_t *>(kv.second->status_host));
+    cudaStreamDestroy(kv.second->copy_in);
+    cudaStreamDestroy(kv.second->copy_out);
     delete kv.second;
   }
   g_rt.clear();
@@ -379,6 +383,85 @@ static int32_t gemm_device(cudaStream_t s, int64_t M, int64_t N, int64_t K, T al
 }
 
 template <typename T>
+static cudaError_t copy_rows(T *dst, int64_t dst_ld, const T *src, int64_t src_ld, int64_t rows,
+                             int64_t cols, cudaMemcpyKind kind, cudaStream_t s) {
+  if (rows == 0 || cols == 0) return cudaSuccess;
+  if (dst_ld == src_ld && (dst_ld == cols || rows == 1))
+    return cudaMemcpyAsync(dst, src, (size_t)rows * cols * sizeof(T), kind, s);
+  return cudaMemcpy2DAsync(dst, dst_ld * sizeof(T), src, src_ld * sizeof(T), cols * sizeof(T),
+                           rows, kind, s);
+}
+
+// Host-array GEMM for large problems: the rows of A and C travel in blocks, so
+// that block i+1 is uploaded and block i-1 downloaded (PCIe is full duplex)
+// while block i is being multiplied.  B goes first, whole.  The result is what
+// the plain staged path gives; only the schedule differs.
+template <typename T>
+static int32_t gemm_host_pipelined(Runtime *rt, cudaStream_t s, int64_t M, int64_t N, int64_t K,
+                                   T alpha, const T *A, int64_t lda, const T *B, int64_t ldb,
+                                   T beta, T *C, int64_t ldc, bool transB) {
+  const int64_t per16 = 16 / (int64_t)sizeof(T);
+  auto pad = [&](int64_t c) { return (c + per16 - 1) / per16 * per16; };
+  const int64_t b_rows = transB ? N : K, b_cols = transB ? K : N;
+  const int64_t dlda = pad(K), dldb = pad(b_cols), dldc = pad(N);
+  T *dA = nullptr, *dB = nullptr, *dC = nullptr;
+  PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dA), (size_t)M * dlda * sizeof(T), s));
+  PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dB), (size_t)b_rows * dldb * sizeof(T), s));
+  PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dC), (size_t)M * dldc * sizeof(T), s));
+  constexpr int MAXB = 16;
+  int nb = (int)(M / 512);
+  if (nb > MAXB) nb = MAXB;
+  if (nb < 1) nb = 1;
+  int64_t rows_per = ((M + nb - 1) / nb + 127) / 128 * 128;
+  nb = (int)((M + rows_per - 1) / rows_per);
+  cudaEvent_t ev_start, ev_in[MAXB], ev_c[MAXB], ev_done;
+  PGB_CUDA(cudaEventCreateWithFlags(&ev_start, cudaEventDisableTiming));
+  PGB_CUDA(cudaEventCreateWithFlags(&ev_done, cudaEventDisableTiming));
+  for (int i = 0; i < nb; i++) {
+    PGB_CUDA(cudaEventCreateWithFlags(&ev_in[i], cudaEventDisableTiming));
+    PGB_CUDA(cudaEventCreateWithFlags(&ev_c[i], cudaEventDisableTiming));
+  }
+  PGB_CUDA(cudaEventRecord(ev_start, s));  // buffers exist, earlier work on s is done
+  PGB_CUDA(cudaStreamWaitEvent(rt->copy_in, ev_start, 0));
+  PGB_CUDA(cudaStreamWaitEvent(rt->copy_out, ev_start, 0));
+  PGB_CUDA(copy_rows(dB, dldb, B, ldb, b_rows, b_cols, cudaMemcpyHostToDevice, rt->copy_in));
+  for (int i = 0; i < nb; i++) {
+    const int64_t r0 = i * rows_per, rows = (M - r0 < rows_per) ? (M - r0) : rows_per;
+    PGB_CUDA(copy_rows(dA + r0 * dlda, dlda, A + r0 * lda, lda, rows, K, cudaMemcpyHostToDevice,
+                       rt->copy_in));
+    if (beta != (T)0)
+      PGB_CUDA(copy_rows(dC + r0 * dldc, dldc, C + r0 * ldc, ldc, rows, N, cudaMemcpyHostToDevice,
+                         rt->copy_in));
+    PGB_CUDA(cudaEventRecord(ev_in[i], rt->copy_in));
+  }
+  int32_t st = PGB200_OK;
+  for (int i = 0; i < nb && st == PGB200_OK; i++) {
+    const int64_t r0 = i * rows_per, rows = (M - r0 < rows_per) ? (M - r0) : rows_per;
+    PGB_CUDA(cudaStreamWaitEvent(s, ev_in[i], 0));
+    st = gemm_device<T>(s, rows, N, K, alpha, dA + r0 * dlda, dlda, dB, dldb, transB, beta,
+                        dC + r0 * dldc, dldc, false, 0);
+    PGB_CUDA(cudaEventRecord(ev_c[i], s));
+    PGB_CUDA(cudaStreamWaitEvent(rt->copy_out, ev_c[i], 0));
+    PGB_CUDA(copy_rows(C + r0 * ldc, ldc, dC + r0 * dldc, dldc, rows, N, cudaMemcpyDeviceToHost,
+                       rt->copy_out));
+  }
+  PGB_CUDA(cudaEventRecord(ev_done, rt->copy_out));
+  PGB_CUDA(cudaStreamWaitEvent(s, ev_done, 0));
+  PGB_CUDA(cudaFreeAsync(dA, s));
+  PGB_CUDA(cudaFreeAsync(dB, s));
+  PGB_CUDA(cudaFreeAsync(dC, s));
+  PGB_CUDA(cudaStreamSynchronize(rt->copy_in));
+  PGB_CUDA(cudaStreamSynchronize(s));
+  cudaEventDestroy(ev_start);
+  cudaEventDestroy(ev_done);
+  for (int i = 0; i < nb; i++) {
+    cudaEventDestroy(ev_in[i]);
+    cudaEventDestroy(ev_c[i]);
+  }
+  return st;
+}
+
+template <typename T>
 static int32_t gemm_entry(void *stream, int64_t M, int64_t N, int64_t K, T alpha, const T *A,
                           int64_t lda, const T *B, int64_t ldb, T beta, T *C, int64_t ldc,
                           bool transB = false) {
@@ -393,6 +476,9 @@ static int32_t gemm_entry(void *stream, int64_t M, int64_t N, int64_t K, T alpha
               "gemm: A/B null or lda (%lld) < K (%lld) or ldb (%lld) too small for N (%lld)",
               (long long)lda, (long long)K, (long long)ldb, (long long)N);
   cudaStream_t s = (cudaStream_t)stream;
+  if (K > 0 && M >= 1024 && (double)M * (double)N * (double)K >= 1e9 && is_host_pointer(A) &&
+      is_host_pointer(B) && is_host_pointer(C))
+    return gemm_host_pipelined<T>(rt, s, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, transB);
   Staged<T> sa, sb, sc;
   PGB_TRY(stage<T>(s, A, M, K, lda, true, false, &sa));
   if (transB)

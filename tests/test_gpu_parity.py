@@ -511,6 +511,74 @@ def test_bounded_wait_reports_timeout_and_context_survives():
     assert float((Cm - A @ B).abs().max()) <= 1e-12
 
 
+@pytest.mark.parametrize("np_dtype", [np.float64, np.float32])
+@pytest.mark.parametrize("beta", [1.2, 0.0])
+def test_large_host_array_gemm_is_pipelined_and_correct(np_dtype, beta):
+    """Host arrays above the pipelining threshold: rows of A and C travel in
+    blocks beside the products; the result must equal the oracle's."""
+    M, N, K = 2304, 1000, 520          # M not a multiple of the block height, padded pitches
+    lo = -1.0 if np_dtype == np.float64 else 0.0
+    A = pbo.fill(M, K, np_dtype, SEED, 1, lo, 1.0)
+    B = pbo.fill(K, N, np_dtype, SEED, 2, lo, 1.0)
+    C0 = pbo.fill(M, N, np_dtype, SEED, 3, lo, 1.0)
+    got = C0.copy() if beta else np.full_like(C0, np.nan)
+    polybench.kernel_gemm(M, N, K, 1.5, beta, got, A, B)
+    pgb.poll_device_status()
+    rows = [0, 1, 127, 128, 1151, 1152, M - 1]
+    for r in rows:
+        ref = pbo.gemm(1.5, beta, C0[r:r + 1].copy(), A[r:r + 1], B)
+        if np_dtype == np.float64:
+            assert normwise(got[r:r + 1], ref) <= 1e-12
+        else:
+            assert elementwise_rel(got[r:r + 1], ref) <= 1e-5
+    truth = 1.5 * (A.astype(np.float64) @ B.astype(np.float64)) + beta * (C0.astype(np.float64) if beta else 0.0)
+    assert normwise(got, truth) <= (1e-12 if np_dtype == np.float64 else 1e-5)
+
+
+def test_concurrent_host_threads_on_their_own_streams():
+    """Generated code may call from OpenMP worker threads: two threads, each on
+    its own stream, interleave fp64/fp32 GEMMs and the fused mat-vec (all of
+    which use per-stream scratch) and must both get the right answers."""
+    import threading
+    errs = []
+
+    def worker(tid):
+        try:
+            torch.cuda.set_device(0)
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                n = 384 + 128 * tid
+                A = dev_fill(n, n, torch.float64, 10 + tid, -1.0, 1.0)
+                B = dev_fill(n, n, torch.float64, 20 + tid, -1.0, 1.0)
+                A32 = dev_fill(n, n, torch.float32, 30 + tid, 0.0, 1.0)
+                B32 = dev_fill(n, n, torch.float32, 40 + tid, 0.0, 1.0)
+                x = dev_fill(1, n, torch.float64, 50 + tid, 0.0, 1.0).reshape(n).contiguous()
+                for _ in range(5):
+                    Cm = torch.zeros((n, n), dtype=torch.float64, device=DEV)
+                    C32 = torch.zeros((n, n), dtype=torch.float32, device=DEV)
+                    y1 = torch.zeros(n, dtype=torch.float64, device=DEV)
+                    y2 = torch.zeros(n, dtype=torch.float64, device=DEV)
+                    pgb.gemm(1.0, A, B, 0.0, Cm, stream=st)
+                    pgb.gemm(1.0, A32, B32, 0.0, C32, stream=st)
+                    pgb.gemv_pair(1.0, A, x, x, 0.0, y1, y2, stream=st)
+                    st.synchronize()
+                    assert float((Cm - A @ B).abs().max() / (A @ B).abs().max()) <= 1e-12
+                    t32 = A32.double() @ B32.double()
+                    assert float(((C32.double() - t32).abs() / t32).max()) <= 1e-5
+                    assert float((y1 - A @ x).abs().max() / (A @ x).abs().max()) <= 1e-12
+                    assert float((y2 - A.T @ x).abs().max() / (A.T @ x).abs().max()) <= 1e-12
+        except Exception as e:  # surfaced in the main thread
+            errs.append((tid, repr(e)))
+
+    ts = [threading.Thread(target=worker, args=(t,)) for t in range(2)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    assert not errs, errs
+    pgb.poll_device_status()
+
+
 def test_host_and_device_operands_can_be_mixed():
     M, N, K = 96, 64, 48
     A = dev_fill(M, K, torch.float64, 1, -1.0, 1.0)
