@@ -435,7 +435,7 @@ def run_pgb200(args, w, name):
         step()
     barrier()
     sampler = None
-    if rank == 0:
+    if rank == 0 and not os.environ.get("PGB_BENCH_NO_CLOCKS"):
         sampler = NvmlSampler(local)
         if not sampler.ok:
             sampler = ClockSampler(local)
