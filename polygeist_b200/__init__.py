@@ -110,8 +110,10 @@ def check(status):
         raise PGB200Error(status, load().pgb200GetLastErrorString().decode())
 
 
-def init(log_level=0, sgemm_chunk_kblocks=0, force_generic=0, sgemm_planes_only=0, reserve_sms=0):
+def init(log_level=0, sgemm_chunk_kblocks=0, force_generic=0, sgemm_planes_only=0, reserve_sms=0,
+         sgemm_two_cta=0):
     cfg = Config(log_level, sgemm_chunk_kblocks, force_generic, sgemm_planes_only, reserve_sms)
+    cfg.reserved[0] = sgemm_two_cta
     check(load().pgb200Init(C.byref(cfg)))
 
 

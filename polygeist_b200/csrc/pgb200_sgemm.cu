@@ -32,8 +32,10 @@
 // accumulator with truncation, which biases long all-positive sums (measured:
 // -3.0e-4 relative at K=32768 in one accumulation).  Draining every
 // `chunk_kblocks` K-blocks and adding the chunks in round-to-nearest fp32
-// registers bounds that bias independently of K (about 2e-6 at the default 4;
-// the drain overlaps the next chunk, so short chunks cost nothing measurable).
+// registers bounds that bias independently of K.  Each hand-off costs the tensor
+// pipe about 0.3 us (the tensor-memory reads of the drain compete with the
+// running MMAs), so the default of 8 K-blocks trades ~3e-6 of bias for ~5 % of
+// time; 4 gives 2e-6 for ~13 %, 16 gives 5e-6 for ~2 %.
 //
 // Every wait is time-bounded: on expiry the kernel records a code in the
 // host-visible status word, leaves its loops, frees its tensor memory and
@@ -55,7 +57,7 @@ constexpr int FIRST_EPI_WARP = 4;                         // warps 0-3: producer
 constexpr int THREADS = 32 * (FIRST_EPI_WARP + EPI_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_CYCLES = 4000000000ll;           // ~2 s
-constexpr int DEFAULT_CHUNK_KBLOCKS = 4;                  // 64 K-elements
+constexpr int DEFAULT_CHUNK_KBLOCKS = 8;                  // 128 K-elements
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -95,11 +97,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 // Same, for waits entered by whole warps: sleeps between polls so that the
 // spinning warps do not compete with the single MMA-issuing thread.
 __device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity) {
-  if (mbar_try(bar, parity)) return true;
+  // The accumulator hand-off is on the critical path of short chunks: poll
+  // back to back for a while before starting to sleep between polls.
+  for (int i = 0; i < 64; i++)
+    if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
     for (int i = 0; i < 16; i++) {
-      __nanosleep(64);
+      __nanosleep(32);
       if (mbar_try(bar, parity)) return true;
     }
     if (clock64() - t0 > WAIT_CYCLES) return false;
@@ -202,6 +207,73 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t saddr) {
 constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
                            ((uint32_t)(BM >> 4) << 24);
 constexpr uint32_t IDESC_BMN = IDESC | (1u << 16);
+
+// alpha/beta epilogue of one drain warp: `acc` holds, per thread, one row x COLS
+// columns of the tile (row = r_base + lane, columns cb..cb+COLS-1).  Accessing C
+// that way would touch 32 different rows per instruction, so the warp turns
+// 32x32 blocks through a padded shared tile and reads/writes C as full 128-byte
+// row segments (lane = column).  Interior blocks are software-pipelined: the 16
+// loads of the next half-block are in flight while the current one is stored.
+template <int COLS>
+__device__ __forceinline__ void epilogue_store(const float (&acc)[COLS], float (*st)[33], int lane,
+                                               int64_t r_base, int64_t cb, int64_t M, int64_t N,
+                                               int64_t ldc, float *__restrict__ C, float alpha,
+                                               float beta, bool lower, int64_t row0) {
+  constexpr int NB = COLS / 32;
+  const bool all_interior = (r_base + 31 < M) && (cb + COLS - 1 < N) &&
+                            (!lower || cb + COLS - 1 <= r_base + row0);
+  if (all_interior) {
+    float *cptr = C + r_base * ldc + cb + lane;
+    float cur[16], nxt[16];
+    if (beta != 0.0f) {
+#pragma unroll
+      for (int q = 0; q < 16; q++) cur[q] = __ldcs(cptr + q * ldc);
+    }
+#pragma unroll
+    for (int hb = 0; hb < 2 * NB; hb++) {
+      const int blk = hb >> 1, h = hb & 1;
+      if (h == 0) {
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 32; i++) st[lane][i] = alpha * acc[blk * 32 + i];
+        __syncwarp();
+      }
+      if (beta != 0.0f && hb + 1 < 2 * NB) {
+        const int nblk = (hb + 1) >> 1, nh = (hb + 1) & 1;
+#pragma unroll
+        for (int q = 0; q < 16; q++) nxt[q] = __ldcs(cptr + nblk * 32 + (nh * 16 + q) * ldc);
+      }
+#pragma unroll
+      for (int q = 0; q < 16; q++) {
+        const float o = st[h * 16 + q][lane];
+        cptr[blk * 32 + (h * 16 + q) * ldc] = (beta != 0.0f) ? fmaf(beta, cur[q], o) : o;
+      }
+#pragma unroll
+      for (int q = 0; q < 16; q++) cur[q] = nxt[q];
+    }
+    return;
+  }
+  // Ragged edge or diagonal tile: block by block, element by element.
+#pragma unroll
+  for (int blk = 0; blk < NB; blk++) {
+    if (cb + blk * 32 >= N) break;
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 32; i++) st[lane][i] = alpha * acc[blk * 32 + i];
+    __syncwarp();
+    const int64_t c = cb + blk * 32 + lane;
+    float *cptr = C + r_base * ldc + c;
+#pragma unroll 4
+    for (int rr = 0; rr < 32; rr++) {
+      const int64_t r = r_base + rr;
+      if (c < N && r < M && (!lower || c <= r + row0)) {
+        float o = st[rr][lane];
+        if (beta != 0.0f) o = fmaf(beta, cptr[rr * ldc], o);
+        cptr[rr * ldc] = o;
+      }
+    }
+  }
+}
 
 struct Tiles {
   int64_t tiles_m, tiles_n, total;
@@ -466,12 +538,17 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
         const uint32_t taddr =
             tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + (uint32_t)(half * COLS);
 #pragma unroll
-        for (int j = 0; j < COLS / 32; j++) {
-          uint32_t v[32];
-          tc_ld32(taddr + j * 32, v);
+        for (int j = 0; j < COLS / 32; j += 2) {
+          uint32_t v0[32], v1[32];
+          tc_ld32(taddr + j * 32, v0);
+          if (j + 1 < COLS / 32) tc_ld32(taddr + j * 32 + 32, v1);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; i++) acc[j * 32 + i] += __uint_as_float(v[i]);
+          for (int i = 0; i < 32; i++) acc[j * 32 + i] += __uint_as_float(v0[i]);
+          if (j + 1 < COLS / 32) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) acc[j * 32 + 32 + i] += __uint_as_float(v1[i]);
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -479,57 +556,8 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
       }
       if (!ok) break;
 
-      // alpha/beta epilogue.  A thread holds one row x 128 columns of the tile;
-      // accessing C that way would touch 32 different rows per instruction.
-      // Each warp instead turns 32x32 blocks through a padded shared tile, so
-      // that a load/store instruction covers one full 128-byte row segment.
-      // The 32 loads of a block are all issued before their first use.
-      const int64_t r_base = tm * BM + quarter * 32;
-      const int64_t cb = tn * BN + half * COLS;
-      float(*st)[33] = epi_stage[ew];
-#pragma unroll
-      for (int cc = 0; cc < COLS / 32; cc++) {
-        if (cb + cc * 32 >= N) break;
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 32; i++) st[lane][i] = alpha * acc[cc * 32 + i];
-        __syncwarp();
-        const int64_t c = cb + cc * 32 + lane;
-        float *cptr = C + r_base * ldc + c;
-        const int64_t c_last = cb + cc * 32 + 31;
-        const bool interior = (r_base + 31 < M) && (c_last < N) &&
-                              (!tiles.lower || c_last <= r_base + tiles.row0);
-        if (interior) {
-          // Whole 32x32 block inside the matrix (and below the diagonal): no
-          // per-element predicates, 16 loads in flight.
-#pragma unroll
-          for (int h = 0; h < 2; h++) {
-            float old[16];
-            if (beta != 0.0f) {
-#pragma unroll
-              for (int q = 0; q < 16; q++) old[q] = __ldcs(cptr + (h * 16 + q) * ldc);
-            } else {
-#pragma unroll
-              for (int q = 0; q < 16; q++) old[q] = 0.0f;
-            }
-#pragma unroll
-            for (int q = 0; q < 16; q++)
-              cptr[(h * 16 + q) * ldc] = fmaf(beta, old[q], st[h * 16 + q][lane]);
-          }
-        } else {
-          // Ragged edge or diagonal block: element by element.
-          const bool col_ok = c < N;
-#pragma unroll 4
-          for (int rr = 0; rr < 32; rr++) {
-            const int64_t r = r_base + rr;
-            if (col_ok && r < M && (!tiles.lower || c <= r + tiles.row0)) {
-              float o = st[rr][lane];
-              if (beta != 0.0f) o = fmaf(beta, cptr[rr * ldc], o);
-              cptr[rr * ldc] = o;
-            }
-          }
-        }
-      }
+      epilogue_store<COLS>(acc, epi_stage[ew], lane, tm * BM + quarter * 32, tn * BN + half * COLS,
+                           M, N, ldc, C, alpha, beta, tiles.lower != 0, tiles.row0);
     }
   }
 
@@ -727,6 +755,311 @@ __global__ void __launch_bounds__(128, 1) tf32_probe_kernel(int iters, int32_t *
 
 }  // namespace
 
+// ===========================================================================
+// Two-CTA variant (cta_group::2) of the same pipeline for large full products.
+//
+// A cluster of two CTAs on an SM pair shares one 256x256 output tile: CTA r
+// holds rows [128r, 128r+128) of the tile's A panel and columns
+// [128r, 128r+128) of its B panel, and the accumulator rows of its own half in
+// its own tensor memory.  One thread of the leader CTA (rank 0) issues
+// tcgen05.mma.cta_group::2 (M=256, N=256, K=8); the tensor cores of both SMs
+// read A from their own shared memory and B from both.  Per CTA a K-block
+// stage is therefore 32 KiB instead of 48 KiB (each B column is fetched by one
+// of the two SMs only), which buys two more ring stages and a third less
+// L2 -> SM traffic.
+//
+// Hand-offs: both CTAs' TMA loads signal the leader's "full" barrier
+// (cp.async.bulk.tensor...cta_group::2 with the barrier address's CTA bit
+// cleared; no multicast load is used); the leader's tcgen05.commit arrives on
+// the "empty" / "accumulator ready" barriers of both CTAs (commit multicast);
+// the peer's drain warps arrive on the leader's "accumulator drained" barrier
+// through its cluster address.  All waits are time-bounded and every thread of
+// both CTAs reaches the two cluster barriers (start, end) unconditionally.
+// ===========================================================================
+namespace {
+
+constexpr int P2_BNH = 128;                                  // B columns held per CTA
+constexpr int P2_B_BYTES = P2_BNH * BK * 4;                  // 8 KiB per plane tile
+constexpr int P2_STAGE_BYTES = 2 * A_BYTES + 2 * P2_B_BYTES; // 32 KiB per CTA
+constexpr int P2_STAGES = 6;
+constexpr uint32_t P2_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(256 >> 3) << 17) |
+                              ((uint32_t)(256 >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tma2_load_2d(uint32_t dst, const CUtensorMap *map,
+                                             uint32_t leader_bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(leader_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(uint32_t dst, const CUtensorMap *map,
+                                             uint32_t leader_bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tc2_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this offset in both CTAs of the pair once all
+// earlier MMAs of this thread have retired.
+__device__ __forceinline__ void tc2_commit_both(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .b16 m;\n\t"
+      "mov.b16 m, 3;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], m;\n\t}" ::"r"(bar)
+      : "memory");
+}
+
+template <bool B_MN>
+__global__ void __launch_bounds__(THREADS, 1)
+tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
+                        const __grid_constant__ CUtensorMap mapAlo,
+                        const __grid_constant__ CUtensorMap mapBhi,
+                        const __grid_constant__ CUtensorMap mapBlo, int64_t M, int64_t N,
+                        int64_t K, float alpha, float beta, float *__restrict__ C, int64_t ldc,
+                        int64_t tiles_m2, int64_t tiles_n, int chunk_kblocks, int32_t *status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * P2_STAGES + 4];
+  __shared__ uint32_t tmem_slot;
+  __shared__ float epi_stage[EPI_WARPS][32][33];
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[P2_STAGES]);
+  const uint32_t accf0 = smem_u32(&bars[2 * P2_STAGES]);
+  const uint32_t acce0 = smem_u32(&bars[2 * P2_STAGES + 2]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int64_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int64_t total = tiles_m2 * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P2_STAGES; s++) {
+      mbar_init(full0 + 8 * s, 1);   // the leader's arrive.expect_tx (bytes of both CTAs)
+      mbar_init(empty0 + 8 * s, 1);  // one commit arrival per CTA
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(accf0 + 8 * b, 1);
+      mbar_init(acce0 + 8 * b, 2 * EPI_WARPS);  // drain warps of both CTAs (leader's copy is used)
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  const int64_t nkb = (K + BK - 1) / BK;
+  const int64_t nchunks = (nkb + chunk_kblocks - 1) / chunk_kblocks;
+  // Pair tiles in bands of 8 pair-rows (16 tile rows), column by column.
+  auto tile_of = [&](int64_t idx, int64_t *tm2, int64_t *tn) {
+    constexpr int64_t G = 8;
+    const int64_t per_group = G * tiles_n;
+    const int64_t grp = idx / per_group;
+    const int64_t first = grp * G;
+    const int64_t rows = (tiles_m2 - first < G) ? (tiles_m2 - first) : G;
+    const int64_t in = idx - grp * per_group;
+    *tm2 = first + in % rows;
+    *tn = in / rows;
+  };
+
+  if (warp < FIRST_EPI_WARP) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0) {
+      // ------------------------------------------------ TMA producer (both CTAs)
+      if (lane == 0) {
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        const uint32_t leader_full0 = map_to_cta(full0, 0);
+        for (int64_t t = pair; t < total && ok; t += npairs) {
+          int64_t tm2, tn;
+          tile_of(t, &tm2, &tn);
+          const int row_a = (int)(tm2 * 256 + rank * 128);
+          const int col_b = (int)(tn * 256 + rank * P2_BNH);
+          for (int64_t kb = 0; kb < nkb; kb++) {
+            if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) {
+              report_status(status, 31, (int32_t)blockIdx.x);
+              ok = false;
+              break;
+            }
+            const uint32_t dst = ring + stage * P2_STAGE_BYTES;
+            if (rank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * P2_STAGE_BYTES);
+            // The same barrier in the leader CTA, as a cluster address.
+            const uint32_t lbar = leader_full0 + 8 * stage;
+            const int k0 = (int)(kb * BK);
+            tma2_load_2d(dst, &mapAhi, lbar, k0, row_a);
+            tma2_load_2d(dst + A_BYTES, &mapAlo, lbar, k0, row_a);
+            if (B_MN) {
+              tma2_load_3d(dst + 2 * A_BYTES, &mapBhi, lbar, 0, k0, col_b / 32);
+              tma2_load_3d(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, 0, k0, col_b / 32);
+            } else {
+              tma2_load_2d(dst + 2 * A_BYTES, &mapBhi, lbar, k0, col_b);
+              tma2_load_2d(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, k0, col_b);
+            }
+            if (++stage == P2_STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+        }
+      }
+    } else if (warp == 1 && rank == 0) {
+      // ------------------------------------------------ MMA issuer (leader only)
+      if (lane == 0) {
+        uint32_t stage = 0, phase = 0;
+        int64_t cc = 0;
+        bool ok = true;
+        for (int64_t t = pair; t < total && ok; t += npairs) {
+          for (int64_t ch = 0; ch < nchunks && ok; ch++, cc++) {
+            const uint32_t buf = (uint32_t)(cc & 1);
+            const uint32_t use = (uint32_t)((cc >> 1) & 1);
+            if (!mbar_wait(acce0 + 8 * buf, use ^ 1)) {
+              report_status(status, 32, (int32_t)blockIdx.x);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + buf * 256;
+            const int64_t kb_end =
+                (ch + 1) * chunk_kblocks < nkb ? (ch + 1) * chunk_kblocks : nkb;
+            for (int64_t kb = ch * chunk_kblocks; kb < kb_end; kb++) {
+              if (!mbar_wait(full0 + 8 * stage, phase)) {
+                report_status(status, 33, (int32_t)blockIdx.x);
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              const uint32_t sa = ring + stage * P2_STAGE_BYTES;
+              const uint64_t ahi = smem_desc_sw64(sa), alo = smem_desc_sw64(sa + A_BYTES);
+              const uint64_t bhi = B_MN ? smem_desc_mn_sw128(sa + 2 * A_BYTES)
+                                        : smem_desc_sw64(sa + 2 * A_BYTES);
+              const uint64_t blo = B_MN ? smem_desc_mn_sw128(sa + 2 * A_BYTES + P2_B_BYTES)
+                                        : smem_desc_sw64(sa + 2 * A_BYTES + P2_B_BYTES);
+              constexpr uint32_t idesc = B_MN ? (P2_IDESC | (1u << 16)) : P2_IDESC;
+              const bool first = (kb == ch * chunk_kblocks);
+#pragma unroll
+              for (int ks = 0; ks < BK / 8; ks++) {
+                const uint64_t ko = (uint64_t)(ks * 2);
+                const uint64_t kob = B_MN ? (uint64_t)(ks * 64) : ko;
+                tc2_mma_tf32(tmem_d, alo + ko, bhi + kob, idesc, (first && ks == 0) ? 0u : 1u);
+                tc2_mma_tf32(tmem_d, ahi + ko, blo + kob, idesc, 1u);
+                tc2_mma_tf32(tmem_d, ahi + ko, bhi + kob, idesc, 1u);
+              }
+              tc2_commit_both(empty0 + 8 * stage);
+              if (++stage == P2_STAGES) {
+                stage = 0;
+                phase ^= 1;
+              }
+            }
+            if (ok) tc2_commit_both(accf0 + 8 * buf);
+          }
+        }
+      }
+    }
+  } else {
+    // --------------------------------------------------- drain warps (both CTAs)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int ew = warp - FIRST_EPI_WARP;
+    const int quarter = warp & 3;
+    const int half = ew >> 2;
+    const uint32_t leader_acce0 = map_to_cta(acce0, 0);
+    int64_t cc = 0;
+    bool ok = true;
+    for (int64_t t = pair; t < total && ok; t += npairs) {
+      int64_t tm2, tn;
+      tile_of(t, &tm2, &tn);
+      const int64_t r_base = tm2 * 256 + rank * 128 + quarter * 32;
+      const int64_t cb = tn * 256 + half * 128;
+      float acc[128];
+#pragma unroll
+      for (int i = 0; i < 128; i++) acc[i] = 0.0f;
+      if (beta != 0.0f && r_base + lane < M) {
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+          if (cb + q * 32 < N)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(C + (r_base + lane) * ldc + cb + q * 32));
+      }
+      for (int64_t ch = 0; ch < nchunks && ok; ch++, cc++) {
+        const uint32_t buf = (uint32_t)(cc & 1);
+        const uint32_t use = (uint32_t)((cc >> 1) & 1);
+        if (!mbar_wait_backoff(accf0 + 8 * buf, use)) {
+          if (lane == 0) report_status(status, 34, (int32_t)blockIdx.x);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr =
+            tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256 + (uint32_t)(half * 128);
+#pragma unroll
+        for (int j = 0; j < 4; j += 2) {
+          uint32_t v0[32], v1[32];
+          tc_ld32(taddr + j * 32, v0);
+          tc_ld32(taddr + j * 32 + 32, v1);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i++) acc[j * 32 + i] += __uint_as_float(v0[i]);
+#pragma unroll
+          for (int i = 0; i < 32; i++) acc[j * 32 + 32 + i] += __uint_as_float(v1[i]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_acce0 + 8 * buf);
+      }
+      if (!ok) break;
+      epilogue_store<128>(acc, epi_stage[ew], lane, r_base, cb, M, N, ldc, C, alpha, beta, false,
+                          0);
+    }
+  }
+
+  // Nobody leaves while the peer may still signal one of its barriers or use
+  // the paired tensor memory.
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+}  // namespace
+
 // Self-test of the bounded-wait machinery: one CTA waits on an mbarrier that
 // nothing ever arrives at, with a caller-chosen cycle limit, and must come back
 // with a status code instead of hanging.
@@ -916,6 +1249,57 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   int64_t ctas = rt->num_sms - (rt->cfg.reserve_sms > 0 ? rt->cfg.reserve_sms : 0);
   if (ctas < 1) ctas = 1;
   const unsigned grid = (unsigned)(tiles.total < ctas ? tiles.total : ctas);
+  // Large full products: the two-CTA kernel (256x256 tiles on SM pairs).
+  // Measured: 2-6 % faster than the one-CTA kernel on products that run for
+  // milliseconds (8192^3: 4.18 vs 4.45 ms), 4-9 % slower on products long
+  // enough to sit at the power cap (16384^3, 32768^3).  reserved[0]: 1 forces
+  // it on, 2 forces it off.
+  const double work = (double)M * (double)N * (double)K;
+  const bool two_cta_ok = !lower && bn == 256 && M >= 512 && (!b_mn || bhi_blocked);
+  const bool two_cta = two_cta_ok && rt->cfg.reserved[0] != 2 &&
+                       (rt->cfg.reserved[0] == 1 || work <= 1.2e12);
+  if (two_cta) {
+    CUtensorMap m2Bhi, m2Blo;
+    if (b_mn) {
+      PGB_TRY(make_nmajor_map_blocked(&m2Bhi, Bhi, K, N, bhi_ld, P2_BNH));
+      PGB_TRY(make_nmajor_map_blocked(&m2Blo, Blo, K, Np, Np, P2_BNH));
+    } else {
+      PGB_TRY(make_plane_map(&m2Bhi, Bhi, N, K, bhi_ld, P2_BNH));
+      PGB_TRY(make_plane_map(&m2Blo, Blo, N, K, Kp, P2_BNH));
+    }
+    const int64_t tiles_m2 = (M + 255) / 256, tiles_n2 = (N + 255) / 256;
+    int64_t pairs = tiles_m2 * tiles_n2;
+    const int64_t max_pairs = ctas / 2 > 0 ? ctas / 2 : 1;
+    if (pairs > max_pairs) pairs = max_pairs;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    lc.blockDim = dim3(THREADS, 1, 1);
+    lc.dynamicSmemBytes = SMEM_BYTES;
+    lc.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    if (b_mn) {
+      PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_2cta_kernel<true>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      PGB_CUDA(cudaLaunchKernelEx(&lc, tf32x3_gemm_2cta_kernel<true>, mAhi, mAlo, m2Bhi, m2Blo, M,
+                                  N, K, alpha, beta, C, ldc, tiles_m2, tiles_n2, chunk,
+                                  rt->status_dev));
+    } else {
+      PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_2cta_kernel<false>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      PGB_CUDA(cudaLaunchKernelEx(&lc, tf32x3_gemm_2cta_kernel<false>, mAhi, mAlo, m2Bhi, m2Blo, M,
+                                  N, K, alpha, beta, C, ldc, tiles_m2, tiles_n2, chunk,
+                                  rt->status_dev));
+    }
+    note_launch(PATH_TCGEN05);
+    PGB_CUDA(cudaGetLastError());
+    return PGB200_OK;
+  }
   auto launch = [&](auto kernel, int bhi_blk) -> int32_t {
     PGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     kernel<<<grid, THREADS, SMEM_BYTES, s>>>(mAhi, mAlo, mBhi, mBlo, M, N, K, alpha, beta, C, ldc,
