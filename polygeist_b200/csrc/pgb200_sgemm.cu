@@ -280,12 +280,13 @@ struct Tiles {
   int64_t row0;  // absolute row of local row 0 (lower only)
   int lower;
   int bn;        // tile width in columns (256, or 64 for problems with few tiles)
+  int bm;        // tile height in rows (128; 256 for the two-CTA kernel's pair tiles)
 };
 
 // Columns tiles of tile-row tm that intersect j <= i (lower) or all of them.
 __device__ __forceinline__ int64_t row_tiles(const Tiles &t, int64_t tm) {
   if (!t.lower) return t.tiles_n;
-  const int64_t last_col = t.row0 + tm * BM + BM - 1;  // largest j of the tile row
+  const int64_t last_col = t.row0 + tm * t.bm + t.bm - 1;  // largest j of the tile row
   const int64_t c = last_col / t.bn + 1;
   return c < t.tiles_n ? c : t.tiles_n;
 }
@@ -325,8 +326,8 @@ struct TileCursor {
     int64_t in = idx - before;
     for (int64_t tn = 0;; tn++) {
       // Smallest tile row whose last matrix row reaches column tile tn.
-      int64_t need = tn * t.bn - t.row0 - (BM - 1);
-      int64_t lo = need <= 0 ? 0 : (need + BM - 1) / BM;
+      int64_t need = tn * t.bn - t.row0 - (t.bm - 1);
+      int64_t lo = need <= 0 ? 0 : (need + t.bm - 1) / t.bm;
       if (lo < first) lo = first;
       const int64_t c = last - lo + 1;
       if (c > 0) {
@@ -847,7 +848,7 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
                         const __grid_constant__ CUtensorMap mapBhi,
                         const __grid_constant__ CUtensorMap mapBlo, int64_t M, int64_t N,
                         int64_t K, float alpha, float beta, float *__restrict__ C, int64_t ldc,
-                        int64_t tiles_m2, int64_t tiles_n, int chunk_kblocks, int32_t *status) {
+                        Tiles tiles, int chunk_kblocks, int32_t *status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * P2_STAGES + 4];
   __shared__ uint32_t tmem_slot;
@@ -859,7 +860,7 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int64_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-  const int64_t total = tiles_m2 * tiles_n;
+  const int64_t total = tiles.total;  // pair tiles of 256 x 256 (tiles.bm == tiles.bn == 256)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P2_STAGES; s++) {
@@ -886,18 +887,6 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
 
   const int64_t nkb = (K + BK - 1) / BK;
   const int64_t nchunks = (nkb + chunk_kblocks - 1) / chunk_kblocks;
-  // Pair tiles in bands of 8 pair-rows (16 tile rows), column by column.
-  auto tile_of = [&](int64_t idx, int64_t *tm2, int64_t *tn) {
-    constexpr int64_t G = 8;
-    const int64_t per_group = G * tiles_n;
-    const int64_t grp = idx / per_group;
-    const int64_t first = grp * G;
-    const int64_t rows = (tiles_m2 - first < G) ? (tiles_m2 - first) : G;
-    const int64_t in = idx - grp * per_group;
-    *tm2 = first + in % rows;
-    *tn = in / rows;
-  };
-
   if (warp < FIRST_EPI_WARP) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
@@ -906,9 +895,10 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         const uint32_t leader_full0 = map_to_cta(full0, 0);
+        TileCursor cur;
         for (int64_t t = pair; t < total && ok; t += npairs) {
           int64_t tm2, tn;
-          tile_of(t, &tm2, &tn);
+          cur.seek(tiles, t, &tm2, &tn);
           const int row_a = (int)(tm2 * 256 + rank * 128);
           const int col_b = (int)(tn * 256 + rank * P2_BNH);
           for (int64_t kb = 0; kb < nkb; kb++) {
@@ -998,11 +988,12 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
     const int quarter = warp & 3;
     const int half = ew >> 2;
     const uint32_t leader_acce0 = map_to_cta(acce0, 0);
+    TileCursor cur;
     int64_t cc = 0;
     bool ok = true;
     for (int64_t t = pair; t < total && ok; t += npairs) {
       int64_t tm2, tn;
-      tile_of(t, &tm2, &tn);
+      cur.seek(tiles, t, &tm2, &tn);
       const int64_t r_base = tm2 * 256 + rank * 128 + quarter * 32;
       const int64_t cb = tn * 256 + half * 128;
       float acc[128];
@@ -1041,8 +1032,8 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
         if (lane == 0) mbar_arrive_cluster(leader_acce0 + 8 * buf);
       }
       if (!ok) break;
-      epilogue_store<128>(acc, epi_stage[ew], lane, r_base, cb, M, N, ldc, C, alpha, beta, false,
-                          0);
+      epilogue_store<128>(acc, epi_stage[ew], lane, r_base, cb, M, N, ldc, C, alpha, beta,
+                          tiles.lower != 0, tiles.row0);
     }
   }
 
@@ -1233,6 +1224,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   tiles.tiles_m = (M + BM - 1) / BM;
   tiles.tiles_n = (N + bn - 1) / bn;
   tiles.bn = bn;
+  tiles.bm = BM;
   tiles.row0 = row0;
   tiles.lower = lower ? 1 : 0;
   if (lower) {
@@ -1254,8 +1246,8 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   // milliseconds (8192^3: 4.18 vs 4.45 ms), 4-9 % slower on products long
   // enough to sit at the power cap (16384^3, 32768^3).  reserved[0]: 1 forces
   // it on, 2 forces it off.
-  const double work = (double)M * (double)N * (double)K;
-  const bool two_cta_ok = !lower && bn == 256 && M >= 512 && (!b_mn || bhi_blocked);
+  const double work = (double)M * (double)N * (double)K * (lower ? 0.5 : 1.0);
+  const bool two_cta_ok = bn == 256 && M >= 512 && (!b_mn || bhi_blocked);
   const bool two_cta = two_cta_ok && rt->cfg.reserved[0] != 2 &&
                        (rt->cfg.reserved[0] == 1 || work <= 1.2e12);
   if (two_cta) {
@@ -1267,8 +1259,22 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
       PGB_TRY(make_plane_map(&m2Bhi, Bhi, N, K, bhi_ld, P2_BNH));
       PGB_TRY(make_plane_map(&m2Blo, Blo, N, K, Kp, P2_BNH));
     }
-    const int64_t tiles_m2 = (M + 255) / 256, tiles_n2 = (N + 255) / 256;
-    int64_t pairs = tiles_m2 * tiles_n2;
+    Tiles t2 = tiles;
+    t2.bm = 256;
+    t2.bn = 256;
+    t2.tiles_m = (M + 255) / 256;
+    t2.tiles_n = (N + 255) / 256;
+    if (lower) {
+      int64_t tot = 0;
+      for (int64_t tm = 0; tm < t2.tiles_m; tm++) {
+        const int64_t c = (row0 + tm * 256 + 255) / 256 + 1;
+        tot += c < t2.tiles_n ? c : t2.tiles_n;
+      }
+      t2.total = tot;
+    } else {
+      t2.total = t2.tiles_m * t2.tiles_n;
+    }
+    int64_t pairs = t2.total;
     const int64_t max_pairs = ctas / 2 > 0 ? ctas / 2 : 1;
     if (pairs > max_pairs) pairs = max_pairs;
     cudaLaunchConfig_t lc = {};
@@ -1287,14 +1293,12 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
       PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_2cta_kernel<true>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
       PGB_CUDA(cudaLaunchKernelEx(&lc, tf32x3_gemm_2cta_kernel<true>, mAhi, mAlo, m2Bhi, m2Blo, M,
-                                  N, K, alpha, beta, C, ldc, tiles_m2, tiles_n2, chunk,
-                                  rt->status_dev));
+                                  N, K, alpha, beta, C, ldc, t2, chunk, rt->status_dev));
     } else {
       PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_2cta_kernel<false>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
       PGB_CUDA(cudaLaunchKernelEx(&lc, tf32x3_gemm_2cta_kernel<false>, mAhi, mAlo, m2Bhi, m2Blo, M,
-                                  N, K, alpha, beta, C, ldc, tiles_m2, tiles_n2, chunk,
-                                  rt->status_dev));
+                                  N, K, alpha, beta, C, ldc, t2, chunk, rt->status_dev));
     }
     note_launch(PATH_TCGEN05);
     PGB_CUDA(cudaGetLastError());

@@ -265,17 +265,25 @@ def test_ssyrk_matches_oracle(n, k):
     assert np.array_equal(got[iu], C0[iu])
 
 
-def test_ssyrk_row_block_equals_rows_of_full_update():
-    n, k = 384, 128
+@pytest.mark.parametrize("n,k,blocks", [
+    (384, 128, [(0, 100), (100, 256), (256, 384)]),            # one-CTA kernel, 128x64 tiles
+    (2048, 256, [(0, 640), (640, 1408), (1408, 2048)]),        # two-CTA kernel, row0 != 0
+])
+def test_ssyrk_row_block_equals_rows_of_full_update(n, k, blocks):
     A = dev_fill(n, k, torch.float32, 1, 0.0, 1.0)
     C1 = dev_fill(n, n, torch.float32, 2, 0.0, 1.0)
     C2 = C1.clone()
+    C0 = C1.clone()
     pgb.syrk(1.5, A, 1.2, C1)
-    for r0, r1 in [(0, 100), (100, 256), (256, 384)]:
+    for r0, r1 in blocks:
         pgb.syrk(1.5, A, 1.2, C2, rows=(r0, r1))
     sync_ok()
     il = np.tril_indices(n)
     assert elementwise_rel(C2.cpu().numpy()[il], C1.cpu().numpy()[il]) <= 1e-6
+    truth = 1.5 * (A.double() @ A.double().T) + 1.2 * C0.double()
+    assert elementwise_rel(C1.cpu().numpy()[il], truth.cpu().numpy()[il]) <= 1e-5
+    iu = np.triu_indices(n, 1)
+    assert np.array_equal(C2.cpu().numpy()[iu], C0.cpu().numpy()[iu])
 
 
 def test_ssyrk_config4_full_size():
