@@ -56,9 +56,9 @@ typedef struct pgb200Config {
   int32_t reserve_sms;        /* SMs the persistent GEMM kernels leave free, so
                                  that a concurrent collective (NCCL broadcast
                                  of the next operand chunk) can run beside them */
-  int32_t reserved[3];        /* [0]: two-CTA (cta_group::2) fp32 kernel - 0 auto
-                                 (mid-size full products), 1 always when
-                                 possible, 2 never                            */
+  int32_t reserved[3];        /* [0] == 2: never use the two-CTA (cta_group::2)
+                                 fp32 kernel (default: whenever a product has
+                                 >= 512 rows and enough tiles)               */
 } pgb200Config;
 
 /* Runtime life cycle.  Replaces nothing in the reference one-to-one; plays the

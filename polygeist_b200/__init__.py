@@ -111,9 +111,10 @@ def check(status):
 
 
 def init(log_level=0, sgemm_chunk_kblocks=0, force_generic=0, sgemm_planes_only=0, reserve_sms=0,
-         sgemm_two_cta=0):
+         sgemm_two_cta=0, sgemm_b_in_place=0):
     cfg = Config(log_level, sgemm_chunk_kblocks, force_generic, sgemm_planes_only, reserve_sms)
     cfg.reserved[0] = sgemm_two_cta
+    cfg.reserved[1] = sgemm_b_in_place
     check(load().pgb200Init(C.byref(cfg)))
 
 

@@ -757,7 +757,8 @@ __global__ void __launch_bounds__(128, 1) tf32_probe_kernel(int iters, int32_t *
 }  // namespace
 
 // ===========================================================================
-// Two-CTA variant (cta_group::2) of the same pipeline for large full products.
+// Two-CTA variant (cta_group::2) of the same pipeline: every product with at
+// least 512 rows and enough 128x256 tiles to fill the GPU.
 //
 // A cluster of two CTAs on an SM pair shares one 256x256 output tile: CTA r
 // holds rows [128r, 128r+128) of the tile's A panel and columns
@@ -1128,7 +1129,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   // layout several percent slower (measured: 398 vs 372 ms at 32768^3).  The
   // pre-pass is paid once per call, the slowdown per row of A: for tall
   // products transpose B once, otherwise use it in place.
-  const bool b_mn = !transB && b_raw && M < 12288;
+  const bool b_mn = !transB && b_raw && (M < 12288 || rt->cfg.reserved[1] == 1);
 
   // Scratch layout (floats): [B lo][B hi?][A lo?][A hi?]
   const size_t b_lo_n = b_mn ? (size_t)K * Np : (size_t)N * Kp;
@@ -1242,14 +1243,10 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   if (ctas < 1) ctas = 1;
   const unsigned grid = (unsigned)(tiles.total < ctas ? tiles.total : ctas);
   // Large full products: the two-CTA kernel (256x256 tiles on SM pairs).
-  // Measured: 2-6 % faster than the one-CTA kernel on products that run for
-  // milliseconds (8192^3: 4.18 vs 4.45 ms), 4-9 % slower on products long
-  // enough to sit at the power cap (16384^3, 32768^3).  reserved[0]: 1 forces
-  // it on, 2 forces it off.
-  const double work = (double)M * (double)N * (double)K * (lower ? 0.5 : 1.0);
-  const bool two_cta_ok = bn == 256 && M >= 512 && (!b_mn || bhi_blocked);
-  const bool two_cta = two_cta_ok && rt->cfg.reserved[0] != 2 &&
-                       (rt->cfg.reserved[0] == 1 || work <= 1.2e12);
+  // Measured against the one-CTA kernel: 8192^3 4.01-4.18 vs 4.45 ms, 16384^3
+  // 36.7-38.1 vs 40.5-40.8 ms, 32768^3 354-356 vs 423-443 ms (same GPU, back to
+  // back).  reserved[0] == 2 switches it off.
+  const bool two_cta = bn == 256 && M >= 512 && (!b_mn || bhi_blocked) && rt->cfg.reserved[0] != 2;
   if (two_cta) {
     CUtensorMap m2Bhi, m2Blo;
     if (b_mn) {
