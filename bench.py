@@ -33,7 +33,7 @@ ALPHA, BETA = 1.5, 1.2
 
 # DRAM bytes (read + write) per launch of the dominant kernel from the ncu
 # captures summarised under profiles/ (mvt32768: the N=16384 capture x 4).
-TRAFFIC = {"dgemm4096": 1.1345e9, "mvt16384": 2.156e9, "mvt32768": 8.624e9, "sgemm4096": 7.64e8}
+TRAFFIC = {"dgemm4096": 1.1345e9, "mvt16384": 2.156e9, "mvt32768": 8.624e9, "sgemm4096": 8.31e8}
 
 WORKLOADS = {
     # name: (metric, unit, dtype, description)
@@ -489,19 +489,32 @@ def run_pgb200(args, w, name):
             # 3xTF32: every useful FMA costs three tensor-core FMAs, so the
             # tensor pipe does 3 * 2MNK flop per step; compare with dense TF32.
             peak_hot = pgb.probe_peak(pgb.PEAK_TF32) / 1e3
-            # A step that runs for seconds settles at the power-capped clock:
-            # judge it against the probe taken in that state; short steps
-            # against the burst figure.
-            long_run = ms_per_step * args.steps > 1000.0
-            peak = peak_hot if long_run else max(peak_cold, peak_hot)
+            burst = max(peak_cold, peak_hot)
+            # A kernel timed alone is judged against the burst figure.  A step that
+            # runs for >= 100 ms sits at the 1 kW power cap; MEASURED_PEAKS.json has
+            # the driver's own burst and sustained numbers for a tensor-core GEMM
+            # (bf16), and their ratio is applied to the TF32 burst probe.  (The
+            # issue-loop probe run right after a long step is NOT an upper bound:
+            # the two-CTA GEMM is more power-efficient than the probe and beats it.)
+            derate = 1.0
+            long_run = ms_per_step >= 100.0
+            try:
+                mp = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+                if long_run:
+                    derate = mp["bf16_tflops_sustained"] / mp["bf16_tflops"]
+            except (OSError, KeyError):
+                if long_run:
+                    derate = 1.4 / 1.59  # fallback ratio of the profiling recipe
+            peak = burst * derate
             ach = 3 * (units / world if strong else units) / (ms_per_step * 1e-3) / 1e12
             roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                     "frac": ach / peak, "traffic": TRAFFIC.get(name),
-                    "peak_burst": peak_cold, "peak_after_run": peak_hot,
+                    "peak_burst": burst, "peak_after_run": peak_hot,
                     "peak_source": "dense TF32 tcgen05.mma issue-rate probe of this library "
                                    "(MEASURED_PEAKS.json has no TF32 figure): "
-                                   + ("sustained (after the timed region)" if long_run else
-                                      "burst (max of before/after)")
+                                   + (f"burst x {derate:.3f} (sustained/burst ratio of the measured "
+                                      "bf16 GEMM) for this long, power-capped step" if long_run
+                                      else "burst (max of before/after the timed region)")
                                    + "; achieved counts the 3 tensor products per useful product"}
 
     # ---- end to end through the reference-facing drop-in, host arrays ----
