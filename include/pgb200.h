@@ -129,6 +129,25 @@ int32_t pgb200SsyrkRows(void *stream, int64_t N, int64_t K, int64_t row0,
                         int64_t row1, float alpha, const float *A, int64_t lda,
                         float beta, float *C, int64_t ldc);
 
+/* The same GEMM / rank-k update on `ndev` GPUs of one box (devices 0..ndev-1)
+ * from a single host thread: the rows of the output are partitioned across the
+ * GPUs (equal heights for the GEMM, equal triangular areas for the update) and
+ * the shared operand is broadcast from device 0 by NCCL in K-slices, each
+ * slice's product running while the next slice travels.  Arrays are host
+ * memory or memory of device 0; the call returns when the result is back in
+ * C.  NCCL is loaded at run time (libnccl.so.2); ndev == 1 makes no NCCL call.
+ * The reference has no multi-GPU path: the nests are those of gemm.c:104-113 and
+ * syrk.c:97-106, whose rows are independent. */
+int32_t pgb200DgemmMg(int32_t ndev, int64_t M, int64_t N, int64_t K, double alpha,
+                      const double *A, int64_t lda, const double *B, int64_t ldb,
+                      double beta, double *C, int64_t ldc);
+int32_t pgb200SgemmMg(int32_t ndev, int64_t M, int64_t N, int64_t K, float alpha,
+                      const float *A, int64_t lda, const float *B, int64_t ldb,
+                      float beta, float *C, int64_t ldc);
+int32_t pgb200SsyrkMg(int32_t ndev, int64_t N, int64_t K, float alpha,
+                      const float *A, int64_t lda, float beta, float *C,
+                      int64_t ldc);
+
 /* y[.] = alpha * op(A) * x + beta * y with A[MxN] row-major;
  * transA == 0: op(A) = A (y has M entries), transA != 0: op(A) = A^T (y has N).
  * Replaces either nest of kernel_mvt taken alone,

@@ -52,6 +52,9 @@ SIGNATURES = {
     "pgb200SgemmNT": (_i32, [_vp, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64, _f32, _vp, _i64]),
     "pgb200Dsyr2k": (_i32, [_vp, _i64, _i64, _f64, _vp, _i64, _vp, _i64, _f64, _vp, _i64]),
     "pgb200Ssyr2k": (_i32, [_vp, _i64, _i64, _f32, _vp, _i64, _vp, _i64, _f32, _vp, _i64]),
+    "pgb200DgemmMg": (_i32, [_i32, _i64, _i64, _i64, _f64, _vp, _i64, _vp, _i64, _f64, _vp, _i64]),
+    "pgb200SgemmMg": (_i32, [_i32, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64, _f32, _vp, _i64]),
+    "pgb200SsyrkMg": (_i32, [_i32, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
     "pgb200Dsyrk": (_i32, [_vp, _i64, _i64, _f64, _vp, _i64, _f64, _vp, _i64]),
     "pgb200Ssyrk": (_i32, [_vp, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
     "pgb200SsyrkRows": (_i32, [_vp, _i64, _i64, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
@@ -231,6 +234,23 @@ def syrk_rows(alpha, A, beta, C_block, r0, r1, stream=None):
     s = _stream(stream) if stream is not None else current_stream_for(A, C_block)
     check(load().pgb200SsyrkRows(s, N, K, r0, r1, alpha, _ptr(A), _ld(A), beta, base, ldc))
     return C_block
+
+
+def gemm_mg(ndev, alpha, A, B, beta, Cm):
+    """Cm = alpha*A@B + beta*Cm on `ndev` GPUs from this one process (host arrays
+    or tensors of device 0); returns when Cm holds the result."""
+    M, K = A.shape
+    N = B.shape[1]
+    fn = load().pgb200DgemmMg if _is_f64(Cm) else load().pgb200SgemmMg
+    check(fn(ndev, M, N, K, alpha, _ptr(A), _ld(A), _ptr(B), _ld(B), beta, _ptr(Cm), _ld(Cm)))
+    return Cm
+
+
+def syrk_mg(ndev, alpha, A, beta, Cm):
+    """Lower triangle of Cm = alpha*A@A^T + beta*Cm on `ndev` GPUs (fp32)."""
+    N, K = A.shape
+    check(load().pgb200SsyrkMg(ndev, N, K, alpha, _ptr(A), _ld(A), beta, _ptr(Cm), _ld(Cm)))
+    return Cm
 
 
 def gemv(trans, alpha, A, x, beta, y, stream=None):

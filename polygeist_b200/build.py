@@ -49,7 +49,7 @@ def build(force=False, verbose=False):
                 if r.returncode:
                     raise RuntimeError("nvcc failed: " + " ".join(r.args))
     if jobs or force or _stale(LIB, objs):
-        cmd = [NVCC, "-shared", "-o", LIB, *objs]
+        cmd = [NVCC, "-shared", "-o", LIB, *objs, "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)

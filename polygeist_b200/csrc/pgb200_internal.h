@@ -114,6 +114,14 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
                     const float *A, int64_t lda, const float *B, int64_t ldb, bool transB,
                     float beta, float *C, int64_t ldc, bool lower, int64_t row0);
 
+// Device-pointer GEMM core on the current device: picks the tensor-core path,
+// falls back to the SIMT kernels.  C[MxN] = alpha*A*op(B) + beta*C; `lower` and
+// `row0` as in simt_gemm.
+template <typename T>
+int32_t gemm_device(cudaStream_t s, int64_t M, int64_t N, int64_t K, T alpha, const T *A,
+                    int64_t lda, const T *B, int64_t ldb, bool transB, T beta, T *C, int64_t ldc,
+                    bool lower, int64_t row0);
+
 // kind::tf32 tensor-pipe issue-rate probe (dense GFLOP/s).
 int32_t tf32_peak_probe(cudaStream_t s, double *gflops);
 

@@ -1,0 +1,361 @@
+// Single-process multi-GPU entry points: one host thread drives the GPUs of one
+// box, the output rows are partitioned across them and the shared operand is
+// broadcast by NCCL over NVLink in K-slices, each slice's product (or rank-k
+// update) running while the next slice is in flight.  The reference has no
+// multi-GPU path; the split is exact because the rows of every nest are
+// independent (gemm.c:104-113, syrk.c:97-106).
+//
+// NCCL is bound at run time (dlopen of libnccl.so.2), so the library itself has
+// no link-time dependency on it; with one device no NCCL call is made at all.
+#include <dlfcn.h>
+#include <math.h>
+#include <nccl.h>
+
+#include <mutex>
+#include <vector>
+
+#include "pgb200_internal.h"
+
+namespace pgb200 {
+namespace {
+
+struct NcclApi {
+  ncclResult_t (*CommInitAll)(ncclComm_t *, int, const int *) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t,
+                            cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
+  const char *(*GetErrorString)(ncclResult_t) = nullptr;
+  bool ok = false;
+};
+
+struct MgState {
+  int ndev = 0;
+  std::vector<ncclComm_t> comm;
+  std::vector<cudaStream_t> compute, link;
+};
+
+std::mutex g_mg_mu;
+NcclApi g_nccl;
+MgState g_mg;
+
+int32_t load_nccl() {
+  if (g_nccl.ok) return PGB200_OK;
+  void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) {
+    set_error("multi-GPU entry: cannot load libnccl.so.2 (%s)", dlerror());
+    return PGB200_ERR_NCCL;
+  }
+  g_nccl.CommInitAll = (decltype(g_nccl.CommInitAll))dlsym(h, "ncclCommInitAll");
+  g_nccl.CommDestroy = (decltype(g_nccl.CommDestroy))dlsym(h, "ncclCommDestroy");
+  g_nccl.Broadcast = (decltype(g_nccl.Broadcast))dlsym(h, "ncclBroadcast");
+  g_nccl.GroupStart = (decltype(g_nccl.GroupStart))dlsym(h, "ncclGroupStart");
+  g_nccl.GroupEnd = (decltype(g_nccl.GroupEnd))dlsym(h, "ncclGroupEnd");
+  g_nccl.GetErrorString = (decltype(g_nccl.GetErrorString))dlsym(h, "ncclGetErrorString");
+  if (!g_nccl.CommInitAll || !g_nccl.CommDestroy || !g_nccl.Broadcast || !g_nccl.GroupStart ||
+      !g_nccl.GroupEnd || !g_nccl.GetErrorString) {
+    set_error("multi-GPU entry: libnccl.so.2 lacks a required symbol");
+    return PGB200_ERR_NCCL;
+  }
+  g_nccl.ok = true;
+  return PGB200_OK;
+}
+
+#define PGB_NCCL(expr)                                                             \
+  do {                                                                             \
+    ncclResult_t r__ = (expr);                                                     \
+    if (r__ != ncclSuccess) {                                                      \
+      set_error("'%s' failed with '%s'", #expr, g_nccl.GetErrorString(r__));       \
+      return PGB200_ERR_NCCL;                                                      \
+    }                                                                              \
+  } while (0)
+
+// Streams and (for ndev > 1) communicators for devices 0..ndev-1, created once.
+int32_t mg_state(int ndev, MgState **out) {
+  if (g_mg.ndev == ndev) {
+    *out = &g_mg;
+    return PGB200_OK;
+  }
+  int count = 0;
+  PGB_CUDA(cudaGetDeviceCount(&count));
+  PGB_REQUIRE(ndev >= 1 && ndev <= count, "multi-GPU entry: ndev = %d but %d device(s) visible",
+              ndev, count);
+  if (g_mg.ndev != 0) {  // different device count than last time: rebuild
+    for (int d = 0; d < g_mg.ndev; d++) {
+      cudaSetDevice(d);
+      if (!g_mg.comm.empty()) g_nccl.CommDestroy(g_mg.comm[d]);
+      cudaStreamDestroy(g_mg.compute[d]);
+      cudaStreamDestroy(g_mg.link[d]);
+    }
+    g_mg = MgState();
+  }
+  MgState st;
+  st.compute.resize(ndev);
+  st.link.resize(ndev);
+  for (int d = 0; d < ndev; d++) {
+    PGB_CUDA(cudaSetDevice(d));
+    Runtime *rt = nullptr;
+    PGB_TRY(get_runtime(&rt));
+    PGB_CUDA(cudaStreamCreateWithFlags(&st.compute[d], cudaStreamNonBlocking));
+    PGB_CUDA(cudaStreamCreateWithFlags(&st.link[d], cudaStreamNonBlocking));
+  }
+  if (ndev > 1) {
+    PGB_TRY(load_nccl());
+    st.comm.resize(ndev);
+    std::vector<int> devs(ndev);
+    for (int d = 0; d < ndev; d++) devs[d] = d;
+    PGB_NCCL(g_nccl.CommInitAll(st.comm.data(), ndev, devs.data()));
+  }
+  st.ndev = ndev;
+  g_mg = st;
+  *out = &g_mg;
+  return PGB200_OK;
+}
+
+template <typename T>
+ncclDataType_t nccl_type();
+template <>
+ncclDataType_t nccl_type<float>() { return ncclFloat; }
+template <>
+ncclDataType_t nccl_type<double>() { return ncclDouble; }
+
+int64_t round_to(int64_t x, int64_t a) { return (x + a / 2) / a * a; }
+
+// Broadcast rows [0, rows) x `pitch` elements of `bufs[d]` from device 0 to all.
+template <typename T>
+int32_t bcast(MgState *st, std::vector<T *> &bufs, size_t offset, size_t count) {
+  PGB_NCCL(g_nccl.GroupStart());
+  for (int d = 0; d < st->ndev; d++)
+    PGB_NCCL(g_nccl.Broadcast(bufs[0] + offset, bufs[d] + offset, count, nccl_type<T>(), 0,
+                              st->comm[d], st->link[d]));
+  PGB_NCCL(g_nccl.GroupEnd());
+  return PGB200_OK;
+}
+
+// C = alpha*A*B + beta*C, rows of A and C split over ndev GPUs, B broadcast in
+// K-slices from device 0.  Arrays may be host memory or memory of device 0.
+template <typename T>
+int32_t gemm_mg(int ndev, int64_t M, int64_t N, int64_t K, T alpha, const T *A, int64_t lda,
+                const T *B, int64_t ldb, T beta, T *C, int64_t ldc) {
+  PGB_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm (multi-GPU): negative size");
+  if (M == 0 || N == 0) return PGB200_OK;
+  PGB_REQUIRE(C && ldc >= N && (K == 0 || (A && B && lda >= K && ldb >= N)),
+              "gemm (multi-GPU): null pointer or leading dimension too small");
+  std::lock_guard<std::mutex> lk(g_mg_mu);
+  int entry_dev = 0;
+  PGB_CUDA(cudaGetDevice(&entry_dev));
+  MgState *st = nullptr;
+  PGB_TRY(mg_state(ndev, &st));
+  const int64_t per16 = 16 / (int64_t)sizeof(T);
+  const int64_t pA = (K + per16 - 1) / per16 * per16, pB = (N + per16 - 1) / per16 * per16;
+  const int64_t pC = pB;
+  std::vector<int64_t> b(ndev + 1, 0);
+  for (int d = 1; d < ndev; d++) {
+    int64_t x = round_to(M * d / ndev, 128);
+    if (x > M) x = M;
+    b[d] = x < b[d - 1] ? b[d - 1] : x;
+  }
+  b[ndev] = M;
+  const int nslice = (ndev > 1 && K >= 2048) ? 8 : 1;
+  std::vector<T *> dA(ndev, nullptr), dB(ndev, nullptr), dC(ndev, nullptr);
+  std::vector<std::vector<cudaEvent_t>> ev(ndev);
+  int32_t status = PGB200_OK;
+  // Stage: every device takes its rows of A and C; device 0 takes B.
+  for (int d = 0; d < ndev; d++) {
+    PGB_CUDA(cudaSetDevice(d));
+    const int64_t rows = b[d + 1] - b[d];
+    cudaStream_t cs = st->compute[d];
+    PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dB[d]), (size_t)(K > 0 ? K : 1) * pB * sizeof(T), st->link[d]));
+    if (rows > 0) {
+      PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dA[d]), (size_t)rows * pA * sizeof(T), cs));
+      PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dC[d]), (size_t)rows * pC * sizeof(T), cs));
+      if (K > 0)
+        PGB_CUDA(cudaMemcpy2DAsync(dA[d], pA * sizeof(T), A + b[d] * lda, lda * sizeof(T),
+                                   K * sizeof(T), rows, cudaMemcpyDefault, cs));
+      if (beta != (T)0)
+        PGB_CUDA(cudaMemcpy2DAsync(dC[d], pC * sizeof(T), C + b[d] * ldc, ldc * sizeof(T),
+                                   N * sizeof(T), rows, cudaMemcpyDefault, cs));
+    }
+    ev[d].resize(nslice);
+    for (int c = 0; c < nslice; c++)
+      PGB_CUDA(cudaEventCreateWithFlags(&ev[d][c], cudaEventDisableTiming));
+  }
+  PGB_CUDA(cudaSetDevice(0));
+  if (K > 0)
+    PGB_CUDA(cudaMemcpy2DAsync(dB[0], pB * sizeof(T), B, ldb * sizeof(T), N * sizeof(T), K,
+                               cudaMemcpyDefault, st->link[0]));
+  // The receive buffers must exist before device 0 starts sending into them.
+  for (int d = 0; d < ndev; d++) {
+    PGB_CUDA(cudaSetDevice(d));
+    PGB_CUDA(cudaStreamSynchronize(st->link[d]));
+  }
+  // K-slices: broadcast slice c (all of them queued up front on the link
+  // streams), multiply slice c as soon as it has landed.
+  std::vector<int64_t> kb(nslice + 1, 0);
+  for (int c = 1; c < nslice; c++) kb[c] = round_to(K * c / nslice, 16);
+  kb[nslice] = K;
+  for (int c = 0; c < nslice && status == PGB200_OK; c++) {
+    if (ndev > 1 && kb[c + 1] > kb[c])
+      status = bcast<T>(st, dB, (size_t)kb[c] * pB, (size_t)(kb[c + 1] - kb[c]) * pB);
+    for (int d = 0; d < ndev; d++) {
+      PGB_CUDA(cudaSetDevice(d));
+      PGB_CUDA(cudaEventRecord(ev[d][c], st->link[d]));
+    }
+  }
+  for (int c = 0; c < nslice && status == PGB200_OK; c++) {
+    for (int d = 0; d < ndev && status == PGB200_OK; d++) {
+      const int64_t rows = b[d + 1] - b[d];
+      if (rows == 0) continue;
+      PGB_CUDA(cudaSetDevice(d));
+      PGB_CUDA(cudaStreamWaitEvent(st->compute[d], ev[d][c], 0));
+      if (kb[c + 1] == kb[c] && !(c == 0 && K == 0)) continue;
+      status = gemm_device<T>(st->compute[d], rows, N, kb[c + 1] - kb[c], alpha, dA[d] + kb[c], pA,
+                              dB[d] + kb[c] * pB, pB, false, c == 0 ? beta : (T)1, dC[d], pC,
+                              false, 0);
+    }
+  }
+  for (int d = 0; d < ndev; d++) {
+    PGB_CUDA(cudaSetDevice(d));
+    const int64_t rows = b[d + 1] - b[d];
+    if (rows > 0 && status == PGB200_OK)
+      PGB_CUDA(cudaMemcpy2DAsync(C + b[d] * ldc, ldc * sizeof(T), dC[d], pC * sizeof(T),
+                                 N * sizeof(T), rows, cudaMemcpyDefault, st->compute[d]));
+  }
+  for (int d = 0; d < ndev; d++) {
+    PGB_CUDA(cudaSetDevice(d));
+    PGB_CUDA(cudaStreamSynchronize(st->compute[d]));
+    PGB_CUDA(cudaStreamSynchronize(st->link[d]));
+    if (dA[d]) PGB_CUDA(cudaFreeAsync(dA[d], st->compute[d]));
+    if (dC[d]) PGB_CUDA(cudaFreeAsync(dC[d], st->compute[d]));
+    PGB_CUDA(cudaFreeAsync(dB[d], st->compute[d]));
+    for (auto e : ev[d]) cudaEventDestroy(e);
+    PGB_CUDA(cudaStreamSynchronize(st->compute[d]));
+  }
+  PGB_CUDA(cudaSetDevice(entry_dev));
+  return status;
+}
+
+// Lower triangle of C = alpha*A*A^T + beta*C, rows split by equal triangular
+// area; A is broadcast as packed K-slices (columns [k0,k1) of all rows).
+int32_t ssyrk_mg(int ndev, int64_t N, int64_t K, float alpha, const float *A, int64_t lda,
+                 float beta, float *C, int64_t ldc) {
+  PGB_REQUIRE(N >= 0 && K >= 0, "syrk (multi-GPU): negative size");
+  if (N == 0) return PGB200_OK;
+  PGB_REQUIRE(C && ldc >= N && (K == 0 || (A && lda >= K)),
+              "syrk (multi-GPU): null pointer or leading dimension too small");
+  std::lock_guard<std::mutex> lk(g_mg_mu);
+  int entry_dev = 0;
+  PGB_CUDA(cudaGetDevice(&entry_dev));
+  MgState *st = nullptr;
+  PGB_TRY(mg_state(ndev, &st));
+  std::vector<int64_t> b(ndev + 1, 0);
+  for (int d = 1; d < ndev; d++) {
+    int64_t x = round_to((int64_t)llround((double)N * sqrt((double)d / ndev)), 128);
+    if (x > N) x = N;
+    b[d] = x < b[d - 1] ? b[d - 1] : x;
+  }
+  b[ndev] = N;
+  const int nslice = (K >= 2048) ? 4 : 1;
+  std::vector<int64_t> kb(nslice + 1, 0);
+  for (int c = 1; c < nslice; c++) kb[c] = round_to(K * c / nslice, 16);
+  kb[nslice] = K;
+  const int64_t pC = (N + 3) / 4 * 4;
+  std::vector<float *> dP(ndev, nullptr), dC(ndev, nullptr);
+  std::vector<std::vector<cudaEvent_t>> ev(ndev);
+  // Packed slices: slice c holds columns [kb[c],kb[c+1]) of all N rows, pitch wc.
+  std::vector<size_t> off(nslice + 1, 0);
+  for (int c = 0; c < nslice; c++) {
+    const int64_t wc = (kb[c + 1] - kb[c] + 3) / 4 * 4;
+    off[c + 1] = off[c] + (size_t)N * wc;
+  }
+  int32_t status = PGB200_OK;
+  for (int d = 0; d < ndev; d++) {
+    PGB_CUDA(cudaSetDevice(d));
+    const int64_t rows = b[d + 1] - b[d];
+    PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dP[d]), (off[nslice] ? off[nslice] : 4) * sizeof(float), st->link[d]));
+    if (rows > 0) {
+      PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dC[d]), (size_t)rows * pC * sizeof(float), st->compute[d]));
+      PGB_CUDA(cudaMemcpy2DAsync(dC[d], pC * sizeof(float), C + b[d] * ldc, ldc * sizeof(float),
+                                 N * sizeof(float), rows, cudaMemcpyDefault, st->compute[d]));
+    }
+    ev[d].resize(nslice);
+    for (int c = 0; c < nslice; c++)
+      PGB_CUDA(cudaEventCreateWithFlags(&ev[d][c], cudaEventDisableTiming));
+  }
+  for (int d = 0; d < ndev; d++) {
+    PGB_CUDA(cudaSetDevice(d));
+    PGB_CUDA(cudaStreamSynchronize(st->link[d]));
+  }
+  for (int c = 0; c < nslice && status == PGB200_OK; c++) {
+    const int64_t w = kb[c + 1] - kb[c], wc = (w + 3) / 4 * 4;
+    PGB_CUDA(cudaSetDevice(0));
+    if (w > 0)  // pack columns [kb[c],kb[c+1]) of A on device 0
+      PGB_CUDA(cudaMemcpy2DAsync(dP[0] + off[c], wc * sizeof(float), A + kb[c], lda * sizeof(float),
+                                 w * sizeof(float), N, cudaMemcpyDefault, st->link[0]));
+    if (ndev > 1 && w > 0) status = bcast<float>(st, dP, off[c], (size_t)N * wc);
+    for (int d = 0; d < ndev; d++) {
+      PGB_CUDA(cudaSetDevice(d));
+      PGB_CUDA(cudaEventRecord(ev[d][c], st->link[d]));
+    }
+  }
+  for (int c = 0; c < nslice && status == PGB200_OK; c++) {
+    const int64_t w = kb[c + 1] - kb[c], wc = (w + 3) / 4 * 4;
+    for (int d = 0; d < ndev && status == PGB200_OK; d++) {
+      const int64_t r0 = b[d], r1 = b[d + 1];
+      if (r1 == r0) continue;
+      PGB_CUDA(cudaSetDevice(d));
+      PGB_CUDA(cudaStreamWaitEvent(st->compute[d], ev[d][c], 0));
+      if (w == 0 && !(c == 0 && K == 0)) continue;
+      // Rows [r0,r1) against columns [0,r1): A_p * A[0:r1]^T masked to j <= i.
+      status = gemm_device<float>(st->compute[d], r1 - r0, r1, w, alpha, dP[d] + off[c] + r0 * wc,
+                                  wc, dP[d] + off[c], wc, true, c == 0 ? beta : 1.0f, dC[d], pC,
+                                  true, r0);
+    }
+  }
+  for (int d = 0; d < ndev; d++) {
+    PGB_CUDA(cudaSetDevice(d));
+    const int64_t rows = b[d + 1] - b[d];
+    if (rows > 0 && status == PGB200_OK)
+      PGB_CUDA(cudaMemcpy2DAsync(C + b[d] * ldc, ldc * sizeof(float), dC[d], pC * sizeof(float),
+                                 N * sizeof(float), rows, cudaMemcpyDefault, st->compute[d]));
+  }
+  for (int d = 0; d < ndev; d++) {
+    PGB_CUDA(cudaSetDevice(d));
+    PGB_CUDA(cudaStreamSynchronize(st->compute[d]));
+    PGB_CUDA(cudaStreamSynchronize(st->link[d]));
+    if (dC[d]) PGB_CUDA(cudaFreeAsync(dC[d], st->compute[d]));
+    PGB_CUDA(cudaFreeAsync(dP[d], st->compute[d]));
+    for (auto e : ev[d]) cudaEventDestroy(e);
+    PGB_CUDA(cudaStreamSynchronize(st->compute[d]));
+  }
+  PGB_CUDA(cudaSetDevice(entry_dev));
+  return status;
+}
+
+}  // namespace
+}  // namespace pgb200
+
+using namespace pgb200;
+
+extern "C" {
+
+int32_t pgb200DgemmMg(int32_t ndev, int64_t M, int64_t N, int64_t K, double alpha, const double *A,
+                      int64_t lda, const double *B, int64_t ldb, double beta, double *C,
+                      int64_t ldc) {
+  return gemm_mg<double>(ndev, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
+}
+
+int32_t pgb200SgemmMg(int32_t ndev, int64_t M, int64_t N, int64_t K, float alpha, const float *A,
+                      int64_t lda, const float *B, int64_t ldb, float beta, float *C,
+                      int64_t ldc) {
+  return gemm_mg<float>(ndev, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
+}
+
+int32_t pgb200SsyrkMg(int32_t ndev, int64_t N, int64_t K, float alpha, const float *A, int64_t lda,
+                      float beta, float *C, int64_t ldc) {
+  return ssyrk_mg(ndev, N, K, alpha, A, lda, beta, C, ldc);
+}
+
+}  // extern "C"

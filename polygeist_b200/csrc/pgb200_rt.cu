@@ -369,7 +369,7 @@ static int32_t fast_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float 
 
 // Device-pointer core shared by gemm and syrk.
 template <typename T>
-static int32_t gemm_device(cudaStream_t s, int64_t M, int64_t N, int64_t K, T alpha, const T *A,
+int32_t gemm_device(cudaStream_t s, int64_t M, int64_t N, int64_t K, T alpha, const T *A,
                            int64_t lda, const T *B, int64_t ldb, bool transB, T beta, T *C,
                            int64_t ldc, bool lower, int64_t row0) {
   Runtime *rt = nullptr;
@@ -381,6 +381,13 @@ static int32_t gemm_device(cudaStream_t s, int64_t M, int64_t N, int64_t K, T al
   }
   return simt_gemm<T>(s, M, N, K, alpha, A, lda, B, ldb, transB, beta, C, ldc, lower, row0);
 }
+
+template int32_t gemm_device<double>(cudaStream_t, int64_t, int64_t, int64_t, double, const double *,
+                                     int64_t, const double *, int64_t, bool, double, double *,
+                                     int64_t, bool, int64_t);
+template int32_t gemm_device<float>(cudaStream_t, int64_t, int64_t, int64_t, float, const float *,
+                                    int64_t, const float *, int64_t, bool, float, float *, int64_t,
+                                    bool, int64_t);
 
 template <typename T>
 static cudaError_t copy_rows(T *dst, int64_t dst_ld, const T *src, int64_t src_ld, int64_t rows,

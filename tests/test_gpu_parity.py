@@ -587,6 +587,42 @@ def test_concurrent_host_threads_on_their_own_streams():
     pgb.poll_device_status()
 
 
+@pytest.mark.parametrize("ndev", [1, 2])
+def test_single_process_multi_gpu_entries(ndev):
+    """pgb200{D,S}gemmMg / pgb200SsyrkMg: row blocks on `ndev` GPUs driven by one
+    host thread, shared operand broadcast by NCCL in K-slices."""
+    if torch.cuda.device_count() < ndev:
+        pytest.skip(f"needs {ndev} GPUs")
+    M, N, K = 1100, 520, 2304            # K >= 2048: several K-slices
+    A = pbo.fill(M, K, np.float64, SEED, 1, -1.0, 1.0)
+    B = pbo.fill(K, N, np.float64, SEED, 2, -1.0, 1.0)
+    C0 = pbo.fill(M, N, np.float64, SEED, 3, -1.0, 1.0)
+    got = C0.copy()
+    pgb.gemm_mg(ndev, 1.5, A, B, 1.2, got)
+    assert normwise(got, 1.5 * (A @ B) + 1.2 * C0) <= 1e-12
+    for r in (0, 511, 512, M - 1):
+        ref = pbo.gemm(1.5, 1.2, C0[r:r + 1].copy(), A[r:r + 1], B)
+        assert normwise(got[r:r + 1], ref) <= 1e-12
+    A32 = pbo.fill(M, K, np.float32, SEED, 4, 0.0, 1.0)
+    B32 = pbo.fill(K, N, np.float32, SEED, 5, 0.0, 1.0)
+    C32 = pbo.fill(M, N, np.float32, SEED, 6, 0.0, 1.0)
+    got32 = C32.copy()
+    pgb.gemm_mg(ndev, 1.5, A32, B32, 1.2, got32)
+    t = 1.5 * (A32.astype(np.float64) @ B32.astype(np.float64)) + 1.2 * C32
+    assert elementwise_rel(got32, t) <= 1e-5
+    n, k = 1300, 2100
+    As = pbo.fill(n, k, np.float32, SEED, 7, 0.0, 1.0)
+    Cs = pbo.fill(n, n, np.float32, SEED, 8, 0.0, 1.0)
+    gots = Cs.copy()
+    pgb.syrk_mg(ndev, 1.5, As, 1.2, gots)
+    ts = 1.5 * (As.astype(np.float64) @ As.astype(np.float64).T) + 1.2 * Cs
+    il, iu = np.tril_indices(n), np.triu_indices(n, 1)
+    assert elementwise_rel(gots[il], ts[il]) <= 1e-5
+    assert np.array_equal(gots[iu], Cs[iu])
+    torch.cuda.set_device(0)
+    pgb.poll_device_status()
+
+
 def test_host_and_device_operands_can_be_mixed():
     M, N, K = 96, 64, 48
     A = dev_fill(M, K, torch.float64, 1, -1.0, 1.0)
