@@ -101,6 +101,22 @@ int32_t mg_state(int ndev, MgState **out) {
     PGB_CUDA(cudaStreamCreateWithFlags(&st.compute[d], cudaStreamNonBlocking));
     PGB_CUDA(cudaStreamCreateWithFlags(&st.link[d], cudaStreamNonBlocking));
   }
+  // Direct peer copies (row blocks of device-resident operands travel over
+  // NVLink instead of being staged through the host).
+  for (int d = 0; d < ndev; d++) {
+    PGB_CUDA(cudaSetDevice(d));
+    for (int p = 0; p < ndev; p++) {
+      if (p == d) continue;
+      int can = 0;
+      PGB_CUDA(cudaDeviceCanAccessPeer(&can, d, p));
+      if (can) {
+        cudaError_t e = cudaDeviceEnablePeerAccess(p, 0);
+        if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled)
+          return report_cuda(e, "cudaDeviceEnablePeerAccess");
+        cudaGetLastError();
+      }
+    }
+  }
   if (ndev > 1) {
     PGB_TRY(load_nccl());
     st.comm.resize(ndev);
@@ -122,6 +138,18 @@ template <>
 ncclDataType_t nccl_type<double>() { return ncclDouble; }
 
 int64_t round_to(int64_t x, int64_t a) { return (x + a / 2) / a * a; }
+
+// rows x cols elements between any two memories (host, this device, a peer):
+// one linear copy when both sides are dense, a pitched copy otherwise.
+template <typename T>
+cudaError_t copy_block(T *dst, int64_t dst_ld, const T *src, int64_t src_ld, int64_t rows,
+                       int64_t cols, cudaStream_t s) {
+  if (rows == 0 || cols == 0) return cudaSuccess;
+  if (dst_ld == cols && src_ld == cols)
+    return cudaMemcpyAsync(dst, src, (size_t)rows * cols * sizeof(T), cudaMemcpyDefault, s);
+  return cudaMemcpy2DAsync(dst, dst_ld * sizeof(T), src, src_ld * sizeof(T), cols * sizeof(T), rows,
+                           cudaMemcpyDefault, s);
+}
 
 // Broadcast rows [0, rows) x `pitch` elements of `bufs[d]` from device 0 to all.
 template <typename T>
@@ -171,21 +199,15 @@ int32_t gemm_mg(int ndev, int64_t M, int64_t N, int64_t K, T alpha, const T *A, 
     if (rows > 0) {
       PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dA[d]), (size_t)rows * pA * sizeof(T), cs));
       PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dC[d]), (size_t)rows * pC * sizeof(T), cs));
-      if (K > 0)
-        PGB_CUDA(cudaMemcpy2DAsync(dA[d], pA * sizeof(T), A + b[d] * lda, lda * sizeof(T),
-                                   K * sizeof(T), rows, cudaMemcpyDefault, cs));
-      if (beta != (T)0)
-        PGB_CUDA(cudaMemcpy2DAsync(dC[d], pC * sizeof(T), C + b[d] * ldc, ldc * sizeof(T),
-                                   N * sizeof(T), rows, cudaMemcpyDefault, cs));
+      PGB_CUDA(copy_block<T>(dA[d], pA, A + b[d] * lda, lda, rows, K, cs));
+      if (beta != (T)0) PGB_CUDA(copy_block<T>(dC[d], pC, C + b[d] * ldc, ldc, rows, N, cs));
     }
     ev[d].resize(nslice);
     for (int c = 0; c < nslice; c++)
       PGB_CUDA(cudaEventCreateWithFlags(&ev[d][c], cudaEventDisableTiming));
   }
   PGB_CUDA(cudaSetDevice(0));
-  if (K > 0)
-    PGB_CUDA(cudaMemcpy2DAsync(dB[0], pB * sizeof(T), B, ldb * sizeof(T), N * sizeof(T), K,
-                               cudaMemcpyDefault, st->link[0]));
+  PGB_CUDA(copy_block<T>(dB[0], pB, B, ldb, K, N, st->link[0]));
   // The receive buffers must exist before device 0 starts sending into them.
   for (int d = 0; d < ndev; d++) {
     PGB_CUDA(cudaSetDevice(d));
@@ -220,8 +242,7 @@ int32_t gemm_mg(int ndev, int64_t M, int64_t N, int64_t K, T alpha, const T *A, 
     PGB_CUDA(cudaSetDevice(d));
     const int64_t rows = b[d + 1] - b[d];
     if (rows > 0 && status == PGB200_OK)
-      PGB_CUDA(cudaMemcpy2DAsync(C + b[d] * ldc, ldc * sizeof(T), dC[d], pC * sizeof(T),
-                                 N * sizeof(T), rows, cudaMemcpyDefault, st->compute[d]));
+      PGB_CUDA(copy_block<T>(C + b[d] * ldc, ldc, dC[d], pC, rows, N, st->compute[d]));
   }
   for (int d = 0; d < ndev; d++) {
     PGB_CUDA(cudaSetDevice(d));
@@ -277,8 +298,7 @@ int32_t ssyrk_mg(int ndev, int64_t N, int64_t K, float alpha, const float *A, in
     PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dP[d]), (off[nslice] ? off[nslice] : 4) * sizeof(float), st->link[d]));
     if (rows > 0) {
       PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dC[d]), (size_t)rows * pC * sizeof(float), st->compute[d]));
-      PGB_CUDA(cudaMemcpy2DAsync(dC[d], pC * sizeof(float), C + b[d] * ldc, ldc * sizeof(float),
-                                 N * sizeof(float), rows, cudaMemcpyDefault, st->compute[d]));
+      PGB_CUDA(copy_block<float>(dC[d], pC, C + b[d] * ldc, ldc, rows, N, st->compute[d]));
     }
     ev[d].resize(nslice);
     for (int c = 0; c < nslice; c++)
@@ -292,8 +312,7 @@ int32_t ssyrk_mg(int ndev, int64_t N, int64_t K, float alpha, const float *A, in
     const int64_t w = kb[c + 1] - kb[c], wc = (w + 3) / 4 * 4;
     PGB_CUDA(cudaSetDevice(0));
     if (w > 0)  // pack columns [kb[c],kb[c+1]) of A on device 0
-      PGB_CUDA(cudaMemcpy2DAsync(dP[0] + off[c], wc * sizeof(float), A + kb[c], lda * sizeof(float),
-                                 w * sizeof(float), N, cudaMemcpyDefault, st->link[0]));
+      PGB_CUDA(copy_block<float>(dP[0] + off[c], wc, A + kb[c], lda, N, w, st->link[0]));
     if (ndev > 1 && w > 0) status = bcast<float>(st, dP, off[c], (size_t)N * wc);
     for (int d = 0; d < ndev; d++) {
       PGB_CUDA(cudaSetDevice(d));
@@ -318,8 +337,7 @@ int32_t ssyrk_mg(int ndev, int64_t N, int64_t K, float alpha, const float *A, in
     PGB_CUDA(cudaSetDevice(d));
     const int64_t rows = b[d + 1] - b[d];
     if (rows > 0 && status == PGB200_OK)
-      PGB_CUDA(cudaMemcpy2DAsync(C + b[d] * ldc, ldc * sizeof(float), dC[d], pC * sizeof(float),
-                                 N * sizeof(float), rows, cudaMemcpyDefault, st->compute[d]));
+      PGB_CUDA(copy_block<float>(C + b[d] * ldc, ldc, dC[d], pC, rows, N, st->compute[d]));
   }
   for (int d = 0; d < ndev; d++) {
     PGB_CUDA(cudaSetDevice(d));
