@@ -13,7 +13,10 @@ K-chunked so that the transfer overlaps the product.
 `value`   device-resident throughput, CUDA events on the launching stream.
 `e2e`     same metric through the reference-facing drop-in (pgb200_kernel_gemm
           with host arrays): H2D and D2H copies inside the timed region.
-`roofline`/`cpu_baseline`: see DESIGN.md.
+`roofline` dominant kernel: algorithmic flop (or bytes) per launch / CUDA-event time,
+          against a measured peak (MEASURED_PEAKS.json for HBM; this library's own
+          issue-rate probes for fp64 and TF32 tensor rates).
+`cpu_baseline` the reference's compiled loop nest on the host cores, bounded sample.
 `--impl reference` times the reference's own compiled kernel_gemm
 (oracle/_ref) on the host cores.
 """
@@ -282,13 +285,13 @@ def run_reference(args, w, name):
     }))
 
 
-def cpu_baseline(w, name, budget_s=5.0):
+def cpu_baseline(w, name, seconds=5.0):
     """The same sample timed on rank 0 beside the GPU number."""
     units, step, used, sample, kind = cpu_sample(w, name)
     step()
     t0 = time.perf_counter()
     reps = 0
-    while reps < 2 or time.perf_counter() - t0 < budget_s:
+    while reps < 2 or time.perf_counter() - t0 < seconds:
         step()
         reps += 1
     dt = (time.perf_counter() - t0) / reps
@@ -490,7 +493,7 @@ def run_pgb200(args, w, name):
             # tensor pipe does 3 * 2MNK flop per step; compare with dense TF32.
             peak_hot = pgb.probe_peak(pgb.PEAK_TF32) / 1e3
             burst = max(peak_cold, peak_hot)
-            # A kernel timed alone is judged against the burst figure.  A step that
+            # A kernel timed alone is compared with the burst figure.  A step that
             # runs for >= 100 ms sits at the 1 kW power cap; MEASURED_PEAKS.json has
             # the driver's own burst and sustained numbers for a tensor-core GEMM
             # (bf16), and their ratio is applied to the TF32 burst probe.  (The

@@ -21,7 +21,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("PGB200_REFERENCE_ROOT", "/root/reference")
+REF_ROOT = os.environ.get("PGB200_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
 PB = os.path.join(REF_ROOT, "tools/cgeist/Test/polybench")
 REF_OUT = os.path.join(HERE, "_ref")
 
