@@ -36,6 +36,9 @@ KERNELS = {
     "gesummv": "linear-algebra/blas/gesummv/gesummv.c",
     "syr2k": "linear-algebra/blas/syr2k/syr2k.c",
     "gemver": "linear-algebra/blas/gemver/gemver.c",
+    "symm": "linear-algebra/blas/symm/symm.c",
+    "trmm": "linear-algebra/blas/trmm/trmm.c",
+    "doitgen": "linear-algebra/kernels/doitgen/doitgen.c",
 }
 TYPES = {"f64": [], "f32": ["-DDATA_TYPE_IS_FLOAT"]}
 

@@ -207,6 +207,56 @@ void FN(pbo_gemver)(int64_t n, T alpha, T beta, T *A, int64_t lda, const T *u1, 
       w[i] = w[i] + alpha * A[i * lda + j] * x[j];
 }
 
+/* linear-algebra/blas/symm/symm.c:108-117
+ *   for i for j { temp2 = 0;
+ *                 for k<i { C[k][j] += alpha*B[i][j] * A[i][k]; temp2 += B[k][j] * A[i][k]; }
+ *                 C[i][j] = beta*C[i][j] + alpha*B[i][j]*A[i][i] + alpha*temp2; }
+ * Only the lower triangle of A (diagonal included) is read. */
+void FN(pbo_symm)(int64_t m, int64_t n, T alpha, T beta, T *C, int64_t ldc, const T *A,
+                  int64_t lda, const T *B, int64_t ldb)
+{
+  for (int64_t i = 0; i < m; i++)
+    for (int64_t j = 0; j < n; j++) {
+      T temp2 = (T)0;
+      for (int64_t k = 0; k < i; k++) {
+        C[k * ldc + j] += alpha * B[i * ldb + j] * A[i * lda + k];
+        temp2 += B[k * ldb + j] * A[i * lda + k];
+      }
+      C[i * ldc + j] = beta * C[i * ldc + j] + alpha * B[i * ldb + j] * A[i * lda + i] + alpha * temp2;
+    }
+}
+
+/* linear-algebra/blas/trmm/trmm.c:101-106
+ *   for i for j { for k>i B[i][j] += A[k][i] * B[k][j];  B[i][j] = alpha * B[i][j]; }
+ * Only the strict lower triangle of A is read (unit diagonal). */
+void FN(pbo_trmm)(int64_t m, int64_t n, T alpha, const T *A, int64_t lda, T *B, int64_t ldb)
+{
+  for (int64_t i = 0; i < m; i++)
+    for (int64_t j = 0; j < n; j++) {
+      for (int64_t k = i + 1; k < m; k++)
+        B[i * ldb + j] += A[k * lda + i] * B[k * ldb + j];
+      B[i * ldb + j] = alpha * B[i * ldb + j];
+    }
+}
+
+/* linear-algebra/kernels/doitgen/doitgen.c:88-97, with (r,q) flattened to one
+ * row index (A is nr*nq rows of np entries, contiguous in the source):
+ *   for row { for p { sum[p] = 0; for s sum[p] += A[row][s] * C4[s][p]; }
+ *             for p A[row][p] = sum[p]; } */
+void FN(pbo_doitgen)(int64_t rows, int64_t np, T *A, int64_t lda, const T *C4, int64_t ldc4,
+                     T *sum)
+{
+  for (int64_t r = 0; r < rows; r++) {
+    for (int64_t p = 0; p < np; p++) {
+      sum[p] = (T)0.0;
+      for (int64_t s = 0; s < np; s++)
+        sum[p] += A[r * lda + s] * C4[s * ldc4 + p];
+    }
+    for (int64_t p = 0; p < np; p++)
+      A[r * lda + p] = sum[p];
+  }
+}
+
 /* Same statements as pbo_gemm, but with a double accumulator per output and
  * the fp32 inputs promoted: the "truth" that fp32 results are also gated on
  * (the sequential fp32 sum itself drifts from it as K grows). */

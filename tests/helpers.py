@@ -133,7 +133,41 @@ def init_gemver(n, dtype):
             np.zeros(n, dtype=dtype), np.zeros(n, dtype=dtype), y.astype(dtype), z.astype(dtype))
 
 
-MINI = {"gemver": (40,), "syr2k": (30, 20), "3mm": (16, 18, 20, 22, 24), "atax": (38, 42), "bicg": (38, 42), "gesummv": (30,),
+def init_symm(m, n, dtype):
+    """symm.c:41-63 (the strict upper triangle of A holds the -999 sentinel)"""
+    dt = np.dtype(dtype).type
+    i, j = _grid(m, n)
+    C = ((i + j) % 100).astype(dtype) / dt(m)
+    B = ((n + i - j) % 100).astype(dtype) / dt(m)
+    i, j = _grid(m, m)
+    A = np.where(j <= i, ((i + j) % 100).astype(dtype) / dt(m), dt(-999)).astype(dtype)
+    return dt(1.5), dt(1.2), C, A, B
+
+
+def init_trmm(m, n, dtype):
+    """trmm.c:41-59 (the strict upper triangle of A is left untouched by the
+    reference; zero here, never read by the nest)"""
+    dt = np.dtype(dtype).type
+    i, j = _grid(m, m)
+    A = np.where(j < i, ((i + j) % m).astype(dtype) / dt(m), dt(0)).astype(dtype)
+    A[np.arange(m), np.arange(m)] = dt(1)
+    i, j = _grid(m, n)
+    B = ((n + (i - j)) % n).astype(dtype) / dt(n)
+    return dt(1.5), A, B
+
+
+def init_doitgen(nr, nq, np_, dtype):
+    """doitgen.c:41-54"""
+    dt = np.dtype(dtype).type
+    i, j, k = np.meshgrid(np.arange(nr), np.arange(nq), np.arange(np_), indexing="ij")
+    A = ((i * j + k) % np_).astype(dtype) / dt(np_)
+    i, j = _grid(np_, np_)
+    C4 = (i * j % np_).astype(dtype) / dt(np_)
+    return np.ascontiguousarray(A), C4, np.zeros(np_, dtype=dtype)
+
+
+MINI = {"symm": (20, 30), "trmm": (20, 30), "doitgen": (10, 8, 12),  # doitgen: (NR, NQ, NP)
+        "gemver": (40,), "syr2k": (30, 20), "3mm": (16, 18, 20, 22, 24), "atax": (38, 42), "bicg": (38, 42), "gesummv": (30,),
         "gemm": (20, 25, 30), "2mm": (16, 18, 22, 24), "mvt": (40,), "syrk": (30, 20)}  # syrk: (N, M)
 
 

@@ -5,7 +5,8 @@ import numpy as np
 import pytest
 
 from helpers import (MINI, SEED, assert_dump_equal, init_2mm, init_3mm, init_atax, init_bicg,
-                     init_gemm, init_gemver, init_gesummv, init_mvt, init_syr2k, init_syrk,
+                     init_doitgen, init_gemm, init_gemver, init_gesummv, init_mvt, init_symm,
+                     init_syr2k, init_syrk, init_trmm,
                      read_dump)
 from oracle import pbo, ref
 
@@ -73,6 +74,23 @@ def test_3mm_atax_bicg_gesummv_golden(tname, dtype):
     assert_dump_equal(read_dump("gemver", tname)["w"], w)
 
 
+@pytest.mark.parametrize("tname,dtype", TYPES)
+def test_symm_trmm_doitgen_golden(tname, dtype):
+    m, n = MINI["symm"]
+    alpha, beta, Cm, A, B = init_symm(m, n, dtype)
+    pbo.symm(alpha, beta, Cm, A, B)
+    assert_dump_equal(read_dump("symm", tname)["C"], Cm)
+    m, n = MINI["trmm"]
+    alpha, A, B = init_trmm(m, n, dtype)
+    pbo.trmm(alpha, A, B)
+    assert_dump_equal(read_dump("trmm", tname)["B"], B)
+    nr, nq, np_ = MINI["doitgen"]
+    A, C4, sum_ = init_doitgen(nr, nq, np_, dtype)
+    pbo.doitgen(A, C4, sum_)
+    assert_dump_equal(read_dump("doitgen", tname)["A"], A)
+    assert np.array_equal(sum_, A[-1, -1]), "sum keeps the last row's result"
+
+
 needs_ref = pytest.mark.skipif(not ref.available(), reason="compiled reference kernels absent")
 
 
@@ -116,6 +134,34 @@ def test_oracle_matches_compiled_reference(tname, dtype):
     pbo.syrk(1.5, 1.2, Cs, As)
     ref.kernel_syrk(n, m, 1.5, 1.2, Cs2, As)
     assert np.max(np.abs(Cs - Cs2)) <= tol * np.max(np.abs(Cs2))
+
+
+@needs_ref
+@pytest.mark.parametrize("tname,dtype", TYPES)
+def test_oracle_matches_compiled_reference_symm_trmm_doitgen(tname, dtype):
+    tol = 1e-13 if dtype == np.float64 else 2e-5
+    m, n = 43, 37
+    A, B, Cm = _rand((m, m), dtype, 21), _rand((m, n), dtype, 22), _rand((m, n), dtype, 23)
+    A[np.triu_indices(m, 1)] = -999  # must never be read
+    C2 = Cm.copy()
+    pbo.symm(1.5, 1.2, Cm, A, B)
+    ref.kernel_symm(m, n, 1.5, 1.2, C2, A, B)
+    assert np.max(np.abs(Cm - C2)) <= tol * np.max(np.abs(C2))
+
+    B1, B2 = B.copy(), B.copy()
+    pbo.trmm(1.5, A, B1)
+    ref.kernel_trmm(m, n, 1.5, A, B2)
+    assert np.max(np.abs(B1 - B2)) <= tol * np.max(np.abs(B2))
+    assert np.max(np.abs(B2)) < 1e3, "the sentinel in A's upper triangle leaked into the result"
+
+    nr, nq, np_ = 5, 7, 19
+    A3 = _rand((nr * nq, np_), dtype, 24).reshape(nr, nq, np_)
+    C4 = _rand((np_, np_), dtype, 25)
+    A4 = A3.copy()
+    s1, s2 = np.zeros(np_, dtype), np.zeros(np_, dtype)
+    pbo.doitgen(A3, C4, s1)
+    ref.kernel_doitgen(nr, nq, np_, A4, C4, s2)
+    assert np.max(np.abs(A3 - A4)) <= tol * np.max(np.abs(A4))
 
 
 def test_row_restricted_oracle_is_bit_identical():
