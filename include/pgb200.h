@@ -111,6 +111,37 @@ int32_t pgb200Ssyr2k(void *stream, int64_t N, int64_t K, float alpha,
                      const float *A, int64_t lda, const float *B, int64_t ldb,
                      float beta, float *C, int64_t ldc);
 
+/* C[MxN] = beta * C + alpha * S * B[MxN], S the symmetric M x M matrix whose
+ * lower triangle (diagonal included) is stored in A; the strict upper triangle
+ * of A is never read.  Replaces kernel_symm,
+ * tools/cgeist/Test/polybench/linear-algebra/blas/symm/symm.c:108-117.  One pass
+ * expands A to the dense S in scratch memory, then the dense product runs. */
+int32_t pgb200Dsymm(void *stream, int64_t M, int64_t N, double alpha, const double *A,
+                    int64_t lda, const double *B, int64_t ldb, double beta, double *C,
+                    int64_t ldc);
+int32_t pgb200Ssymm(void *stream, int64_t M, int64_t N, float alpha, const float *A,
+                    int64_t lda, const float *B, int64_t ldb, float beta, float *C,
+                    int64_t ldc);
+
+/* B[MxN] = alpha * (I + L^T) * B in place, L the strict lower triangle of the
+ * M x M array A (unit diagonal: neither A's diagonal nor its upper triangle is
+ * read).  Replaces kernel_trmm,
+ * tools/cgeist/Test/polybench/linear-algebra/blas/trmm/trmm.c:101-106.  The
+ * products read a copy of the old B and skip the zero part of I + L^T by row
+ * blocks.  Entries of B are expected to be finite: inside a diagonal block a
+ * zero of the triangular factor still multiplies the rows above it. */
+int32_t pgb200Dtrmm(void *stream, int64_t M, int64_t N, double alpha, const double *A,
+                    int64_t lda, double *B, int64_t ldb);
+int32_t pgb200Strmm(void *stream, int64_t M, int64_t N, float alpha, const float *A,
+                    int64_t lda, float *B, int64_t ldb);
+
+/* A[RxP] = A * C4[PxP] in place (R = NR*NQ rows of the flattened 3-D array);
+ * `sum` (P entries, may be null) receives the last row of the result, which is
+ * what the nest leaves there.  Replaces kernel_doitgen,
+ * tools/cgeist/Test/polybench/linear-algebra/kernels/doitgen/doitgen.c:88-97. */
+int32_t pgb200Ddoitgen(void *stream, int64_t R, int64_t P, double *A, int64_t lda,
+                       const double *C4, int64_t ldc4, double *sum);
+
 /* Lower triangle of C[NxN] = alpha * A[NxK] * A^T + beta * C; the strict upper
  * triangle of C is neither read nor written.  Replaces kernel_syrk,
  * tools/cgeist/Test/polybench/linear-algebra/blas/syrk/syrk.c:97-106. */
@@ -310,6 +341,17 @@ int32_t pgb200_kernel_bicg(int m, int n, const double *A, double *s, double *q,
 int32_t pgb200_kernel_gesummv(int n, double alpha, double beta, const double *A,
                               const double *B, double *tmp, const double *x,
                               double *y);
+/*   pgb200_kernel_symm     <- kernel_symm     blas/symm/symm.c:89-120
+ *   pgb200_kernel_trmm     <- kernel_trmm     blas/trmm/trmm.c:85-109
+ *   pgb200_kernel_doitgen  <- kernel_doitgen  kernels/doitgen/doitgen.c:80-100 */
+int32_t pgb200_kernel_symm(int m, int n, double alpha, double beta, double *C,
+                           const double *A, const double *B);
+int32_t pgb200_kernel_symm_f32(int m, int n, float alpha, float beta, float *C,
+                               const float *A, const float *B);
+int32_t pgb200_kernel_trmm(int m, int n, double alpha, const double *A, double *B);
+int32_t pgb200_kernel_trmm_f32(int m, int n, float alpha, const float *A, float *B);
+int32_t pgb200_kernel_doitgen(int nr, int nq, int np, double *A, const double *C4,
+                              double *sum);
 
 #ifdef __cplusplus
 }

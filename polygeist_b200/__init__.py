@@ -83,6 +83,16 @@ SIGNATURES = {
     "pgb200_kernel_atax": (_i32, [_int, _int, _vp, _vp, _vp, _vp]),
     "pgb200_kernel_bicg": (_i32, [_int, _int, _vp, _vp, _vp, _vp, _vp]),
     "pgb200_kernel_gesummv": (_i32, [_int, _f64, _f64, _vp, _vp, _vp, _vp, _vp]),
+    "pgb200Dsymm": (_i32, [_vp, _i64, _i64, _f64, _vp, _i64, _vp, _i64, _f64, _vp, _i64]),
+    "pgb200Ssymm": (_i32, [_vp, _i64, _i64, _f32, _vp, _i64, _vp, _i64, _f32, _vp, _i64]),
+    "pgb200Dtrmm": (_i32, [_vp, _i64, _i64, _f64, _vp, _i64, _vp, _i64]),
+    "pgb200Strmm": (_i32, [_vp, _i64, _i64, _f32, _vp, _i64, _vp, _i64]),
+    "pgb200Ddoitgen": (_i32, [_vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "pgb200_kernel_symm": (_i32, [_int, _int, _f64, _f64, _vp, _vp, _vp]),
+    "pgb200_kernel_symm_f32": (_i32, [_int, _int, _f32, _f32, _vp, _vp, _vp]),
+    "pgb200_kernel_trmm": (_i32, [_int, _int, _f64, _vp, _vp]),
+    "pgb200_kernel_trmm_f32": (_i32, [_int, _int, _f32, _vp, _vp]),
+    "pgb200_kernel_doitgen": (_i32, [_int, _int, _int, _vp, _vp, _vp]),
 }
 
 _lib = None
@@ -204,6 +214,36 @@ def syr2k(alpha, A, B, beta, Cm, stream=None):
     fn = load().pgb200Dsyr2k if _is_f64(Cm) else load().pgb200Ssyr2k
     check(fn(s, N, K, alpha, _ptr(A), _ld(A), _ptr(B), _ld(B), beta, _ptr(Cm), _ld(Cm)))
     return Cm
+
+
+def symm(alpha, A, B, beta, Cm, stream=None):
+    """Cm = beta*Cm + alpha*S@B in place, S symmetric with its lower triangle in A."""
+    M, N = Cm.shape
+    assert tuple(A.shape) == (M, M) and tuple(B.shape) == (M, N)
+    s = _stream(stream) if stream is not None else current_stream_for(A, B, Cm)
+    fn = load().pgb200Dsymm if _is_f64(Cm) else load().pgb200Ssymm
+    check(fn(s, M, N, alpha, _ptr(A), _ld(A), _ptr(B), _ld(B), beta, _ptr(Cm), _ld(Cm)))
+    return Cm
+
+
+def trmm(alpha, A, B, stream=None):
+    """B = alpha*(I + L^T)@B in place, L the strict lower triangle of A."""
+    M, N = B.shape
+    assert tuple(A.shape) == (M, M)
+    s = _stream(stream) if stream is not None else current_stream_for(A, B)
+    fn = load().pgb200Dtrmm if _is_f64(B) else load().pgb200Strmm
+    check(fn(s, M, N, alpha, _ptr(A), _ld(A), _ptr(B), _ld(B)))
+    return B
+
+
+def doitgen(A, C4, sum_=None, stream=None):
+    """A[R x P] = A @ C4 in place (float64); `sum_` receives the last row."""
+    R, P = A.shape
+    assert tuple(C4.shape) == (P, P) and _is_f64(A)
+    s = _stream(stream) if stream is not None else current_stream_for(A, C4)
+    check(load().pgb200Ddoitgen(s, R, P, _ptr(A), _ld(A), _ptr(C4), _ld(C4),
+                                _ptr(sum_) if sum_ is not None else None))
+    return A
 
 
 def syrk(alpha, A, beta, Cm, stream=None, rows=None):

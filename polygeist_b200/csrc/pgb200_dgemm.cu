@@ -91,6 +91,17 @@ __device__ __forceinline__ void dmma_m16n8k4(double (&d)[4], const double (&a)[2
 struct TileMap {
   int64_t tiles_m, tiles_n, total;
   int lower;
+  // A is upper triangular (zero left of its diagonal): the K loop of tile row
+  // tm starts at the diagonal block instead of 0.
+  int a_upper;
+  __device__ int64_t first_kblock(int64_t tm) const { return a_upper ? (tm * BM) / BK : 0; }
+  // Tile of CTA `cta` in its round-th turn.  Tiles come in descending K length
+  // when A is triangular, so odd rounds hand them out in reverse CTA order
+  // (each CTA's long and short tiles pair up); otherwise plain round-robin.
+  // May return an index >= total in the last round.
+  __device__ int64_t index(int64_t round, int64_t cta, int64_t ctas) const {
+    return round * ctas + ((a_upper && (round & 1)) ? ctas - 1 - cta : cta);
+  }
   __device__ void get(int64_t idx, int64_t *tm, int64_t *tn) const {
     if (lower) {
       // idx = tm*(tm+1)/2 + tn with tn <= tm (BM == BN).
@@ -141,10 +152,12 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < tiles.total && ok; t += gridDim.x) {
+      for (int64_t round = 0; round * gridDim.x < tiles.total && ok; round++) {
+        const int64_t t = tiles.index(round, blockIdx.x, gridDim.x);
+        if (t >= tiles.total) continue;
         int64_t tm, tn;
         tiles.get(t, &tm, &tn);
-        for (int64_t kb = 0; kb < nkb; kb++) {
+        for (int64_t kb = tiles.first_kblock(tm); kb < nkb; kb++) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) {
             report_status(status, 1, (int32_t)blockIdx.x);
             ok = false;
@@ -172,7 +185,9 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   const int g = lane >> 2, t4 = lane & 3;
   const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps -> 64 x 32 sub-tiles
   uint32_t stage = 0, phase = 0;
-  for (int64_t t = blockIdx.x; t < tiles.total; t += gridDim.x) {
+  for (int64_t round = 0; round * gridDim.x < tiles.total; round++) {
+    const int64_t t = tiles.index(round, blockIdx.x, gridDim.x);
+    if (t >= tiles.total) continue;
     int64_t tm, tn;
     tiles.get(t, &tm, &tn);
     double acc[4][4][4];
@@ -183,7 +198,7 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #pragma unroll
         for (int r = 0; r < 4; r++) acc[i][j][r] = 0.0;
 
-    for (int64_t kb = 0; kb < nkb; kb++) {
+    for (int64_t kb = tiles.first_kblock(tm); kb < nkb; kb++) {
       if (!mbar_wait(full0 + 8 * stage, phase)) {
         report_status(status, 2, (int32_t)blockIdx.x);
         return;
@@ -269,7 +284,7 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 
 int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha, const double *A,
                   int64_t lda, const double *B, int64_t ldb, bool transB, double beta, double *C,
-                  int64_t ldc, bool lower) {
+                  int64_t ldc, bool lower, bool a_upper) {
   Runtime *rt = nullptr;
   PGB_TRY(get_runtime(&rt));
   // TMA rules: 16-byte aligned bases and row pitches; the 3-D views need K
@@ -306,6 +321,7 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
   tiles.tiles_m = (M + BM - 1) / BM;
   tiles.tiles_n = (N + BN - 1) / BN;
   tiles.lower = lower ? 1 : 0;
+  tiles.a_upper = a_upper ? 1 : 0;
   if (lower) {
     // Square lower-triangular update only (row0 == 0, M == N).
     if (M != N) return PGB200_ERR_UNSUPPORTED;

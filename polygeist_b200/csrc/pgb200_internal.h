@@ -103,16 +103,21 @@ int32_t simt_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, T alpha, cons
                   int64_t ldc, bool lower, int64_t row0);
 
 // fp64 DMMA path.  Returns PGB200_ERR_UNSUPPORTED when the operands do not
-// meet its alignment rules (the caller then takes the SIMT path).
+// meet its alignment rules (the caller then takes the SIMT path).  a_upper:
+// A(i,k) is zero for k < i, and the K-blocks left of each tile row's diagonal
+// are skipped (neither loaded nor multiplied).
 int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
                   const double *A, int64_t lda, const double *B, int64_t ldb, bool transB,
-                  double beta, double *C, int64_t ldc, bool lower);
+                  double beta, double *C, int64_t ldc, bool lower, bool a_upper = false);
 
 // fp32 3xTF32 tcgen05 path; rows [row0,row0+M) of a lower-triangular update
-// when `lower`.  Same UNSUPPORTED convention.
+// when `lower`.  Same UNSUPPORTED convention.  a_upper: A(i,k) is zero for
+// k < i; large products then skip the K-blocks left of each tile row's
+// diagonal (a pure optimisation: the zeros are in A either way).
 int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha,
                     const float *A, int64_t lda, const float *B, int64_t ldb, bool transB,
-                    float beta, float *C, int64_t ldc, bool lower, int64_t row0);
+                    float beta, float *C, int64_t ldc, bool lower, int64_t row0,
+                    bool a_upper = false);
 
 // Device-pointer GEMM core on the current device: picks the tensor-core path,
 // falls back to the SIMT kernels.  C[MxN] = alpha*A*op(B) + beta*C; `lower` and

@@ -281,6 +281,17 @@ struct Tiles {
   int lower;
   int bn;        // tile width in columns (256, or 64 for problems with few tiles)
   int bm;        // tile height in rows (128; 256 for the two-CTA kernel's pair tiles)
+  // A(i,k) is zero for k < i (two-CTA kernel only): the K loop of tile row tm
+  // starts at its diagonal block, and odd rounds hand tiles out in reverse
+  // order so every pair gets long and short tiles alike.
+  int a_upper;
+  __device__ __forceinline__ int64_t first_kblock(int64_t tm) const {
+    return a_upper ? (tm * bm) / BK : 0;
+  }
+  // May return an index >= total in the last round.
+  __device__ __forceinline__ int64_t index(int64_t round, int64_t who, int64_t n) const {
+    return round * n + ((a_upper && (round & 1)) ? n - 1 - who : who);
+  }
 };
 
 // Columns tiles of tile-row tm that intersect j <= i (lower) or all of them.
@@ -842,7 +853,7 @@ __device__ __forceinline__ void tc2_commit_both(uint32_t bar) {
       : "memory");
 }
 
-template <bool B_MN>
+template <bool B_MN, bool A_UPPER>
 __global__ void __launch_bounds__(THREADS, 1)
 tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
                         const __grid_constant__ CUtensorMap mapAlo,
@@ -887,7 +898,6 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
   const uint32_t tmem_base = tmem_slot;
 
   const int64_t nkb = (K + BK - 1) / BK;
-  const int64_t nchunks = (nkb + chunk_kblocks - 1) / chunk_kblocks;
   if (warp < FIRST_EPI_WARP) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
@@ -897,12 +907,15 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
         bool ok = true;
         const uint32_t leader_full0 = map_to_cta(full0, 0);
         TileCursor cur;
-        for (int64_t t = pair; t < total && ok; t += npairs) {
+        for (int64_t it = A_UPPER ? 0 : pair; (A_UPPER ? it * npairs < total : it < total) && ok;
+             it += A_UPPER ? 1 : npairs) {
+          const int64_t t = A_UPPER ? tiles.index(it, pair, npairs) : it;
+          if (A_UPPER && t >= total) continue;
           int64_t tm2, tn;
           cur.seek(tiles, t, &tm2, &tn);
           const int row_a = (int)(tm2 * 256 + rank * 128);
           const int col_b = (int)(tn * 256 + rank * P2_BNH);
-          for (int64_t kb = 0; kb < nkb; kb++) {
+          for (int64_t kb = A_UPPER ? tiles.first_kblock(tm2) : 0; kb < nkb; kb++) {
             if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) {
               report_status(status, 31, (int32_t)blockIdx.x);
               ok = false;
@@ -935,7 +948,18 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
         uint32_t stage = 0, phase = 0;
         int64_t cc = 0;
         bool ok = true;
-        for (int64_t t = pair; t < total && ok; t += npairs) {
+        TileCursor cur;
+        for (int64_t it = A_UPPER ? 0 : pair; (A_UPPER ? it * npairs < total : it < total) && ok;
+             it += A_UPPER ? 1 : npairs) {
+          const int64_t t = A_UPPER ? tiles.index(it, pair, npairs) : it;
+          if (A_UPPER && t >= total) continue;
+          int64_t kb0 = 0;
+          if (A_UPPER) {
+            int64_t tm2, tn;
+            cur.seek(tiles, t, &tm2, &tn);
+            kb0 = tiles.first_kblock(tm2);
+          }
+          const int64_t nchunks = (nkb - kb0 + chunk_kblocks - 1) / chunk_kblocks;
           for (int64_t ch = 0; ch < nchunks && ok; ch++, cc++) {
             const uint32_t buf = (uint32_t)(cc & 1);
             const uint32_t use = (uint32_t)((cc >> 1) & 1);
@@ -946,9 +970,9 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
             }
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + buf * 256;
-            const int64_t kb_end =
-                (ch + 1) * chunk_kblocks < nkb ? (ch + 1) * chunk_kblocks : nkb;
-            for (int64_t kb = ch * chunk_kblocks; kb < kb_end; kb++) {
+            const int64_t kb_first = kb0 + ch * chunk_kblocks;
+            const int64_t kb_end = kb_first + chunk_kblocks < nkb ? kb_first + chunk_kblocks : nkb;
+            for (int64_t kb = kb_first; kb < kb_end; kb++) {
               if (!mbar_wait(full0 + 8 * stage, phase)) {
                 report_status(status, 33, (int32_t)blockIdx.x);
                 ok = false;
@@ -962,7 +986,7 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
               const uint64_t blo = B_MN ? smem_desc_mn_sw128(sa + 2 * A_BYTES + P2_B_BYTES)
                                         : smem_desc_sw64(sa + 2 * A_BYTES + P2_B_BYTES);
               constexpr uint32_t idesc = B_MN ? (P2_IDESC | (1u << 16)) : P2_IDESC;
-              const bool first = (kb == ch * chunk_kblocks);
+              const bool first = (kb == kb_first);
 #pragma unroll
               for (int ks = 0; ks < BK / 8; ks++) {
                 const uint64_t ko = (uint64_t)(ks * 2);
@@ -992,9 +1016,14 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
     TileCursor cur;
     int64_t cc = 0;
     bool ok = true;
-    for (int64_t t = pair; t < total && ok; t += npairs) {
+    for (int64_t it = A_UPPER ? 0 : pair; (A_UPPER ? it * npairs < total : it < total) && ok;
+         it += A_UPPER ? 1 : npairs) {
+      const int64_t t = A_UPPER ? tiles.index(it, pair, npairs) : it;
+      if (A_UPPER && t >= total) continue;
       int64_t tm2, tn;
       cur.seek(tiles, t, &tm2, &tn);
+      const int64_t nchunks =
+          (nkb - (A_UPPER ? tiles.first_kblock(tm2) : 0) + chunk_kblocks - 1) / chunk_kblocks;
       const int64_t r_base = tm2 * 256 + rank * 128 + quarter * 32;
       const int64_t cb = tn * 256 + half * 128;
       float acc[128];
@@ -1106,7 +1135,7 @@ int32_t tf32_peak_probe(cudaStream_t s, double *gflops) {
 
 int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha, const float *A,
                     int64_t lda, const float *B, int64_t ldb, bool transB, float beta, float *C,
-                    int64_t ldc, bool lower, int64_t row0) {
+                    int64_t ldc, bool lower, int64_t row0, bool a_upper) {
   Runtime *rt = nullptr;
   PGB_TRY(get_runtime(&rt));
   if (K == 0) return PGB200_ERR_UNSUPPORTED;  // nothing to contract: SIMT path scales C
@@ -1228,6 +1257,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   tiles.bm = BM;
   tiles.row0 = row0;
   tiles.lower = lower ? 1 : 0;
+  tiles.a_upper = 0;  // a hint only the two-CTA kernel takes; the product is the same without it
   if (lower) {
     int64_t total = 0;
     for (int64_t tm = 0; tm < tiles.tiles_m; tm++) {
@@ -1261,6 +1291,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     t2.bn = 256;
     t2.tiles_m = (M + 255) / 256;
     t2.tiles_n = (N + 255) / 256;
+    t2.a_upper = (a_upper && !lower) ? 1 : 0;
     if (lower) {
       int64_t tot = 0;
       for (int64_t tm = 0; tm < t2.tiles_m; tm++) {
@@ -1286,17 +1317,18 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     attr[0].val.clusterDim.z = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    if (b_mn) {
-      PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_2cta_kernel<true>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      PGB_CUDA(cudaLaunchKernelEx(&lc, tf32x3_gemm_2cta_kernel<true>, mAhi, mAlo, m2Bhi, m2Blo, M,
-                                  N, K, alpha, beta, C, ldc, t2, chunk, rt->status_dev));
-    } else {
-      PGB_CUDA(cudaFuncSetAttribute(tf32x3_gemm_2cta_kernel<false>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      PGB_CUDA(cudaLaunchKernelEx(&lc, tf32x3_gemm_2cta_kernel<false>, mAhi, mAlo, m2Bhi, m2Blo, M,
-                                  N, K, alpha, beta, C, ldc, t2, chunk, rt->status_dev));
-    }
+    auto launch2 = [&](auto kernel) -> int32_t {
+      PGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      PGB_CUDA(cudaLaunchKernelEx(&lc, kernel, mAhi, mAlo, m2Bhi, m2Blo, M, N, K, alpha, beta, C, ldc,
+                                  t2, chunk, rt->status_dev));
+      return PGB200_OK;
+    };
+    if (t2.a_upper)
+      PGB_TRY(b_mn ? launch2(tf32x3_gemm_2cta_kernel<true, true>)
+                   : launch2(tf32x3_gemm_2cta_kernel<false, true>));
+    else
+      PGB_TRY(b_mn ? launch2(tf32x3_gemm_2cta_kernel<true, false>)
+                   : launch2(tf32x3_gemm_2cta_kernel<false, false>));
     note_launch(PATH_TCGEN05);
     PGB_CUDA(cudaGetLastError());
     return PGB200_OK;

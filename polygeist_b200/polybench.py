@@ -91,3 +91,19 @@ def kernel_gemver(n, alpha, beta, A, u1, v1, u2, v2, w, x, y, z):
     _f64(A, u1, v1, u2, v2, w, x, y, z)
     vecs = [_req(v, (n,)) for v in (u1, v1, u2, v2, w, x, y, z)]
     check(load().pgb200_kernel_gemver(n, alpha, beta, _req(A, (n, n)), *vecs))
+
+
+def kernel_symm(m, n, alpha, beta, C, A, B):
+    f = load().pgb200_kernel_symm if C.dtype == np.float64 else load().pgb200_kernel_symm_f32
+    check(f(m, n, alpha, beta, _req(C, (m, n)), _req(A, (m, m)), _req(B, (m, n))))
+
+
+def kernel_trmm(m, n, alpha, A, B):
+    f = load().pgb200_kernel_trmm if B.dtype == np.float64 else load().pgb200_kernel_trmm_f32
+    check(f(m, n, alpha, _req(A, (m, m)), _req(B, (m, n))))
+
+
+def kernel_doitgen(nr, nq, np_, A, C4, sum_):
+    _f64(A, C4, sum_)
+    check(load().pgb200_kernel_doitgen(nr, nq, np_, _req(A, (nr, nq, np_)), _req(C4, (np_, np_)),
+                                       _req(sum_, (np_,))))

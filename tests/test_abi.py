@@ -65,3 +65,26 @@ def test_polybench_mirror_rejects_wrong_extents():
     with pytest.raises(ValueError):
         polybench.kernel_mvt(4, np.zeros(4), np.zeros(4), np.zeros(4), np.zeros(4),
                              np.zeros((4, 4), dtype=np.float32))
+
+
+def build_c_caller(tmp_path):
+    """Compile tests/c_harness/polybench_caller.c as strict C99 against the
+    public header and link it with the in-tree library."""
+    import subprocess
+    here = os.path.dirname(os.path.abspath(__file__))
+    root = os.path.dirname(here)
+    libdir = os.path.dirname(pgb.LIB_PATH)
+    pgb.load()  # builds the library when absent
+    exe = str(tmp_path / "polybench_caller")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-O1",
+                    "-I", os.path.join(root, "include"),
+                    os.path.join(here, "c_harness", "polybench_caller.c"), "-o", exe,
+                    "-L", libdir, "-lpgb200", "-lm", f"-Wl,-rpath,{libdir}"], check=True)
+    return exe
+
+
+def test_header_is_c99_and_a_c_program_links(tmp_path):
+    import subprocess
+    exe = build_c_caller(tmp_path)
+    out = subprocess.run([exe], check=True, capture_output=True, text=True).stdout
+    assert "libpgb200 version" in out

@@ -16,8 +16,7 @@ import torch
 import polygeist_b200 as pgb
 from helpers import (MINI, SEED, assert_dump_equal, backward_gemm, elementwise_rel, init_2mm,
                      init_3mm, init_atax, init_bicg, init_gemm, init_gemver, init_gesummv, init_mvt,
-                     init_syr2k,
-                     init_syrk,
+                     init_doitgen, init_symm, init_syr2k, init_syrk, init_trmm,
                      normwise, read_dump)
 from oracle import pbo
 from polygeist_b200 import polybench
@@ -484,6 +483,98 @@ def test_syr2k_matches_oracle_and_golden(np_dtype, tname):
     il, iu = np.tril_indices(n), np.triu_indices(n, 1)
     assert elementwise_rel(got[il], ref[il]) <= (1e-12 if np_dtype == np.float64 else 1e-5)
     assert np.array_equal(got[iu], C0[iu])
+
+
+@pytest.mark.parametrize("np_dtype,tname", [(np.float64, "f64"), (np.float32, "f32")])
+def test_symm_matches_oracle_and_golden(np_dtype, tname):
+    m, n = MINI["symm"]
+    alpha, beta, Cm, A, B = init_symm(m, n, np_dtype)   # upper triangle of A holds -999
+    polybench.kernel_symm(m, n, alpha, beta, Cm, A, B)
+    assert_dump_equal(read_dump("symm", tname)["C"], Cm, slack_ulps=1)
+    tol = 1e-12 if np_dtype == np.float64 else 1e-5
+    for m, n in ((300, 260), (512, 384), (1001, 128)):
+        A = pbo.fill(m, m, np_dtype, SEED, 1, 0.0, 1.0)
+        A[np.triu_indices(m, 1)] = np.nan               # must never be read
+        B = pbo.fill(m, n, np_dtype, SEED, 2, 0.0, 1.0)
+        C0 = pbo.fill(m, n, np_dtype, SEED, 3, 0.0, 1.0)
+        got = C0.copy()
+        polybench.kernel_symm(m, n, 1.5, 1.2, got, A, B)
+        ref = pbo.symm(1.5, 1.2, C0.copy(), A, B)
+        assert np.isfinite(got).all()
+        assert elementwise_rel(got, ref) <= tol, (m, n)
+
+
+@pytest.mark.parametrize("np_dtype,tname", [(np.float64, "f64"), (np.float32, "f32")])
+def test_trmm_matches_oracle_and_golden(np_dtype, tname):
+    m, n = MINI["trmm"]
+    alpha, A, B = init_trmm(m, n, np_dtype)
+    polybench.kernel_trmm(m, n, alpha, A, B)
+    assert_dump_equal(read_dump("trmm", tname)["B"], B, slack_ulps=1)
+    tol = 1e-12 if np_dtype == np.float64 else 1e-5
+    # 1000 rows: four row blocks, inner extent padded; 515: odd extents everywhere
+    for m, n in ((300, 260), (1000, 256), (515, 77), (2304, 128), (2304, 1280)):
+        A = pbo.fill(m, m, np_dtype, SEED, 1, 0.0, 1.0)
+        A[np.triu_indices(m, 0)] = np.nan               # diagonal and above: never read
+        B0 = pbo.fill(m, n, np_dtype, SEED, 2, 0.0, 1.0)
+        got = B0.copy()
+        polybench.kernel_trmm(m, n, 1.5, A, got)
+        ref = pbo.trmm(1.5, A, B0.copy())
+        assert np.isfinite(got).all()
+        assert elementwise_rel(got, ref) <= tol, (m, n)
+
+
+def test_doitgen_matches_oracle_and_golden():
+    nr, nq, np_ = MINI["doitgen"]
+    A, C4, sum_ = init_doitgen(nr, nq, np_, np.float64)
+    polybench.kernel_doitgen(nr, nq, np_, A, C4, sum_)
+    assert_dump_equal(read_dump("doitgen", "f64")["A"], A, slack_ulps=1)
+    assert np.array_equal(sum_, A[-1, -1])
+    for nr, nq, np_ in ((20, 25, 128), (7, 9, 30), (50, 40, 160)):   # the last is PolyBench MEDIUM
+        A = pbo.fill(nr * nq, np_, np.float64, SEED, 1, -1.0, 1.0).reshape(nr, nq, np_)
+        C4 = pbo.fill(np_, np_, np.float64, SEED, 2, -1.0, 1.0)
+        got, s1, s2 = A.copy(), np.zeros(np_), np.zeros(np_)
+        polybench.kernel_doitgen(nr, nq, np_, got, C4, s1)
+        ref = pbo.doitgen(A.copy(), C4, s2)
+        assert normwise(got, ref) <= 1e-12
+        assert np.array_equal(s1, got[-1, -1])
+
+
+def test_symm_trmm_doitgen_device_pointers_on_a_stream():
+    """Device-pointer forms, padded leading dimensions, non-default stream."""
+    m, n = 640, 384
+    st = torch.cuda.Stream(device=DEV)
+    A = dev_fill(m, m, torch.float64, 1, 0.0, 1.0, ld=m + 4)
+    B = dev_fill(m, n, torch.float64, 2, 0.0, 1.0, ld=n + 8)
+    Cm = dev_fill(m, n, torch.float64, 3, 0.0, 1.0, ld=n + 2)
+    hA, hB, hC = (t.cpu().numpy().copy() for t in (A, B, Cm))
+    torch.cuda.synchronize()
+    with torch.cuda.stream(st):
+        pgb.symm(1.5, A, B, 1.2, Cm)
+        assert pgb.last_path() == pgb.PATH_DMMA
+        pgb.trmm(1.5, A, B)
+    st.synchronize()
+    sync_ok()
+    assert elementwise_rel(Cm.cpu().numpy(), pbo.symm(1.5, 1.2, hC, hA, hB)) <= 1e-12
+    assert elementwise_rel(B.cpu().numpy(), pbo.trmm(1.5, hA, hB.copy())) <= 1e-12
+    r, p = 1500, 256
+    A3 = dev_fill(r, p, torch.float64, 4, -1.0, 1.0)
+    C4 = dev_fill(p, p, torch.float64, 5, -1.0, 1.0)
+    h3, h4 = A3.cpu().numpy().copy(), C4.cpu().numpy().copy()
+    s_dev = torch.zeros(p, dtype=torch.float64, device=DEV)
+    pgb.doitgen(A3, C4, s_dev)
+    sync_ok()
+    ref = pbo.doitgen(h3, h4, np.zeros(p))
+    assert normwise(A3.cpu().numpy(), ref) <= 1e-12
+    assert torch.equal(s_dev, A3[-1])
+
+
+def test_plain_c_caller_runs_the_drop_ins(tmp_path):
+    """The C ABI used from C: a PolyBench-style program calls the drop-ins on
+    malloc'd arrays and checks them against its own loop nests."""
+    import subprocess
+    from test_abi import build_c_caller
+    r = subprocess.run([build_c_caller(tmp_path), "--compute"], capture_output=True, text=True)
+    assert r.returncode == 0 and "OK" in r.stdout, r.stdout + r.stderr
 
 
 def test_gemver_matches_oracle_and_golden():
