@@ -415,7 +415,8 @@ def run_pgb200(args, w, name):
             # B is small here (128 MiB against 4 ms of compute): one chunk, the
             # broadcast simply precedes the product.
             plan = partition.PartitionedGemm(dist, pgb.gemm, src=0, peer_broadcast=pb,
-                                             chunk=int(os.environ.get("PGB_BENCH_KCHUNK", K)))
+                                             chunk=int(os.environ.get("PGB_BENCH_KCHUNK", K)),
+                                             first_chunk=int(os.environ.get("PGB_BENCH_KFIRST", 0)))
 
             def step():
                 plan.run(ALPHA, A, B, BETA, Cm)

@@ -40,9 +40,15 @@ def syrk_row_blocks(N, P, align=128):
     return b
 
 
-def k_chunks(K, chunk):
+def k_chunks(K, chunk, first=0):
+    """[k0,k1) slices of the inner extent: `chunk` wide, optionally preceded by
+    one narrower slice of `first` (so the first product can start while most
+    of the shared operand is still in flight)."""
     chunk = max(1, int(chunk))
-    return [(k0, min(K, k0 + chunk)) for k0 in range(0, K, chunk)] or [(0, 0)]
+    first = min(int(first), K)
+    head = [(0, first)] if 0 < first < K else []
+    start = first if head else 0
+    return head + [(k0, min(K, k0 + chunk)) for k0 in range(start, K, chunk)] or [(0, 0)]
 
 
 def pull_plan(rank, world, src, k0, k1):
@@ -113,11 +119,13 @@ class PartitionedGemm:
     polygeist_b200.gemm, which enqueues on the current CUDA stream).
     """
 
-    def __init__(self, dist, compute, src=0, chunk=1024, group=None, peer_broadcast=None):
+    def __init__(self, dist, compute, src=0, chunk=1024, group=None, peer_broadcast=None,
+                 first_chunk=0):
         self.dist = dist
         self.compute = compute
         self.src = src
         self.chunk = chunk
+        self.first_chunk = first_chunk
         self.group = group
         self.peer_broadcast = peer_broadcast  # PeerPullBroadcast, or None for NCCL
 
@@ -126,7 +134,7 @@ class PartitionedGemm:
         holds valid data on entry, all hold it on return."""
         dist = self.dist
         K = A_p.shape[1]
-        chunks = k_chunks(K, self.chunk)
+        chunks = k_chunks(K, self.chunk, self.first_chunk)
         world = dist.get_world_size(self.group)
         works = []
         if world > 1 and self.peer_broadcast is not None:

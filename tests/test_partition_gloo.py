@@ -35,6 +35,9 @@ def test_syrk_blocks_balance_area():
 def test_k_chunks():
     assert partition.k_chunks(10, 4) == [(0, 4), (4, 8), (8, 10)]
     assert partition.k_chunks(0, 4) == [(0, 0)]
+    assert partition.k_chunks(10, 10, first=2) == [(0, 2), (2, 10)]
+    assert partition.k_chunks(10, 4, first=3) == [(0, 3), (3, 7), (7, 10)]
+    assert partition.k_chunks(10, 4, first=10) == partition.k_chunks(10, 4)   # no room for a head
 
 
 def test_pull_plan_covers_every_row_once():
@@ -96,6 +99,12 @@ def _worker(rank, world, port, q):
         plan.run(1.5, A_p, B_local, 1.2, C_p)
         ok = np.allclose(C_p.numpy(), ref[r0:r1], rtol=1e-13, atol=1e-13)
         ok = ok and np.array_equal(B_local.numpy(), B)       # every rank ends with all of B
+        # a narrow first K-slice, then the rest in one piece
+        C_q = torch.from_numpy(C[r0:r1].copy())
+        B_q = torch.from_numpy(B.copy()) if rank == 0 else torch.full((K, N), float("nan"), dtype=torch.float64)
+        partition.PartitionedGemm(dist, _np_gemm, src=0, chunk=K, first_chunk=8).run(1.5, A_p, B_q, 1.2, C_q)
+        ok = ok and np.allclose(C_q.numpy(), ref[r0:r1], rtol=1e-13, atol=1e-13)
+        ok = ok and np.array_equal(B_q.numpy(), B)
 
         Ns, Ks = 80, 24
         As = rng.uniform(0, 1, (Ns, Ks))
