@@ -73,14 +73,43 @@ int32_t encode_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank,
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // A caller array that may live on the host: staged to the device on demand.
+// finish() copies an output back and releases the device copy; a Staged that
+// goes out of scope unfinished (an error return) only releases it, so a failed
+// call never overwrites the caller's array.
 template <typename T>
 struct Staged {
   T *dev = nullptr;       // pointer the kernels use
   int64_t ld = 0;         // its leading dimension
-  T *host = nullptr;      // non-null when staged
+  T *host = nullptr;      // non-null while a device copy is held
   int64_t host_ld = 0;
   int64_t rows = 0, cols = 0;
   bool copy_back = false;
+  cudaStream_t stream = nullptr;
+  Staged() = default;
+  Staged(const Staged &) = delete;
+  Staged &operator=(const Staged &) = delete;
+  ~Staged() {
+    if (host && dev) cudaFreeAsync(dev, stream);
+  }
+};
+
+// Scratch from the stream-ordered pool, released (in stream order) when the
+// holder goes out of scope.
+struct PoolBuffer {
+  void *ptr = nullptr;
+  cudaStream_t stream = nullptr;
+  PoolBuffer() = default;
+  PoolBuffer(const PoolBuffer &) = delete;
+  PoolBuffer &operator=(const PoolBuffer &) = delete;
+  ~PoolBuffer() {
+    if (ptr) cudaFreeAsync(ptr, stream);
+  }
+  cudaError_t alloc(size_t bytes, cudaStream_t s) {
+    stream = s;
+    return cudaMallocAsync(&ptr, bytes, s);
+  }
+  template <typename T>
+  T *as() const { return static_cast<T *>(ptr); }
 };
 
 bool is_host_pointer(const void *p);

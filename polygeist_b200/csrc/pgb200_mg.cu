@@ -162,6 +162,32 @@ int32_t bcast(MgState *st, std::vector<T *> &bufs, size_t offset, size_t count) 
   return PGB200_OK;
 }
 
+// Common exit of the multi-GPU entries, also taken after a failure: drain both
+// streams of every device, release the scratch, destroy the events and make
+// the caller's device current again.  Returns `status`, or the first error of
+// the drain when `status` was PGB200_OK.
+int32_t mg_release(MgState *st, int entry_dev, int32_t status,
+                   const std::vector<std::vector<void *>> &bufs,
+                   std::vector<std::vector<cudaEvent_t>> &ev) {
+  cudaError_t drain = cudaSuccess;
+  auto note = [&](cudaError_t e) {
+    if (e != cudaSuccess && drain == cudaSuccess) drain = e;
+  };
+  for (int d = 0; d < st->ndev; d++) {
+    note(cudaSetDevice(d));
+    note(cudaStreamSynchronize(st->compute[d]));
+    note(cudaStreamSynchronize(st->link[d]));
+    for (void *p : bufs[d])
+      if (p) note(cudaFreeAsync(p, st->compute[d]));
+    for (auto e : ev[d])
+      if (e) cudaEventDestroy(e);
+    note(cudaStreamSynchronize(st->compute[d]));
+  }
+  note(cudaSetDevice(entry_dev));
+  if (status == PGB200_OK && drain != cudaSuccess) return report_cuda(drain, "multi-GPU drain");
+  return status;
+}
+
 // C = alpha*A*B + beta*C, rows of A and C split over ndev GPUs, B broadcast in
 // K-slices from device 0.  Arrays may be host memory or memory of device 0.
 template <typename T>
@@ -190,72 +216,67 @@ int32_t gemm_mg(int ndev, int64_t M, int64_t N, int64_t K, T alpha, const T *A, 
   std::vector<T *> dA(ndev, nullptr), dB(ndev, nullptr), dC(ndev, nullptr);
   std::vector<std::vector<cudaEvent_t>> ev(ndev);
   int32_t status = PGB200_OK;
-  // Stage: every device takes its rows of A and C; device 0 takes B.
-  for (int d = 0; d < ndev; d++) {
-    PGB_CUDA(cudaSetDevice(d));
-    const int64_t rows = b[d + 1] - b[d];
-    cudaStream_t cs = st->compute[d];
-    PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dB[d]), (size_t)(K > 0 ? K : 1) * pB * sizeof(T), st->link[d]));
-    if (rows > 0) {
-      PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dA[d]), (size_t)rows * pA * sizeof(T), cs));
-      PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dC[d]), (size_t)rows * pC * sizeof(T), cs));
-      PGB_CUDA(copy_block<T>(dA[d], pA, A + b[d] * lda, lda, rows, K, cs));
-      if (beta != (T)0) PGB_CUDA(copy_block<T>(dC[d], pC, C + b[d] * ldc, ldc, rows, N, cs));
-    }
-    ev[d].resize(nslice);
-    for (int c = 0; c < nslice; c++)
-      PGB_CUDA(cudaEventCreateWithFlags(&ev[d][c], cudaEventDisableTiming));
-  }
-  PGB_CUDA(cudaSetDevice(0));
-  PGB_CUDA(copy_block<T>(dB[0], pB, B, ldb, K, N, st->link[0]));
-  // The receive buffers must exist before device 0 starts sending into them.
-  for (int d = 0; d < ndev; d++) {
-    PGB_CUDA(cudaSetDevice(d));
-    PGB_CUDA(cudaStreamSynchronize(st->link[d]));
-  }
-  // K-slices: broadcast slice c (all of them queued up front on the link
-  // streams), multiply slice c as soon as it has landed.
-  std::vector<int64_t> kb(nslice + 1, 0);
-  for (int c = 1; c < nslice; c++) kb[c] = round_to(K * c / nslice, 16);
-  kb[nslice] = K;
-  for (int c = 0; c < nslice && status == PGB200_OK; c++) {
-    if (ndev > 1 && kb[c + 1] > kb[c])
-      status = bcast<T>(st, dB, (size_t)kb[c] * pB, (size_t)(kb[c + 1] - kb[c]) * pB);
+  auto run = [&]() -> int32_t {
+    // Stage: every device takes its rows of A and C; device 0 takes B.
     for (int d = 0; d < ndev; d++) {
       PGB_CUDA(cudaSetDevice(d));
-      PGB_CUDA(cudaEventRecord(ev[d][c], st->link[d]));
-    }
-  }
-  for (int c = 0; c < nslice && status == PGB200_OK; c++) {
-    for (int d = 0; d < ndev && status == PGB200_OK; d++) {
       const int64_t rows = b[d + 1] - b[d];
-      if (rows == 0) continue;
-      PGB_CUDA(cudaSetDevice(d));
-      PGB_CUDA(cudaStreamWaitEvent(st->compute[d], ev[d][c], 0));
-      if (kb[c + 1] == kb[c] && !(c == 0 && K == 0)) continue;
-      status = gemm_device<T>(st->compute[d], rows, N, kb[c + 1] - kb[c], alpha, dA[d] + kb[c], pA,
-                              dB[d] + kb[c] * pB, pB, false, c == 0 ? beta : (T)1, dC[d], pC,
-                              false, 0);
+      cudaStream_t cs = st->compute[d];
+      PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dB[d]), (size_t)(K > 0 ? K : 1) * pB * sizeof(T), st->link[d]));
+      if (rows > 0) {
+        PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dA[d]), (size_t)rows * pA * sizeof(T), cs));
+        PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dC[d]), (size_t)rows * pC * sizeof(T), cs));
+        PGB_CUDA(copy_block<T>(dA[d], pA, A + b[d] * lda, lda, rows, K, cs));
+        if (beta != (T)0) PGB_CUDA(copy_block<T>(dC[d], pC, C + b[d] * ldc, ldc, rows, N, cs));
+      }
+      ev[d].resize(nslice);
+      for (int c = 0; c < nslice; c++)
+        PGB_CUDA(cudaEventCreateWithFlags(&ev[d][c], cudaEventDisableTiming));
     }
-  }
-  for (int d = 0; d < ndev; d++) {
-    PGB_CUDA(cudaSetDevice(d));
-    const int64_t rows = b[d + 1] - b[d];
-    if (rows > 0 && status == PGB200_OK)
-      PGB_CUDA(copy_block<T>(C + b[d] * ldc, ldc, dC[d], pC, rows, N, st->compute[d]));
-  }
-  for (int d = 0; d < ndev; d++) {
-    PGB_CUDA(cudaSetDevice(d));
-    PGB_CUDA(cudaStreamSynchronize(st->compute[d]));
-    PGB_CUDA(cudaStreamSynchronize(st->link[d]));
-    if (dA[d]) PGB_CUDA(cudaFreeAsync(dA[d], st->compute[d]));
-    if (dC[d]) PGB_CUDA(cudaFreeAsync(dC[d], st->compute[d]));
-    PGB_CUDA(cudaFreeAsync(dB[d], st->compute[d]));
-    for (auto e : ev[d]) cudaEventDestroy(e);
-    PGB_CUDA(cudaStreamSynchronize(st->compute[d]));
-  }
-  PGB_CUDA(cudaSetDevice(entry_dev));
-  return status;
+    PGB_CUDA(cudaSetDevice(0));
+    PGB_CUDA(copy_block<T>(dB[0], pB, B, ldb, K, N, st->link[0]));
+    // The receive buffers must exist before device 0 starts sending into them.
+    for (int d = 0; d < ndev; d++) {
+      PGB_CUDA(cudaSetDevice(d));
+      PGB_CUDA(cudaStreamSynchronize(st->link[d]));
+    }
+    // K-slices: broadcast slice c (all of them queued up front on the link
+    // streams), multiply slice c as soon as it has landed.
+    std::vector<int64_t> kb(nslice + 1, 0);
+    for (int c = 1; c < nslice; c++) kb[c] = round_to(K * c / nslice, 16);
+    kb[nslice] = K;
+    for (int c = 0; c < nslice && status == PGB200_OK; c++) {
+      if (ndev > 1 && kb[c + 1] > kb[c])
+        status = bcast<T>(st, dB, (size_t)kb[c] * pB, (size_t)(kb[c + 1] - kb[c]) * pB);
+      for (int d = 0; d < ndev; d++) {
+        PGB_CUDA(cudaSetDevice(d));
+        PGB_CUDA(cudaEventRecord(ev[d][c], st->link[d]));
+      }
+    }
+    for (int c = 0; c < nslice && status == PGB200_OK; c++) {
+      for (int d = 0; d < ndev && status == PGB200_OK; d++) {
+        const int64_t rows = b[d + 1] - b[d];
+        if (rows == 0) continue;
+        PGB_CUDA(cudaSetDevice(d));
+        PGB_CUDA(cudaStreamWaitEvent(st->compute[d], ev[d][c], 0));
+        if (kb[c + 1] == kb[c] && !(c == 0 && K == 0)) continue;
+        status = gemm_device<T>(st->compute[d], rows, N, kb[c + 1] - kb[c], alpha, dA[d] + kb[c], pA,
+                                dB[d] + kb[c] * pB, pB, false, c == 0 ? beta : (T)1, dC[d], pC,
+                                false, 0);
+      }
+    }
+    for (int d = 0; d < ndev; d++) {
+      PGB_CUDA(cudaSetDevice(d));
+      const int64_t rows = b[d + 1] - b[d];
+      if (rows > 0 && status == PGB200_OK)
+        PGB_CUDA(copy_block<T>(C + b[d] * ldc, ldc, dC[d], pC, rows, N, st->compute[d]));
+    }
+    return status;
+  };
+  status = run();
+  std::vector<std::vector<void *>> bufs(ndev);
+  for (int d = 0; d < ndev; d++) bufs[d] = {dA[d], dB[d], dC[d]};
+  return mg_release(st, entry_dev, status, bufs, ev);
 }
 
 // Lower triangle of C = alpha*A*A^T + beta*C, rows split by equal triangular
@@ -292,64 +313,60 @@ int32_t ssyrk_mg(int ndev, int64_t N, int64_t K, float alpha, const float *A, in
     off[c + 1] = off[c] + (size_t)N * wc;
   }
   int32_t status = PGB200_OK;
-  for (int d = 0; d < ndev; d++) {
-    PGB_CUDA(cudaSetDevice(d));
-    const int64_t rows = b[d + 1] - b[d];
-    PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dP[d]), (off[nslice] ? off[nslice] : 4) * sizeof(float), st->link[d]));
-    if (rows > 0) {
-      PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dC[d]), (size_t)rows * pC * sizeof(float), st->compute[d]));
-      PGB_CUDA(copy_block<float>(dC[d], pC, C + b[d] * ldc, ldc, rows, N, st->compute[d]));
-    }
-    ev[d].resize(nslice);
-    for (int c = 0; c < nslice; c++)
-      PGB_CUDA(cudaEventCreateWithFlags(&ev[d][c], cudaEventDisableTiming));
-  }
-  for (int d = 0; d < ndev; d++) {
-    PGB_CUDA(cudaSetDevice(d));
-    PGB_CUDA(cudaStreamSynchronize(st->link[d]));
-  }
-  for (int c = 0; c < nslice && status == PGB200_OK; c++) {
-    const int64_t w = kb[c + 1] - kb[c], wc = (w + 3) / 4 * 4;
-    PGB_CUDA(cudaSetDevice(0));
-    if (w > 0)  // pack columns [kb[c],kb[c+1]) of A on device 0
-      PGB_CUDA(copy_block<float>(dP[0] + off[c], wc, A + kb[c], lda, N, w, st->link[0]));
-    if (ndev > 1 && w > 0) status = bcast<float>(st, dP, off[c], (size_t)N * wc);
+  auto run = [&]() -> int32_t {
     for (int d = 0; d < ndev; d++) {
       PGB_CUDA(cudaSetDevice(d));
-      PGB_CUDA(cudaEventRecord(ev[d][c], st->link[d]));
+      const int64_t rows = b[d + 1] - b[d];
+      PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dP[d]), (off[nslice] ? off[nslice] : 4) * sizeof(float), st->link[d]));
+      if (rows > 0) {
+        PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dC[d]), (size_t)rows * pC * sizeof(float), st->compute[d]));
+        PGB_CUDA(copy_block<float>(dC[d], pC, C + b[d] * ldc, ldc, rows, N, st->compute[d]));
+      }
+      ev[d].resize(nslice);
+      for (int c = 0; c < nslice; c++)
+        PGB_CUDA(cudaEventCreateWithFlags(&ev[d][c], cudaEventDisableTiming));
     }
-  }
-  for (int c = 0; c < nslice && status == PGB200_OK; c++) {
-    const int64_t w = kb[c + 1] - kb[c], wc = (w + 3) / 4 * 4;
-    for (int d = 0; d < ndev && status == PGB200_OK; d++) {
-      const int64_t r0 = b[d], r1 = b[d + 1];
-      if (r1 == r0) continue;
+    for (int d = 0; d < ndev; d++) {
       PGB_CUDA(cudaSetDevice(d));
-      PGB_CUDA(cudaStreamWaitEvent(st->compute[d], ev[d][c], 0));
-      if (w == 0 && !(c == 0 && K == 0)) continue;
-      // Rows [r0,r1) against columns [0,r1): A_p * A[0:r1]^T masked to j <= i.
-      status = gemm_device<float>(st->compute[d], r1 - r0, r1, w, alpha, dP[d] + off[c] + r0 * wc,
-                                  wc, dP[d] + off[c], wc, true, c == 0 ? beta : 1.0f, dC[d], pC,
-                                  true, r0);
+      PGB_CUDA(cudaStreamSynchronize(st->link[d]));
     }
-  }
-  for (int d = 0; d < ndev; d++) {
-    PGB_CUDA(cudaSetDevice(d));
-    const int64_t rows = b[d + 1] - b[d];
-    if (rows > 0 && status == PGB200_OK)
-      PGB_CUDA(copy_block<float>(C + b[d] * ldc, ldc, dC[d], pC, rows, N, st->compute[d]));
-  }
-  for (int d = 0; d < ndev; d++) {
-    PGB_CUDA(cudaSetDevice(d));
-    PGB_CUDA(cudaStreamSynchronize(st->compute[d]));
-    PGB_CUDA(cudaStreamSynchronize(st->link[d]));
-    if (dC[d]) PGB_CUDA(cudaFreeAsync(dC[d], st->compute[d]));
-    PGB_CUDA(cudaFreeAsync(dP[d], st->compute[d]));
-    for (auto e : ev[d]) cudaEventDestroy(e);
-    PGB_CUDA(cudaStreamSynchronize(st->compute[d]));
-  }
-  PGB_CUDA(cudaSetDevice(entry_dev));
-  return status;
+    for (int c = 0; c < nslice && status == PGB200_OK; c++) {
+      const int64_t w = kb[c + 1] - kb[c], wc = (w + 3) / 4 * 4;
+      PGB_CUDA(cudaSetDevice(0));
+      if (w > 0)  // pack columns [kb[c],kb[c+1]) of A on device 0
+        PGB_CUDA(copy_block<float>(dP[0] + off[c], wc, A + kb[c], lda, N, w, st->link[0]));
+      if (ndev > 1 && w > 0) status = bcast<float>(st, dP, off[c], (size_t)N * wc);
+      for (int d = 0; d < ndev; d++) {
+        PGB_CUDA(cudaSetDevice(d));
+        PGB_CUDA(cudaEventRecord(ev[d][c], st->link[d]));
+      }
+    }
+    for (int c = 0; c < nslice && status == PGB200_OK; c++) {
+      const int64_t w = kb[c + 1] - kb[c], wc = (w + 3) / 4 * 4;
+      for (int d = 0; d < ndev && status == PGB200_OK; d++) {
+        const int64_t r0 = b[d], r1 = b[d + 1];
+        if (r1 == r0) continue;
+        PGB_CUDA(cudaSetDevice(d));
+        PGB_CUDA(cudaStreamWaitEvent(st->compute[d], ev[d][c], 0));
+        if (w == 0 && !(c == 0 && K == 0)) continue;
+        // Rows [r0,r1) against columns [0,r1): A_p * A[0:r1]^T masked to j <= i.
+        status = gemm_device<float>(st->compute[d], r1 - r0, r1, w, alpha, dP[d] + off[c] + r0 * wc,
+                                    wc, dP[d] + off[c], wc, true, c == 0 ? beta : 1.0f, dC[d], pC,
+                                    true, r0);
+      }
+    }
+    for (int d = 0; d < ndev; d++) {
+      PGB_CUDA(cudaSetDevice(d));
+      const int64_t rows = b[d + 1] - b[d];
+      if (rows > 0 && status == PGB200_OK)
+        PGB_CUDA(copy_block<float>(C + b[d] * ldc, ldc, dC[d], pC, rows, N, st->compute[d]));
+    }
+    return status;
+  };
+  status = run();
+  std::vector<std::vector<void *>> bufs(ndev);
+  for (int d = 0; d < ndev; d++) bufs[d] = {dP[d], dC[d]};
+  return mg_release(st, entry_dev, status, bufs, ev);
 }
 
 }  // namespace

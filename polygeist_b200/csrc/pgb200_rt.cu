@@ -170,9 +170,9 @@ int32_t stage(cudaStream_t s, const T *p, int64_t rows, int64_t cols, int64_t ld
     st->host = nullptr;
     return PGB200_OK;
   }
-  st->host = const_cast<T *>(p);
   st->host_ld = ld;
   st->copy_back = out;
+  st->stream = s;
   // Pad the device pitch to 16 bytes so staged operands always meet the
   // alignment rules of the tensor-core paths.
   const int64_t per16 = 16 / (int64_t)sizeof(T);
@@ -180,6 +180,7 @@ int32_t stage(cudaStream_t s, const T *p, int64_t rows, int64_t cols, int64_t ld
   void *d = nullptr;
   PGB_CUDA(cudaMallocAsync(&d, (size_t)rows * st->ld * sizeof(T), s));
   st->dev = static_cast<T *>(d);
+  st->host = const_cast<T *>(p);  // from here on the destructor owns the device copy
   if (in) {
     if (st->ld == ld)
       PGB_CUDA(cudaMemcpyAsync(st->dev, p, (size_t)rows * ld * sizeof(T), cudaMemcpyHostToDevice,
@@ -202,8 +203,9 @@ int32_t finish(cudaStream_t s, Staged<T> *st) {
       PGB_CUDA(cudaMemcpy2DAsync(st->host, st->host_ld * sizeof(T), st->dev, st->ld * sizeof(T),
                                  st->cols * sizeof(T), st->rows, cudaMemcpyDeviceToHost, s));
   }
-  PGB_CUDA(cudaFreeAsync(st->dev, s));
-  st->host = nullptr;
+  T *d = st->dev;
+  st->host = nullptr;  // released below, whatever cudaFreeAsync answers
+  PGB_CUDA(cudaFreeAsync(d, s));
   return PGB200_OK;
 }
 
@@ -411,61 +413,63 @@ static int32_t gemm_host_pipelined(Runtime *rt, cudaStream_t s, int64_t M, int64
   auto pad = [&](int64_t c) { return (c + per16 - 1) / per16 * per16; };
   const int64_t b_rows = transB ? N : K, b_cols = transB ? K : N;
   const int64_t dlda = pad(K), dldb = pad(b_cols), dldc = pad(N);
-  T *dA = nullptr, *dB = nullptr, *dC = nullptr;
-  PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dA), (size_t)M * dlda * sizeof(T), s));
-  PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dB), (size_t)b_rows * dldb * sizeof(T), s));
-  PGB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dC), (size_t)M * dldc * sizeof(T), s));
+  PoolBuffer bufA, bufB, bufC;
+  PGB_CUDA(bufA.alloc((size_t)M * dlda * sizeof(T), s));
+  PGB_CUDA(bufB.alloc((size_t)b_rows * dldb * sizeof(T), s));
+  PGB_CUDA(bufC.alloc((size_t)M * dldc * sizeof(T), s));
+  T *dA = bufA.as<T>(), *dB = bufB.as<T>(), *dC = bufC.as<T>();
   constexpr int MAXB = 16;
   int nb = (int)(M / 512);
   if (nb > MAXB) nb = MAXB;
   if (nb < 1) nb = 1;
   int64_t rows_per = ((M + nb - 1) / nb + 127) / 128 * 128;
   nb = (int)((M + rows_per - 1) / rows_per);
-  cudaEvent_t ev_start, ev_in[MAXB], ev_c[MAXB], ev_done;
-  PGB_CUDA(cudaEventCreateWithFlags(&ev_start, cudaEventDisableTiming));
-  PGB_CUDA(cudaEventCreateWithFlags(&ev_done, cudaEventDisableTiming));
-  for (int i = 0; i < nb; i++) {
-    PGB_CUDA(cudaEventCreateWithFlags(&ev_in[i], cudaEventDisableTiming));
-    PGB_CUDA(cudaEventCreateWithFlags(&ev_c[i], cudaEventDisableTiming));
-  }
-  PGB_CUDA(cudaEventRecord(ev_start, s));  // buffers exist, earlier work on s is done
-  PGB_CUDA(cudaStreamWaitEvent(rt->copy_in, ev_start, 0));
-  PGB_CUDA(cudaStreamWaitEvent(rt->copy_out, ev_start, 0));
-  PGB_CUDA(copy_rows(dB, dldb, B, ldb, b_rows, b_cols, cudaMemcpyHostToDevice, rt->copy_in));
-  for (int i = 0; i < nb; i++) {
-    const int64_t r0 = i * rows_per, rows = (M - r0 < rows_per) ? (M - r0) : rows_per;
-    PGB_CUDA(copy_rows(dA + r0 * dlda, dlda, A + r0 * lda, lda, rows, K, cudaMemcpyHostToDevice,
-                       rt->copy_in));
-    if (beta != (T)0)
-      PGB_CUDA(copy_rows(dC + r0 * dldc, dldc, C + r0 * ldc, ldc, rows, N, cudaMemcpyHostToDevice,
+  cudaEvent_t ev[2 * MAXB + 2] = {};
+  int nev = 0;
+  // The pipeline proper; any failure falls through to the common exit below,
+  // which drains the side streams before the buffers and events go away.
+  auto run = [&]() -> int32_t {
+    for (; nev < 2 * nb + 2; nev++)
+      PGB_CUDA(cudaEventCreateWithFlags(&ev[nev], cudaEventDisableTiming));
+    cudaEvent_t ev_start = ev[0], ev_done = ev[1], *ev_in = ev + 2, *ev_c = ev + 2 + nb;
+    PGB_CUDA(cudaEventRecord(ev_start, s));  // buffers exist, earlier work on s is done
+    PGB_CUDA(cudaStreamWaitEvent(rt->copy_in, ev_start, 0));
+    PGB_CUDA(cudaStreamWaitEvent(rt->copy_out, ev_start, 0));
+    PGB_CUDA(copy_rows(dB, dldb, B, ldb, b_rows, b_cols, cudaMemcpyHostToDevice, rt->copy_in));
+    for (int i = 0; i < nb; i++) {
+      const int64_t r0 = i * rows_per, rows = (M - r0 < rows_per) ? (M - r0) : rows_per;
+      PGB_CUDA(copy_rows(dA + r0 * dlda, dlda, A + r0 * lda, lda, rows, K, cudaMemcpyHostToDevice,
                          rt->copy_in));
-    PGB_CUDA(cudaEventRecord(ev_in[i], rt->copy_in));
-  }
-  int32_t st = PGB200_OK;
-  for (int i = 0; i < nb && st == PGB200_OK; i++) {
-    const int64_t r0 = i * rows_per, rows = (M - r0 < rows_per) ? (M - r0) : rows_per;
-    PGB_CUDA(cudaStreamWaitEvent(s, ev_in[i], 0));
-    st = gemm_device<T>(s, rows, N, K, alpha, dA + r0 * dlda, dlda, dB, dldb, transB, beta,
-                        dC + r0 * dldc, dldc, false, 0);
-    PGB_CUDA(cudaEventRecord(ev_c[i], s));
-    PGB_CUDA(cudaStreamWaitEvent(rt->copy_out, ev_c[i], 0));
-    PGB_CUDA(copy_rows(C + r0 * ldc, ldc, dC + r0 * dldc, dldc, rows, N, cudaMemcpyDeviceToHost,
-                       rt->copy_out));
-  }
-  PGB_CUDA(cudaEventRecord(ev_done, rt->copy_out));
-  PGB_CUDA(cudaStreamWaitEvent(s, ev_done, 0));
-  PGB_CUDA(cudaFreeAsync(dA, s));
-  PGB_CUDA(cudaFreeAsync(dB, s));
-  PGB_CUDA(cudaFreeAsync(dC, s));
-  PGB_CUDA(cudaStreamSynchronize(rt->copy_in));
-  PGB_CUDA(cudaStreamSynchronize(s));
-  cudaEventDestroy(ev_start);
-  cudaEventDestroy(ev_done);
-  for (int i = 0; i < nb; i++) {
-    cudaEventDestroy(ev_in[i]);
-    cudaEventDestroy(ev_c[i]);
-  }
-  return st;
+      if (beta != (T)0)
+        PGB_CUDA(copy_rows(dC + r0 * dldc, dldc, C + r0 * ldc, ldc, rows, N, cudaMemcpyHostToDevice,
+                           rt->copy_in));
+      PGB_CUDA(cudaEventRecord(ev_in[i], rt->copy_in));
+    }
+    for (int i = 0; i < nb; i++) {
+      const int64_t r0 = i * rows_per, rows = (M - r0 < rows_per) ? (M - r0) : rows_per;
+      PGB_CUDA(cudaStreamWaitEvent(s, ev_in[i], 0));
+      // A block whose product failed is not copied back.
+      PGB_TRY(gemm_device<T>(s, rows, N, K, alpha, dA + r0 * dlda, dlda, dB, dldb, transB, beta,
+                             dC + r0 * dldc, dldc, false, 0));
+      PGB_CUDA(cudaEventRecord(ev_c[i], s));
+      PGB_CUDA(cudaStreamWaitEvent(rt->copy_out, ev_c[i], 0));
+      PGB_CUDA(copy_rows(C + r0 * ldc, ldc, dC + r0 * dldc, dldc, rows, N, cudaMemcpyDeviceToHost,
+                         rt->copy_out));
+    }
+    PGB_CUDA(cudaEventRecord(ev_done, rt->copy_out));
+    PGB_CUDA(cudaStreamWaitEvent(s, ev_done, 0));
+    return PGB200_OK;
+  };
+  const int32_t st = run();
+  const cudaError_t e1 = cudaStreamSynchronize(rt->copy_in);
+  const cudaError_t e2 = cudaStreamSynchronize(rt->copy_out);
+  const cudaError_t e3 = cudaStreamSynchronize(s);
+  for (int i = 0; i < nev; i++) cudaEventDestroy(ev[i]);
+  if (st != PGB200_OK) return st;
+  PGB_CUDA(e1);
+  PGB_CUDA(e2);
+  PGB_CUDA(e3);
+  return PGB200_OK;
 }
 
 template <typename T>
@@ -496,6 +500,7 @@ static int32_t gemm_entry(void *stream, int64_t M, int64_t N, int64_t K, T alpha
   const bool staged = sa.host || sb.host || sc.host;
   int32_t st = gemm_device<T>(s, M, N, K, alpha, sa.dev, sa.ld, sb.dev, sb.ld, transB, beta,
                               sc.dev, sc.ld, false, 0);
+  if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sc));
@@ -527,6 +532,7 @@ static int32_t syrk_entry(void *stream, int64_t N, int64_t K, int64_t row0, int6
   // product A[row0:row1,:] * A[0:row1,:]^T masked to j <= i.
   int32_t st = gemm_device<T>(s, row1 - row0, row1, K, alpha, sa.dev + row0 * sa.ld, sa.ld,
                               sa.dev, sa.ld, true, beta, sc.dev, sc.ld, true, row0);
+  if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sc));
   if (staged) PGB_CUDA(cudaStreamSynchronize(s));
@@ -556,6 +562,7 @@ static int32_t syr2k_entry(void *stream, int64_t N, int64_t K, T alpha, const T 
   if (st == PGB200_OK)
     st = gemm_device<T>(s, N, N, K, alpha, sa.dev, sa.ld, sb.dev, sb.ld, true, (T)1, sc.dev, sc.ld,
                         true, 0);
+  if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sc));
@@ -587,6 +594,7 @@ static int32_t matvec_entry(void *stream, int64_t M, int64_t N, const double *A,
   int32_t st = stream_matvec(s, M, N, sa.dev, sa.ld, alpha, beta, y1 ? sx1.dev : nullptr,
                              y1 ? sy1.dev : nullptr, y2 ? sx2.dev : nullptr,
                              y2 ? sy2.dev : nullptr);
+  if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sx1));
   PGB_TRY(finish(s, &sy1));
@@ -688,6 +696,7 @@ int32_t pgb200Dgemver(void *stream, int64_t N, double alpha, double beta, double
                       sx.host || sy.host || sz.host;
   int32_t st = stream_gemver(s, N, alpha, beta, sa.dev, sa.ld, su1.dev, sv1.dev, su2.dev, sv2.dev,
                              sw.dev, sx.dev, sy.dev, sz.dev);
+  if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &su1));
   PGB_TRY(finish(s, &sv1));
@@ -736,6 +745,7 @@ int32_t pgb200_kernel_2mm(int ni, int nj, int nk, int nl, double alpha, double b
   int32_t r = pgb200Dgemm(s, ni, nj, nk, alpha, sa.dev, sa.ld, sb.dev, sb.ld, 0.0, st.dev, st.ld);
   if (r == PGB200_OK)
     r = pgb200Dgemm(s, ni, nl, nj, 1.0, st.dev, st.ld, sc.dev, sc.ld, beta, sd.dev, sd.ld);
+  if (r != PGB200_OK) return r;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sc));
@@ -772,6 +782,7 @@ int32_t pgb200_kernel_3mm(int ni, int nj, int nk, int nl, int nm, double *E, con
     r = pgb200Dgemm(s, nj, nl, nm, 1.0, sc.dev, sc.ld, sd.dev, sd.ld, 0.0, sf.dev, sf.ld);
   if (r == PGB200_OK)
     r = pgb200Dgemm(s, ni, nl, nj, 1.0, se.dev, se.ld, sf.dev, sf.ld, 0.0, sg.dev, sg.ld);
+  if (r != PGB200_OK) return r;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sc));
@@ -797,6 +808,7 @@ int32_t pgb200_kernel_atax(int m, int n, const double *A, const double *x, doubl
   PGB_TRY(stage<double>(s, tmp, 1, m, m, false, true, &st));
   int32_t r = pgb200Dgemv(s, 0, m, n, 1.0, sa.dev, sa.ld, sx.dev, 0.0, st.dev);
   if (r == PGB200_OK) r = pgb200Dgemv(s, 1, m, n, 1.0, sa.dev, sa.ld, st.dev, 0.0, sy.dev);
+  if (r != PGB200_OK) return r;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sx));
   PGB_TRY(finish(s, &sy));
@@ -826,6 +838,7 @@ int32_t pgb200_kernel_gesummv(int n, double alpha, double beta, const double *A,
   int32_t r = pgb200Dgemv(s, 0, n, n, 1.0, sa.dev, sa.ld, sx.dev, 0.0, st.dev);  // tmp = A x
   if (r == PGB200_OK) r = pgb200Dgemv(s, 0, n, n, 1.0, sb.dev, sb.ld, sx.dev, 0.0, sy.dev);  // y = B x
   if (r == PGB200_OK) r = stream_axpby(s, n, alpha, st.dev, beta, sy.dev);  // y = alpha*tmp + beta*y
+  if (r != PGB200_OK) return r;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sx));

@@ -74,15 +74,14 @@ template <typename T>
 int32_t symm_device(cudaStream_t s, int64_t M, int64_t N, T alpha, const T *A, int64_t lda,
                     const T *B, int64_t ldb, T beta, T *C, int64_t ldc) {
   const int64_t lds = round_up(M, 4);
-  T *S = nullptr;
-  PGB_CUDA(cudaMallocAsync((void **)&S, (size_t)M * lds * sizeof(T), s));
+  PoolBuffer sbuf;
+  PGB_CUDA(sbuf.alloc((size_t)M * lds * sizeof(T), s));
+  T *S = sbuf.as<T>();
   const unsigned nt = (unsigned)((M + TILE - 1) / TILE);
   symmetrize_lower_kernel<T><<<dim3(nt, nt), dim3(TILE, TROWS), 0, s>>>(M, A, lda, S, lds);
   PGB_CUDA(cudaGetLastError());
   note_launch(PATH_STREAM);
-  const int32_t st = gemm_device<T>(s, M, N, M, alpha, S, lds, B, ldb, false, beta, C, ldc, false, 0);
-  PGB_CUDA(cudaFreeAsync(S, s));
-  return st;
+  return gemm_device<T>(s, M, N, M, alpha, S, lds, B, ldb, false, beta, C, ldc, false, 0);
 }
 
 template <typename T>
@@ -91,9 +90,10 @@ int32_t trmm_device(Runtime *rt, cudaStream_t s, int64_t M, int64_t N, T alpha, 
   // The inner extent is padded to a multiple of four (zero columns of U, zero
   // rows of the copy of B) so the tensor-core kernels' K rule always holds.
   const int64_t Kp = round_up(M, 4), ldu = Kp, ldo = round_up(N, 4);
-  T *U = nullptr, *Bold = nullptr;
-  PGB_CUDA(cudaMallocAsync((void **)&U, (size_t)M * ldu * sizeof(T), s));
-  PGB_CUDA(cudaMallocAsync((void **)&Bold, (size_t)Kp * ldo * sizeof(T), s));
+  PoolBuffer ubuf, bbuf;
+  PGB_CUDA(ubuf.alloc((size_t)M * ldu * sizeof(T), s));
+  PGB_CUDA(bbuf.alloc((size_t)Kp * ldo * sizeof(T), s));
+  T *U = ubuf.as<T>(), *Bold = bbuf.as<T>();
   const unsigned nti = (unsigned)((M + TILE - 1) / TILE), ntk = (unsigned)((Kp + TILE - 1) / TILE);
   unit_upper_from_lower_kernel<T><<<dim3(ntk, nti), dim3(TILE, TROWS), 0, s>>>(M, Kp, A, lda, U, ldu);
   PGB_CUDA(cudaGetLastError());
@@ -126,8 +126,6 @@ int32_t trmm_device(Runtime *rt, cudaStream_t s, int64_t M, int64_t N, T alpha, 
                           false, (T)0, B + r0 * ldb, ldb, false, 0);
     }
   }
-  PGB_CUDA(cudaFreeAsync(U, s));
-  PGB_CUDA(cudaFreeAsync(Bold, s));
   return st;
 }
 
@@ -150,6 +148,7 @@ int32_t symm_entry(void *stream, int64_t M, int64_t N, T alpha, const T *A, int6
   const bool staged = sa.host || sb.host || sc.host;
   const int32_t st =
       symm_device<T>(s, M, N, alpha, sa.dev, sa.ld, sb.dev, sb.ld, beta, sc.dev, sc.ld);
+  if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sc));
@@ -173,6 +172,7 @@ int32_t trmm_entry(void *stream, int64_t M, int64_t N, T alpha, const T *A, int6
   PGB_TRY(stage<T>(s, B, M, N, ldb, true, true, &sb));
   const bool staged = sa.host || sb.host;
   const int32_t st = trmm_device<T>(rt, s, M, N, alpha, sa.dev, sa.ld, sb.dev, sb.ld);
+  if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   if (staged) PGB_CUDA(cudaStreamSynchronize(s));
@@ -196,8 +196,9 @@ int32_t doitgen_entry(void *stream, int64_t R, int64_t P, double *A, int64_t lda
   // The product cannot be formed in place; the result goes to a second buffer
   // and from there to the caller's A (host array: by the copy-back itself).
   const int64_t ldo = round_up(P, 2);
-  double *out = nullptr;
-  PGB_CUDA(cudaMallocAsync((void **)&out, (size_t)R * ldo * sizeof(double), s));
+  PoolBuffer obuf;
+  PGB_CUDA(obuf.alloc((size_t)R * ldo * sizeof(double), s));
+  double *out = obuf.as<double>();
   const int32_t st = gemm_device<double>(s, R, P, P, 1.0, sa.dev, sa.ld, sc.dev, sc.ld, false, 0.0,
                                          out, ldo, false, 0);
   if (st == PGB200_OK) {
@@ -206,8 +207,8 @@ int32_t doitgen_entry(void *stream, int64_t R, int64_t P, double *A, int64_t lda
     if (sum)
       PGB_CUDA(cudaMemcpyAsync(sum, out + (R - 1) * ldo, P * sizeof(double), cudaMemcpyDefault, s));
   }
-  PGB_CUDA(cudaFreeAsync(out, s));
   const bool staged = sa.host || sc.host || is_host_pointer(sum);
+  if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sc));
   if (staged) PGB_CUDA(cudaStreamSynchronize(s));
