@@ -18,6 +18,8 @@
 // half-warp then read 128 contiguous bytes.  The innermost TMA coordinate is
 // always 0, so every copy starts on a 16-byte boundary.  Out-of-range rows,
 // columns and K are zero-filled by TMA; the epilogue masks the stores.
+#include <vector>
+
 #include "pgb200_internal.h"
 
 namespace pgb200 {
@@ -94,7 +96,9 @@ struct TileMap {
   // A is upper triangular (zero left of its diagonal): the K loop of tile row
   // tm starts at the diagonal block instead of 0.
   int a_upper;
-  __device__ int64_t first_kblock(int64_t tm) const { return a_upper ? (tm * BM) / BK : 0; }
+  __host__ __device__ int64_t first_kblock(int64_t tm) const {
+    return a_upper ? (tm * BM) / BK : 0;
+  }
   // Tile of CTA `cta` in its round-th turn.  Tiles come in descending K length
   // when A is triangular, so odd rounds hand them out in reverse CTA order
   // (each CTA's long and short tiles pair up); otherwise plain round-robin.
@@ -102,7 +106,7 @@ struct TileMap {
   __device__ int64_t index(int64_t round, int64_t cta, int64_t ctas) const {
     return round * ctas + ((a_upper && (round & 1)) ? ctas - 1 - cta : cta);
   }
-  __device__ void get(int64_t idx, int64_t *tm, int64_t *tn) const {
+  __host__ __device__ void get(int64_t idx, int64_t *tm, int64_t *tn) const {
     if (lower) {
       // idx = tm*(tm+1)/2 + tn with tn <= tm (BM == BN).
       int64_t r = (int64_t)((sqrt(8.0 * (double)idx + 1.0) - 1.0) * 0.5);
@@ -123,11 +127,30 @@ struct TileMap {
   }
 };
 
-template <bool TRANSB>
-__global__ void __launch_bounds__(THREADS, 1)
-dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                 int64_t M, int64_t N, int64_t K, double alpha, double beta,
-                 double *__restrict__ C, int64_t ldc, TileMap tiles, int32_t *status) {
+// The tiles of this CTA, in order: from the host-built schedule when SCHED,
+// else round-robin (reversed in odd rounds when A is triangular).  Returns
+// false when the CTA is done; *t < 0 means "no tile in this turn".
+template <bool SCHED>
+__device__ __forceinline__ bool next_tile(const TileMap &tiles, const TileSchedule *sched,
+                                          int64_t turn, int64_t *t) {
+  if (SCHED) {
+    const int64_t i = (int64_t)sched->off[blockIdx.x] + turn;
+    if (i >= (int64_t)sched->off[blockIdx.x + 1]) return false;
+    *t = sched->idx[i];
+    return true;
+  }
+  if (turn * gridDim.x >= tiles.total) return false;
+  const int64_t x = tiles.index(turn, blockIdx.x, gridDim.x);
+  *t = x < tiles.total ? x : -1;
+  return true;
+}
+
+template <bool TRANSB, bool SCHED>
+__device__ __forceinline__ void dmma_gemm_body(const CUtensorMap *mapA, const CUtensorMap *mapB,
+                                               int64_t M, int64_t N, int64_t K, double alpha,
+                                               double beta, double *__restrict__ C, int64_t ldc,
+                                               const TileMap &tiles, const TileSchedule *sched,
+                                               int32_t *status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * STAGES];
   // 1024-byte aligned ring base.
@@ -152,9 +175,10 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int64_t round = 0; round * gridDim.x < tiles.total && ok; round++) {
-        const int64_t t = tiles.index(round, blockIdx.x, gridDim.x);
-        if (t >= tiles.total) continue;
+      for (int64_t turn = 0; ok; turn++) {
+        int64_t t;
+        if (!next_tile<SCHED>(tiles, sched, turn, &t)) break;
+        if (t < 0) continue;
         int64_t tm, tn;
         tiles.get(t, &tm, &tn);
         for (int64_t kb = tiles.first_kblock(tm); kb < nkb; kb++) {
@@ -166,11 +190,11 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           const uint32_t dstA = ring + stage * STAGE_BYTES;
           const uint32_t dstB = dstA + A_STAGE_BYTES;
           mbar_expect_tx(full0 + 8 * stage, STAGE_BYTES);
-          tma_load_3d(dstA, &mapA, full0 + 8 * stage, 0, (int)(tm * BM), (int)(kb * (BK / 4)));
+          tma_load_3d(dstA, mapA, full0 + 8 * stage, 0, (int)(tm * BM), (int)(kb * (BK / 4)));
           if (TRANSB)
-            tma_load_3d(dstB, &mapB, full0 + 8 * stage, 0, (int)(tn * BN), (int)(kb * (BK / 4)));
+            tma_load_3d(dstB, mapB, full0 + 8 * stage, 0, (int)(tn * BN), (int)(kb * (BK / 4)));
           else
-            tma_load_3d(dstB, &mapB, full0 + 8 * stage, 0, (int)(kb * BK), (int)(tn * (BN / 4)));
+            tma_load_3d(dstB, mapB, full0 + 8 * stage, 0, (int)(kb * BK), (int)(tn * (BN / 4)));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -185,9 +209,10 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   const int g = lane >> 2, t4 = lane & 3;
   const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps -> 64 x 32 sub-tiles
   uint32_t stage = 0, phase = 0;
-  for (int64_t round = 0; round * gridDim.x < tiles.total; round++) {
-    const int64_t t = tiles.index(round, blockIdx.x, gridDim.x);
-    if (t >= tiles.total) continue;
+  for (int64_t turn = 0;; turn++) {
+    int64_t t;
+    if (!next_tile<SCHED>(tiles, sched, turn, &t)) break;
+    if (t < 0) continue;
     int64_t tm, tn;
     tiles.get(t, &tm, &tn);
     double acc[4][4][4];
@@ -280,6 +305,24 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   }
 }
 
+template <bool TRANSB>
+__global__ void __launch_bounds__(THREADS, 1)
+dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                 int64_t M, int64_t N, int64_t K, double alpha, double beta,
+                 double *__restrict__ C, int64_t ldc, TileMap tiles, int32_t *status) {
+  dmma_gemm_body<TRANSB, false>(&mapA, &mapB, M, N, K, alpha, beta, C, ldc, tiles, nullptr, status);
+}
+
+// Same kernel with its tiles taken from a host-built schedule (triangular A).
+__global__ void __launch_bounds__(THREADS, 1)
+dmma_gemm_sched_kernel(const __grid_constant__ CUtensorMap mapA,
+                       const __grid_constant__ CUtensorMap mapB, int64_t M, int64_t N, int64_t K,
+                       double alpha, double beta, double *__restrict__ C, int64_t ldc,
+                       TileMap tiles, const __grid_constant__ TileSchedule sched,
+                       int32_t *status) {
+  dmma_gemm_body<false, true>(&mapA, &mapB, M, N, K, alpha, beta, C, ldc, tiles, &sched, status);
+}
+
 }  // namespace
 
 int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha, const double *A,
@@ -332,6 +375,29 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
   int64_t ctas = rt->num_sms - (rt->cfg.reserve_sms > 0 ? rt->cfg.reserve_sms : 0);
   if (ctas < 1) ctas = 1;
   const unsigned grid = (unsigned)(tiles.total < ctas ? tiles.total : ctas);
+  // Triangular A: tiles differ in length.  With few tiles per CTA a static
+  // round-robin leaves SMs idle at the end (13 % at 4096 x 4096), so the tiles
+  // are handed out longest-first on the host when the table fits.
+  if (a_upper && !transB && !lower && tiles.total > (int64_t)grid) {
+    const int64_t nkb = (K + BK - 1) / BK;
+    std::vector<int64_t> cost((size_t)tiles.total);
+    for (int64_t t = 0; t < tiles.total; t++) {
+      int64_t tm, tn;
+      tiles.get(t, &tm, &tn);
+      const int64_t len = nkb - tiles.first_kblock(tm);
+      cost[(size_t)t] = (len > 0 ? len : 0) + 2;  // + the tile's epilogue
+    }
+    TileSchedule sched;
+    if (build_lpt_schedule(cost.data(), tiles.total, (int)grid, &sched)) {
+      PGB_CUDA(cudaFuncSetAttribute(dmma_gemm_sched_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      dmma_gemm_sched_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(mapA, mapB, M, N, K, alpha, beta, C,
+                                                               ldc, tiles, sched, rt->status_dev);
+      note_launch(PATH_DMMA);
+      PGB_CUDA(cudaGetLastError());
+      return PGB200_OK;
+    }
+  }
   if (transB) {
     PGB_CUDA(cudaFuncSetAttribute(dmma_gemm_kernel<true>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));

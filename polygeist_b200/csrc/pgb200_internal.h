@@ -70,6 +70,20 @@ int32_t encode_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank,
                           const uint64_t *strides_bytes, const uint32_t *box,
                           CUtensorMapSwizzle swizzle);
 
+// Static schedule for kernels whose tiles differ in length (triangular K
+// loops): the tile indices of every worker (a CTA, or a CTA pair), assigned
+// longest-processing-time-first on the host and passed by value as a kernel
+// parameter, so nothing is allocated or copied for it.
+struct TileSchedule {
+  static constexpr int MAX_TILES = 1408, MAX_WORKERS = 160;
+  uint16_t off[MAX_WORKERS + 1];  // tiles of worker w: idx[off[w]] .. idx[off[w+1]-1]
+  uint16_t idx[MAX_TILES];
+};
+// cost[t] > 0 is the relative length of tile t.  Tiles go, longest first (ties:
+// lowest index), to the worker with the least work so far (ties: lowest id).
+// Returns false when the problem does not fit the fixed-size table.
+bool build_lpt_schedule(const int64_t *cost, int64_t tiles, int workers, TileSchedule *out);
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // A caller array that may live on the host: staged to the device on demand.

@@ -8,6 +8,9 @@
 #include <mutex>
 #include <utility>
 
+#include <algorithm>
+#include <vector>
+
 #include "pgb200_internal.h"
 
 namespace pgb200 {
@@ -147,6 +150,32 @@ int32_t encode_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank,
     return PGB200_ERR_CUDA;
   }
   return PGB200_OK;
+}
+
+bool build_lpt_schedule(const int64_t *cost, int64_t tiles, int workers, TileSchedule *out) {
+  if (tiles < 0 || tiles > TileSchedule::MAX_TILES || workers < 1 ||
+      workers > TileSchedule::MAX_WORKERS)
+    return false;
+  std::vector<int32_t> order((size_t)tiles);
+  for (int64_t t = 0; t < tiles; t++) order[(size_t)t] = (int32_t)t;
+  std::stable_sort(order.begin(), order.end(),
+                   [&](int32_t a, int32_t b) { return cost[a] > cost[b]; });
+  std::vector<int64_t> load((size_t)workers, 0);
+  std::vector<std::vector<uint16_t>> mine((size_t)workers);
+  for (int32_t t : order) {
+    int w = 0;
+    for (int i = 1; i < workers; i++)
+      if (load[(size_t)i] < load[(size_t)w]) w = i;
+    load[(size_t)w] += cost[t];
+    mine[(size_t)w].push_back((uint16_t)t);
+  }
+  int64_t n = 0;
+  for (int w = 0; w < workers; w++) {
+    out->off[w] = (uint16_t)n;
+    for (uint16_t t : mine[(size_t)w]) out->idx[n++] = t;
+  }
+  for (int w = workers; w <= TileSchedule::MAX_WORKERS; w++) out->off[w] = (uint16_t)n;
+  return true;
 }
 
 bool is_host_pointer(const void *p) {

@@ -40,6 +40,8 @@
 // Every wait is time-bounded: on expiry the kernel records a code in the
 // host-visible status word, leaves its loops, frees its tensor memory and
 // returns.
+#include <vector>
+
 #include "pgb200_internal.h"
 
 namespace pgb200 {
@@ -853,6 +855,40 @@ __device__ __forceinline__ void tc2_commit_both(uint32_t bar) {
       : "memory");
 }
 
+// Optional host-built tile schedule of the triangular variant (an empty
+// parameter for the dense one).
+template <bool ON>
+struct SchedParam {};
+template <>
+struct SchedParam<true> {
+  int use;  // 0: round-robin with reversed odd rounds
+  TileSchedule s;
+};
+
+// Turn `it` of CTA pair `pair`: is there one, and which tile (-1: none this turn).
+template <bool A_UPPER>
+__device__ __forceinline__ bool p2_more(const SchedParam<A_UPPER> &sp, int64_t it, int64_t pair,
+                                        int64_t npairs, int64_t total) {
+  if constexpr (A_UPPER) {
+    if (sp.use) return (int64_t)sp.s.off[pair] + it < (int64_t)sp.s.off[pair + 1];
+    return it * npairs < total;
+  } else {
+    return it < total;
+  }
+}
+template <bool A_UPPER>
+__device__ __forceinline__ int64_t p2_tile(const SchedParam<A_UPPER> &sp, const Tiles &tiles,
+                                           int64_t it, int64_t pair, int64_t npairs,
+                                           int64_t total) {
+  if constexpr (A_UPPER) {
+    if (sp.use) return sp.s.idx[(int64_t)sp.s.off[pair] + it];
+    const int64_t x = tiles.index(it, pair, npairs);
+    return x < total ? x : -1;
+  } else {
+    return it;
+  }
+}
+
 template <bool B_MN, bool A_UPPER>
 __global__ void __launch_bounds__(THREADS, 1)
 tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
@@ -860,7 +896,8 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
                         const __grid_constant__ CUtensorMap mapBhi,
                         const __grid_constant__ CUtensorMap mapBlo, int64_t M, int64_t N,
                         int64_t K, float alpha, float beta, float *__restrict__ C, int64_t ldc,
-                        Tiles tiles, int chunk_kblocks, int32_t *status) {
+                        Tiles tiles, int chunk_kblocks,
+                        const __grid_constant__ SchedParam<A_UPPER> sp, int32_t *status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * P2_STAGES + 4];
   __shared__ uint32_t tmem_slot;
@@ -907,10 +944,10 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
         bool ok = true;
         const uint32_t leader_full0 = map_to_cta(full0, 0);
         TileCursor cur;
-        for (int64_t it = A_UPPER ? 0 : pair; (A_UPPER ? it * npairs < total : it < total) && ok;
+        for (int64_t it = A_UPPER ? 0 : pair; p2_more<A_UPPER>(sp, it, pair, npairs, total) && ok;
              it += A_UPPER ? 1 : npairs) {
-          const int64_t t = A_UPPER ? tiles.index(it, pair, npairs) : it;
-          if (A_UPPER && t >= total) continue;
+          const int64_t t = p2_tile<A_UPPER>(sp, tiles, it, pair, npairs, total);
+          if (A_UPPER && t < 0) continue;
           int64_t tm2, tn;
           cur.seek(tiles, t, &tm2, &tn);
           const int row_a = (int)(tm2 * 256 + rank * 128);
@@ -949,10 +986,10 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
         int64_t cc = 0;
         bool ok = true;
         TileCursor cur;
-        for (int64_t it = A_UPPER ? 0 : pair; (A_UPPER ? it * npairs < total : it < total) && ok;
+        for (int64_t it = A_UPPER ? 0 : pair; p2_more<A_UPPER>(sp, it, pair, npairs, total) && ok;
              it += A_UPPER ? 1 : npairs) {
-          const int64_t t = A_UPPER ? tiles.index(it, pair, npairs) : it;
-          if (A_UPPER && t >= total) continue;
+          const int64_t t = p2_tile<A_UPPER>(sp, tiles, it, pair, npairs, total);
+          if (A_UPPER && t < 0) continue;
           int64_t kb0 = 0;
           if (A_UPPER) {
             int64_t tm2, tn;
@@ -1016,10 +1053,10 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
     TileCursor cur;
     int64_t cc = 0;
     bool ok = true;
-    for (int64_t it = A_UPPER ? 0 : pair; (A_UPPER ? it * npairs < total : it < total) && ok;
+    for (int64_t it = A_UPPER ? 0 : pair; p2_more<A_UPPER>(sp, it, pair, npairs, total) && ok;
          it += A_UPPER ? 1 : npairs) {
-      const int64_t t = A_UPPER ? tiles.index(it, pair, npairs) : it;
-      if (A_UPPER && t >= total) continue;
+      const int64_t t = p2_tile<A_UPPER>(sp, tiles, it, pair, npairs, total);
+      if (A_UPPER && t < 0) continue;
       int64_t tm2, tn;
       cur.seek(tiles, t, &tm2, &tn);
       const int64_t nchunks =
@@ -1317,18 +1354,38 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     attr[0].val.clusterDim.z = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    auto launch2 = [&](auto kernel) -> int32_t {
+    auto launch2 = [&](auto kernel, const auto &sp) -> int32_t {
       PGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
       PGB_CUDA(cudaLaunchKernelEx(&lc, kernel, mAhi, mAlo, m2Bhi, m2Blo, M, N, K, alpha, beta, C, ldc,
-                                  t2, chunk, rt->status_dev));
+                                  t2, chunk, sp, rt->status_dev));
       return PGB200_OK;
     };
-    if (t2.a_upper)
-      PGB_TRY(b_mn ? launch2(tf32x3_gemm_2cta_kernel<true, true>)
-                   : launch2(tf32x3_gemm_2cta_kernel<false, true>));
-    else
-      PGB_TRY(b_mn ? launch2(tf32x3_gemm_2cta_kernel<true, false>)
-                   : launch2(tf32x3_gemm_2cta_kernel<false, false>));
+    if (t2.a_upper) {
+      // Tiles differ in length: hand them out longest-first when the table fits
+      // (same band walk as TileCursor::seek for a full product).
+      SchedParam<true> sp;
+      sp.use = 0;
+      if (t2.total > pairs) {
+        const int64_t nkb = (K + BK - 1) / BK;
+        std::vector<int64_t> cost((size_t)t2.total);
+        const int64_t per_group = TileCursor::G * t2.tiles_n;
+        for (int64_t t = 0; t < t2.total; t++) {
+          const int64_t grp = t / per_group, first = grp * TileCursor::G;
+          const int64_t rows =
+              (t2.tiles_m - first < TileCursor::G) ? (t2.tiles_m - first) : TileCursor::G;
+          const int64_t tm = first + (t - grp * per_group) % rows;
+          const int64_t len = nkb - (tm * 256) / BK;
+          cost[(size_t)t] = (len > 0 ? len : 0) + 1;
+        }
+        if (build_lpt_schedule(cost.data(), t2.total, (int)pairs, &sp.s)) sp.use = 1;
+      }
+      PGB_TRY(b_mn ? launch2(tf32x3_gemm_2cta_kernel<true, true>, sp)
+                   : launch2(tf32x3_gemm_2cta_kernel<false, true>, sp));
+    } else {
+      const SchedParam<false> sp;
+      PGB_TRY(b_mn ? launch2(tf32x3_gemm_2cta_kernel<true, false>, sp)
+                   : launch2(tf32x3_gemm_2cta_kernel<false, false>, sp));
+    }
     note_launch(PATH_TCGEN05);
     PGB_CUDA(cudaGetLastError());
     return PGB200_OK;

@@ -568,6 +568,68 @@ def test_symm_trmm_doitgen_device_pointers_on_a_stream():
     assert torch.equal(s_dev, A3[-1])
 
 
+def test_symm_trmm_doitgen_empty_and_rejected_arguments():
+    lib = pgb.load()
+    B = dev_fill(8, 6, torch.float64, 1, 0.0, 1.0)
+    B0 = B.clone()
+    p = B.data_ptr()
+    # empty extents: nothing is touched, null pointers are fine
+    assert lib.pgb200Dsymm(None, 0, 6, 1.5, None, 1, None, 6, 1.2, None, 6) == pgb.OK
+    assert lib.pgb200Dtrmm(None, 8, 0, 1.5, None, 8, None, 1) == pgb.OK
+    assert lib.pgb200Ddoitgen(None, 0, 6, None, 6, None, 6, None) == pgb.OK
+    # negative sizes, null operands, leading dimensions below the row length
+    assert lib.pgb200Dsymm(None, -1, 6, 1.5, p, 8, p, 6, 1.2, p, 6) == pgb.ERR_INVALID
+    assert lib.pgb200Dsymm(None, 8, 6, 1.5, None, 8, p, 6, 1.2, p, 6) == pgb.ERR_INVALID
+    assert lib.pgb200Dsymm(None, 8, 6, 1.5, p, 7, p, 6, 1.2, p, 6) == pgb.ERR_INVALID   # lda < M
+    assert lib.pgb200Dtrmm(None, 8, 6, 1.5, p, 8, p, 5) == pgb.ERR_INVALID              # ldb < N
+    assert lib.pgb200Strmm(None, 8, 6, 1.5, p, 8, None, 6) == pgb.ERR_INVALID
+    assert lib.pgb200Ddoitgen(None, 8, 6, p, 5, p, 6, None) == pgb.ERR_INVALID          # lda < NP
+    assert b"doitgen" in lib.pgb200GetLastErrorString()
+    sync_ok()
+    assert torch.equal(B, B0), "a rejected call must leave its arrays alone"
+    # a 1x1 triangular factor is the identity: B = alpha * B
+    A1 = torch.full((1, 1), float("nan"), dtype=torch.float64, device=DEV)
+    row = dev_fill(1, 6, torch.float64, 2, 0.0, 1.0)
+    r0 = row.clone()
+    pgb.trmm(1.5, A1, row)
+    sync_ok()
+    assert torch.equal(row, r0 * 1.5)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-12), (torch.float32, 1e-5)])
+def test_symm_trmm_large_against_row_samples(dtype, tol):
+    """4096-row operands: the triangular K loop runs over several rounds of
+    tiles (DMMA kernel for fp64, two-CTA tcgen05 kernel for fp32).  Sampled
+    rows are recomputed in float64 from the definition of each nest."""
+    m, n = 4096, 2048
+    A = dev_fill(m, m, dtype, 1, 0.0, 1.0)
+    B = dev_fill(m, n, dtype, 2, 0.0, 1.0)
+    Cm = dev_fill(m, n, dtype, 3, 0.0, 1.0)
+    hA, hB, hC = (t.cpu().numpy().astype(np.float64) for t in (A, B, Cm))
+    # poison what the nests never read
+    iu = torch.triu_indices(m, m, 1, device=DEV)
+    A_sym = A.clone()
+    A_sym[iu[0], iu[1]] = float("nan")
+    pgb.symm(1.5, A_sym, B, 1.2, Cm)
+    A_tri = A_sym.clone()
+    A_tri.fill_diagonal_(float("nan"))
+    Bt = B.clone()
+    pgb.trmm(1.5, A_tri, Bt)
+    sync_ok()
+    assert pgb.last_path() == (pgb.PATH_DMMA if dtype == torch.float64 else pgb.PATH_TCGEN05)
+    rows = np.unique(np.concatenate([[0, 1, 127, 128, 255, 256, m - 129, m - 2, m - 1],
+                                     np.random.default_rng(SEED).integers(0, m, 40)]))
+    L = np.tril(hA)                                     # lower triangle, diagonal included
+    gotC, gotB = Cm.cpu().numpy().astype(np.float64), Bt.cpu().numpy().astype(np.float64)
+    assert np.isfinite(gotC).all() and np.isfinite(gotB).all()
+    for i in rows:
+        s_row = np.concatenate([L[i, : i + 1], L[i + 1:, i]])          # row i of the symmetric S
+        ref_c = 1.2 * hC[i] + 1.5 * (s_row @ hB)
+        assert elementwise_rel(gotC[i], ref_c) <= tol, ("symm", i)
+        ref_b = 1.5 * (hB[i] + L[i + 1:, i] @ hB[i + 1:])
+        assert elementwise_rel(gotB[i], ref_b) <= tol, ("trmm", i)
+
+
 def test_plain_c_caller_runs_the_drop_ins(tmp_path):
     """The C ABI used from C: a PolyBench-style program calls the drop-ins on
     malloc'd arrays and checks them against its own loop nests."""
