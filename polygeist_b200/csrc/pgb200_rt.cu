@@ -9,6 +9,8 @@
 #include <utility>
 
 #include <algorithm>
+#include <functional>
+#include <queue>
 #include <vector>
 
 #include "pgb200_internal.h"
@@ -160,14 +162,17 @@ bool build_lpt_schedule(const int64_t *cost, int64_t tiles, int workers, TileSch
   for (int64_t t = 0; t < tiles; t++) order[(size_t)t] = (int32_t)t;
   std::stable_sort(order.begin(), order.end(),
                    [&](int32_t a, int32_t b) { return cost[a] > cost[b]; });
-  std::vector<int64_t> load((size_t)workers, 0);
+  // Min-heap of (work so far, worker id).
+  using Slot = std::pair<int64_t, int>;
+  std::priority_queue<Slot, std::vector<Slot>, std::greater<Slot>> heap;
+  for (int w = 0; w < workers; w++) heap.push({0, w});
   std::vector<std::vector<uint16_t>> mine((size_t)workers);
   for (int32_t t : order) {
-    int w = 0;
-    for (int i = 1; i < workers; i++)
-      if (load[(size_t)i] < load[(size_t)w]) w = i;
-    load[(size_t)w] += cost[t];
-    mine[(size_t)w].push_back((uint16_t)t);
+    Slot top = heap.top();
+    heap.pop();
+    mine[(size_t)top.second].push_back((uint16_t)t);
+    top.first += cost[t];
+    heap.push(top);
   }
   int64_t n = 0;
   for (int w = 0; w < workers; w++) {

@@ -88,3 +88,42 @@ def test_header_is_c99_and_a_c_program_links(tmp_path):
     exe = build_c_caller(tmp_path)
     out = subprocess.run([exe], check=True, capture_output=True, text=True).stdout
     assert "libpgb200 version" in out
+
+
+def test_longest_first_tile_schedule():
+    """The host-built schedule of the triangular products (an internal C++
+    function, reached through its exported symbol): every tile exactly once,
+    loads within one tile of each other, oversize problems refused."""
+    import subprocess
+    lib = pgb.load()
+    out = subprocess.run(["nm", "-D", "--defined-only", pgb.LIB_PATH], check=True,
+                         capture_output=True, text=True).stdout
+    names = [ln.split()[-1] for ln in out.splitlines() if "build_lpt_schedule" in ln]
+    assert len(names) == 1
+    fn = getattr(lib, names[0])
+    fn.restype = C.c_bool
+    fn.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
+    MAX_TILES, MAX_WORKERS = 1408, 160
+
+    class Sched(C.Structure):
+        _fields_ = [("off", C.c_uint16 * (MAX_WORKERS + 1)), ("idx", C.c_uint16 * MAX_TILES)]
+
+    rng = np.random.default_rng(3)
+    for tiles, workers in ((1024, 148), (256, 74), (149, 148), (7, 3), (0, 5)):
+        cost = np.sort(rng.integers(1, 260, tiles).astype(np.int64))[::-1].copy()
+        s = Sched()
+        assert fn(cost.ctypes.data, tiles, workers, C.addressof(s))
+        off = np.array(s.off[: workers + 1], dtype=np.int64)
+        assert off[0] == 0 and off[-1] == tiles and np.all(np.diff(off) >= 0)
+        idx = np.array(s.idx[:tiles], dtype=np.int64)
+        assert sorted(idx.tolist()) == list(range(tiles))
+        loads = np.array([cost[idx[off[w]:off[w + 1]]].sum() for w in range(workers)])
+        if tiles >= workers:
+            assert loads.max() - loads.min() <= cost.max()
+            # within a worker the tiles come longest first
+            for w in range(workers):
+                mine = cost[idx[off[w]:off[w + 1]]]
+                assert np.all(np.diff(mine) <= 0)
+    big = np.ones(MAX_TILES + 1, dtype=np.int64)
+    assert not fn(big.ctypes.data, MAX_TILES + 1, 148, C.addressof(Sched()))
+    assert not fn(big.ctypes.data, 10, MAX_WORKERS + 1, C.addressof(Sched()))
