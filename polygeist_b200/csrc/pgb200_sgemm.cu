@@ -287,6 +287,13 @@ struct Tiles {
   // starts at its diagonal block, and odd rounds hand tiles out in reverse
   // order so every pair gets long and short tiles alike.
   int a_upper;
+  // Split-K (one-CTA kernel, problems with few tiles): the K-blocks of a tile
+  // are dealt to `splits` CTAs, `kper` each; CTA (tile, sp) writes its partial
+  // product to partial[sp][M][ldp] and a second kernel adds them up in order.
+  int splits;
+  int64_t kper;
+  float *partial;
+  int64_t ldp;
   __device__ __forceinline__ int64_t first_kblock(int64_t tm) const {
     return a_upper ? (tm * bm) / BK : 0;
   }
@@ -355,7 +362,7 @@ struct TileCursor {
   }
 };
 
-template <bool B_MN, int TBN>
+template <bool B_MN, int TBN, bool SPLITK>
 __global__ void __launch_bounds__(THREADS, 1)
 tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
                    const __grid_constant__ CUtensorMap mapAlo,
@@ -409,6 +416,7 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
   // thread plus tensor-memory load buffers) grow to 232.
   const int64_t nkb = (K + BK - 1) / BK;
   const int64_t nchunks = (nkb + chunk_kblocks - 1) / chunk_kblocks;
+  const int64_t work = SPLITK ? tiles.total * tiles.splits : tiles.total;  // (tile, K range) items
 
   if (warp < FIRST_EPI_WARP) {
   // Register re-partition between the warpgroups: the producer/MMA group gives
@@ -421,10 +429,13 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
       TileCursor cur;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < tiles.total && ok; t += gridDim.x) {
+      for (int64_t w = blockIdx.x; w < work && ok; w += gridDim.x) {
+        const int64_t t = SPLITK ? w / tiles.splits : w;
+        const int64_t kb_lo = SPLITK ? (w % tiles.splits) * tiles.kper : 0;
+        const int64_t kb_hi = SPLITK ? (kb_lo + tiles.kper < nkb ? kb_lo + tiles.kper : nkb) : nkb;
         int64_t tm, tn;
         cur.seek(tiles, t, &tm, &tn);
-        for (int64_t kb = 0; kb < nkb; kb++) {
+        for (int64_t kb = kb_lo; kb < kb_hi; kb++) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) {
             report_status(status, 11, (int32_t)blockIdx.x);
             ok = false;
@@ -466,8 +477,11 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
       uint32_t stage = 0, phase = 0;
       int64_t cc = 0;  // chunks issued by this CTA so far
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < tiles.total && ok; t += gridDim.x) {
-        for (int64_t ch = 0; ch < nchunks && ok; ch++, cc++) {
+      for (int64_t w = blockIdx.x; w < work && ok; w += gridDim.x) {
+        const int64_t kb_lo = SPLITK ? (w % tiles.splits) * tiles.kper : 0;
+        const int64_t kb_hi = SPLITK ? (kb_lo + tiles.kper < nkb ? kb_lo + tiles.kper : nkb) : nkb;
+        const int64_t nch = SPLITK ? (kb_hi - kb_lo + chunk_kblocks - 1) / chunk_kblocks : nchunks;
+        for (int64_t ch = 0; ch < nch && ok; ch++, cc++) {
           const uint32_t buf = (uint32_t)(cc & 1);
           const uint32_t use = (uint32_t)((cc >> 1) & 1);
           if (!mbar_wait(acce0 + 8 * buf, use ^ 1)) {
@@ -477,8 +491,9 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
           }
           tc_fence_after();
           const uint32_t tmem_d = tmem_base + buf * BN;
-          const int64_t kb_end = (ch + 1) * chunk_kblocks < nkb ? (ch + 1) * chunk_kblocks : nkb;
-          for (int64_t kb = ch * chunk_kblocks; kb < kb_end; kb++) {
+          const int64_t kb_first = kb_lo + ch * chunk_kblocks;
+          const int64_t kb_end = kb_first + chunk_kblocks < kb_hi ? kb_first + chunk_kblocks : kb_hi;
+          for (int64_t kb = kb_first; kb < kb_end; kb++) {
             if (!mbar_wait(full0 + 8 * stage, phase)) {
               report_status(status, 13, (int32_t)blockIdx.x);
               ok = false;
@@ -492,7 +507,7 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
             const uint64_t blo = B_MN ? smem_desc_mn_sw128(sa + 2 * A_BYTES + B_BYTES)
                                       : smem_desc_sw64(sa + 2 * A_BYTES + B_BYTES);
             constexpr uint32_t idesc = B_MN ? IDESC_BMN : IDESC;
-            const bool first = (kb == ch * chunk_kblocks);
+            const bool first = (kb == kb_first);
 #pragma unroll
             for (int ks = 0; ks < BK / 8; ks++) {
               // K=8 step: +32 bytes inside a K-major swizzled row; one group of
@@ -523,13 +538,18 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
     TileCursor cur;
     int64_t cc = 0;
     bool ok = true;
-    for (int64_t t = blockIdx.x; t < tiles.total && ok; t += gridDim.x) {
+    for (int64_t w = blockIdx.x; w < work && ok; w += gridDim.x) {
+      const int64_t t = SPLITK ? w / tiles.splits : w;
+      const int64_t sp = SPLITK ? w % tiles.splits : 0;
+      const int64_t kb_lo = SPLITK ? sp * tiles.kper : 0;
+      const int64_t kb_hi = SPLITK ? (kb_lo + tiles.kper < nkb ? kb_lo + tiles.kper : nkb) : nkb;
+      const int64_t nch = SPLITK ? (kb_hi - kb_lo + chunk_kblocks - 1) / chunk_kblocks : nchunks;
       int64_t tm, tn;
       cur.seek(tiles, t, &tm, &tn);
       float acc[COLS];
 #pragma unroll
       for (int i = 0; i < COLS; i++) acc[i] = 0.0f;
-      if (beta != 0.0f) {
+      if (!SPLITK && beta != 0.0f) {
         // Pull this thread's part of the C tile towards L2 while the tensor
         // cores work, so the epilogue's loads do not wait on HBM.
         const int64_t pr = tm * BM + quarter * 32 + lane, pc = tn * BN + half * COLS;
@@ -540,7 +560,7 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
               asm volatile("prefetch.global.L2 [%0];" ::"l"(C + pr * ldc + pc + q * 32));
         }
       }
-      for (int64_t ch = 0; ch < nchunks && ok; ch++, cc++) {
+      for (int64_t ch = 0; ch < nch && ok; ch++, cc++) {
         const uint32_t buf = (uint32_t)(cc & 1);
         const uint32_t use = (uint32_t)((cc >> 1) & 1);
         if (!mbar_wait_backoff(accf0 + 8 * buf, use)) {
@@ -570,8 +590,14 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
       }
       if (!ok) break;
 
-      epilogue_store<COLS>(acc, epi_stage[ew], lane, tm * BM + quarter * 32, tn * BN + half * COLS,
-                           M, N, ldc, C, alpha, beta, tiles.lower != 0, tiles.row0);
+      if (SPLITK)  // raw partial product of this K range; scaled and added up afterwards
+        epilogue_store<COLS>(acc, epi_stage[ew], lane, tm * BM + quarter * 32,
+                             tn * BN + half * COLS, M, N, tiles.ldp,
+                             tiles.partial + sp * M * tiles.ldp, 1.0f, 0.0f, false, 0);
+      else
+        epilogue_store<COLS>(acc, epi_stage[ew], lane, tm * BM + quarter * 32,
+                             tn * BN + half * COLS, M, N, ldc, C, alpha, beta, tiles.lower != 0,
+                             tiles.row0);
     }
   }
 
@@ -582,6 +608,48 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(TMEM_COLS)
                  : "memory");
+  }
+}
+
+// C = beta*C + alpha*(P[0] + P[1] + ...), the partial products of a split-K
+// launch added in a fixed order (four columns per thread).
+constexpr int MAX_SPLITS = 8;
+__global__ void splitk_reduce_kernel(const float *__restrict__ P, int64_t ldp, int splits, int64_t M,
+                                     int64_t N, float alpha, float beta, float *__restrict__ C,
+                                     int64_t ldc) {
+  const int64_t quads = ldp / 4;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * quads) return;
+  const int64_t r = i / quads, c = (i - r * quads) * 4;
+  // All loads first (independent, up to MAX_SPLITS of them in flight), then the
+  // sum in split order.
+  float4 v[MAX_SPLITS];
+  const float *src = P + r * ldp + c;
+#pragma unroll
+  for (int sp = 0; sp < MAX_SPLITS; sp++)
+    if (sp < splits) v[sp] = __ldcs(reinterpret_cast<const float4 *>(src + (int64_t)sp * M * ldp));
+  float old[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  float *dst = C + r * ldc + c;
+  if (beta != 0.0f) {
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+      if (c + j < N) old[j] = dst[j];
+  }
+  float4 sum = v[0];
+#pragma unroll
+  for (int sp = 1; sp < MAX_SPLITS; sp++)
+    if (sp < splits) {
+      sum.x += v[sp].x;
+      sum.y += v[sp].y;
+      sum.z += v[sp].z;
+      sum.w += v[sp].w;
+    }
+  const float part[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    if (c + j >= N) break;
+    const float o = alpha * part[j];
+    dst[j] = (beta != 0.0f) ? fmaf(beta, old[j], o) : o;
   }
 }
 
@@ -793,13 +861,6 @@ __global__ void __launch_bounds__(128, 1) tf32_probe_kernel(int iters, int32_t *
 // ===========================================================================
 namespace {
 
-constexpr int P2_BNH = 128;                                  // B columns held per CTA
-constexpr int P2_B_BYTES = P2_BNH * BK * 4;                  // 8 KiB per plane tile
-constexpr int P2_STAGE_BYTES = 2 * A_BYTES + 2 * P2_B_BYTES; // 32 KiB per CTA
-constexpr int P2_STAGES = 6;
-constexpr uint32_t P2_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(256 >> 3) << 17) |
-                              ((uint32_t)(256 >> 4) << 24);
-
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -889,7 +950,7 @@ __device__ __forceinline__ int64_t p2_tile(const SchedParam<A_UPPER> &sp, const 
   }
 }
 
-template <bool B_MN, bool A_UPPER>
+template <bool B_MN, bool A_UPPER, int PN>
 __global__ void __launch_bounds__(THREADS, 1)
 tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
                         const __grid_constant__ CUtensorMap mapAlo,
@@ -898,6 +959,16 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
                         int64_t K, float alpha, float beta, float *__restrict__ C, int64_t ldc,
                         Tiles tiles, int chunk_kblocks,
                         const __grid_constant__ SchedParam<A_UPPER> sp, int32_t *status) {
+  // Pair tile of 256 rows x PN columns (256, or 128 for problems with few
+  // tiles); each CTA holds PN/2 of the B columns.
+  static_assert(PN == 256 || PN == 128, "pair tile width");
+  constexpr int P2_BNH = PN / 2;
+  constexpr int P2_B_BYTES = P2_BNH * BK * 4;
+  constexpr int P2_STAGE_BYTES = 2 * A_BYTES + 2 * P2_B_BYTES;  // 32 or 24 KiB per CTA
+  constexpr int P2_STAGES = (192 * 1024) / P2_STAGE_BYTES;      // 6 or 8
+  constexpr uint32_t P2_IDESC = (1u << 4) | (2u << 7) | (2u << 10) |
+                                ((uint32_t)(PN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+  constexpr int COLS = PN / 2;  // columns per drain thread
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * P2_STAGES + 4];
   __shared__ uint32_t tmem_slot;
@@ -909,7 +980,7 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int64_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-  const int64_t total = tiles.total;  // pair tiles of 256 x 256 (tiles.bm == tiles.bn == 256)
+  const int64_t total = tiles.total;  // pair tiles of 256 x PN (tiles.bm == 256, tiles.bn == PN)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P2_STAGES; s++) {
@@ -951,7 +1022,7 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
           int64_t tm2, tn;
           cur.seek(tiles, t, &tm2, &tn);
           const int row_a = (int)(tm2 * 256 + rank * 128);
-          const int col_b = (int)(tn * 256 + rank * P2_BNH);
+          const int col_b = (int)(tn * PN + rank * P2_BNH);
           for (int64_t kb = A_UPPER ? tiles.first_kblock(tm2) : 0; kb < nkb; kb++) {
             if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) {
               report_status(status, 31, (int32_t)blockIdx.x);
@@ -1006,7 +1077,7 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
               break;
             }
             tc_fence_after();
-            const uint32_t tmem_d = tmem_base + buf * 256;
+            const uint32_t tmem_d = tmem_base + buf * PN;
             const int64_t kb_first = kb0 + ch * chunk_kblocks;
             const int64_t kb_end = kb_first + chunk_kblocks < nkb ? kb_first + chunk_kblocks : nkb;
             for (int64_t kb = kb_first; kb < kb_end; kb++) {
@@ -1062,13 +1133,13 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
       const int64_t nchunks =
           (nkb - (A_UPPER ? tiles.first_kblock(tm2) : 0) + chunk_kblocks - 1) / chunk_kblocks;
       const int64_t r_base = tm2 * 256 + rank * 128 + quarter * 32;
-      const int64_t cb = tn * 256 + half * 128;
-      float acc[128];
+      const int64_t cb = tn * PN + half * COLS;
+      float acc[COLS];
 #pragma unroll
-      for (int i = 0; i < 128; i++) acc[i] = 0.0f;
+      for (int i = 0; i < COLS; i++) acc[i] = 0.0f;
       if (beta != 0.0f && r_base + lane < M) {
 #pragma unroll
-        for (int q = 0; q < 4; q++)
+        for (int q = 0; q < COLS / 32; q++)
           if (cb + q * 32 < N)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(C + (r_base + lane) * ldc + cb + q * 32));
       }
@@ -1082,9 +1153,9 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
         }
         tc_fence_after();
         const uint32_t taddr =
-            tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256 + (uint32_t)(half * 128);
+            tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * PN + (uint32_t)(half * COLS);
 #pragma unroll
-        for (int j = 0; j < 4; j += 2) {
+        for (int j = 0; j < COLS / 32; j += 2) {
           uint32_t v0[32], v1[32];
           tc_ld32(taddr + j * 32, v0);
           tc_ld32(taddr + j * 32 + 32, v1);
@@ -1099,7 +1170,7 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
         if (lane == 0) mbar_arrive_cluster(leader_acce0 + 8 * buf);
       }
       if (!ok) break;
-      epilogue_store<128>(acc, epi_stage[ew], lane, r_base, cb, M, N, ldc, C, alpha, beta,
+      epilogue_store<COLS>(acc, epi_stage[ew], lane, r_base, cb, M, N, ldc, C, alpha, beta,
                           tiles.lower != 0, tiles.row0);
     }
   }
@@ -1197,18 +1268,48 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   // products transpose B once, otherwise use it in place.
   const bool b_mn = !transB && b_raw && (M < 12288 || rt->cfg.reserved[1] == 1);
 
-  // Scratch layout (floats): [B lo][B hi?][A lo?][A hi?]
+  // Tile width: 256 columns normally.  When 256-wide tiles would leave more
+  // than half of the SMs without a tile, either the K range of every tile is
+  // split over several CTAs (each keeps the full-rate N = 256 MMA shape; an
+  // M128 MMA takes 128 cycles whatever its N, so narrow tiles waste the tensor
+  // core) or, when K is too short for that, 64-column tiles are used.
+  const int chunk =
+      rt->cfg.sgemm_chunk_kblocks > 0 ? rt->cfg.sgemm_chunk_kblocks : DEFAULT_CHUNK_KBLOCKS;
+  const int64_t tiles256 = ((M + BM - 1) / BM) * ((N + 255) / 256);
+  const int64_t nkb_all = (K + BK - 1) / BK;
+  int bn = (tiles256 * 2 <= rt->num_sms) ? 64 : 256;
+  int splits = 1;
+  int64_t kper = nkb_all;
+  if (bn == 64 && !lower && rt->cfg.reserved[0] != 4) {
+    int64_t sp = rt->num_sms / tiles256;       // CTAs available per tile
+    const int64_t by_k = nkb_all / (2 * chunk);  // at least two chunks per split
+    if (sp > by_k) sp = by_k;
+    if (sp > MAX_SPLITS) sp = MAX_SPLITS;
+    if (sp >= 2) {
+      kper = ((nkb_all + sp - 1) / sp + chunk - 1) / chunk * chunk;
+      splits = (int)((nkb_all + kper - 1) / kper);
+      if (splits >= 2)
+        bn = 256;
+      else
+        splits = 1;
+    }
+  }
+  const int64_t ldp = (N + 3) / 4 * 4;
+  const size_t part_n = splits > 1 ? (size_t)splits * M * ldp : 0;
+
+  // Scratch layout (floats): [B lo][B hi?][A lo?][A hi?][split-K partials?]
   const size_t b_lo_n = b_mn ? (size_t)K * Np : (size_t)N * Kp;
   const bool b_inplace = b_mn || (transB && b_raw);  // B serves as its own hi part
   const size_t b_hi_n = b_inplace ? 0 : (size_t)N * Kp;
   const size_t a_lo_n = shared_planes ? 0 : (size_t)M * Kp;
   const size_t a_hi_n = (shared_planes || a_raw) ? 0 : (size_t)M * Kp;
   void *ws = nullptr;
-  PGB_TRY(get_workspace(s, (b_lo_n + b_hi_n + a_lo_n + a_hi_n) * sizeof(float), &ws));
+  PGB_TRY(get_workspace(s, (b_lo_n + b_hi_n + a_lo_n + a_hi_n + part_n) * sizeof(float), &ws));
   float *Blo = static_cast<float *>(ws);
   float *Bhi_pl = Blo + b_lo_n;
   float *Alo_pl = Bhi_pl + b_hi_n;
   float *Ahi_pl = Alo_pl + a_lo_n;
+  float *partial = Ahi_pl + a_hi_n;
 
   const int64_t cap = (int64_t)rt->num_sms * 8;
   auto grid_for = [&](int64_t total) {
@@ -1271,10 +1372,6 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   CUtensorMap mAhi, mAlo, mBhi, mBlo;
   PGB_TRY(make_plane_map(&mAhi, Ahi, M, K, ahi_ld, BM));
   PGB_TRY(make_plane_map(&mAlo, Alo, M, K, Kp, BM));
-  // Tile width: 256 columns normally; 64 when 256-wide tiles would leave more
-  // than half of the SMs without a tile.
-  const int64_t tiles256 = ((M + BM - 1) / BM) * ((N + 255) / 256);
-  const int bn = (tiles256 * 2 <= rt->num_sms) ? 64 : 256;
   const bool bhi_blocked = b_mn && (N % 32) == 0;
   if (b_mn) {
     if (bhi_blocked)
@@ -1295,6 +1392,10 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   tiles.row0 = row0;
   tiles.lower = lower ? 1 : 0;
   tiles.a_upper = 0;  // a hint only the two-CTA kernel takes; the product is the same without it
+  tiles.splits = splits;
+  tiles.kper = kper;
+  tiles.partial = partial;
+  tiles.ldp = ldp;
   if (lower) {
     int64_t total = 0;
     for (int64_t tm = 0; tm < tiles.tiles_m; tm++) {
@@ -1305,29 +1406,31 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   } else {
     tiles.total = tiles.tiles_m * tiles.tiles_n;
   }
-  int chunk = rt->cfg.sgemm_chunk_kblocks > 0 ? rt->cfg.sgemm_chunk_kblocks : DEFAULT_CHUNK_KBLOCKS;
   int64_t ctas = rt->num_sms - (rt->cfg.reserve_sms > 0 ? rt->cfg.reserve_sms : 0);
   if (ctas < 1) ctas = 1;
-  const unsigned grid = (unsigned)(tiles.total < ctas ? tiles.total : ctas);
+  const int64_t work = tiles.total * splits;
+  const unsigned grid = (unsigned)(work < ctas ? work : ctas);
   // Large full products: the two-CTA kernel (256x256 tiles on SM pairs).
   // Measured against the one-CTA kernel: 8192^3 4.01-4.18 vs 4.45 ms, 16384^3
   // 36.7-38.1 vs 40.5-40.8 ms, 32768^3 354-356 vs 423-443 ms (same GPU, back to
   // back).  reserved[0] == 2 switches it off.
-  const bool two_cta = bn == 256 && M >= 512 && (!b_mn || bhi_blocked) && rt->cfg.reserved[0] != 2;
+  const int pn = 256;  // pair tile width (128 also works: measured slower than split-K where it applied)
+  const bool two_cta = bn == 256 && splits == 1 && M >= 512 && (!b_mn || bhi_blocked) &&
+                       rt->cfg.reserved[0] != 2;
   if (two_cta) {
     CUtensorMap m2Bhi, m2Blo;
     if (b_mn) {
-      PGB_TRY(make_nmajor_map_blocked(&m2Bhi, Bhi, K, N, bhi_ld, P2_BNH));
-      PGB_TRY(make_nmajor_map_blocked(&m2Blo, Blo, K, Np, Np, P2_BNH));
+      PGB_TRY(make_nmajor_map_blocked(&m2Bhi, Bhi, K, N, bhi_ld, pn / 2));
+      PGB_TRY(make_nmajor_map_blocked(&m2Blo, Blo, K, Np, Np, pn / 2));
     } else {
-      PGB_TRY(make_plane_map(&m2Bhi, Bhi, N, K, bhi_ld, P2_BNH));
-      PGB_TRY(make_plane_map(&m2Blo, Blo, N, K, Kp, P2_BNH));
+      PGB_TRY(make_plane_map(&m2Bhi, Bhi, N, K, bhi_ld, pn / 2));
+      PGB_TRY(make_plane_map(&m2Blo, Blo, N, K, Kp, pn / 2));
     }
     Tiles t2 = tiles;
     t2.bm = 256;
-    t2.bn = 256;
+    t2.bn = pn;
     t2.tiles_m = (M + 255) / 256;
-    t2.tiles_n = (N + 255) / 256;
+    t2.tiles_n = (N + pn - 1) / pn;
     t2.a_upper = (a_upper && !lower) ? 1 : 0;
     if (lower) {
       int64_t tot = 0;
@@ -1379,12 +1482,12 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
         }
         if (build_lpt_schedule(cost.data(), t2.total, (int)pairs, &sp.s)) sp.use = 1;
       }
-      PGB_TRY(b_mn ? launch2(tf32x3_gemm_2cta_kernel<true, true>, sp)
-                   : launch2(tf32x3_gemm_2cta_kernel<false, true>, sp));
+      PGB_TRY(b_mn ? launch2(tf32x3_gemm_2cta_kernel<true, true, 256>, sp)
+                   : launch2(tf32x3_gemm_2cta_kernel<false, true, 256>, sp));
     } else {
       const SchedParam<false> sp;
-      PGB_TRY(b_mn ? launch2(tf32x3_gemm_2cta_kernel<true, false>, sp)
-                   : launch2(tf32x3_gemm_2cta_kernel<false, false>, sp));
+      PGB_TRY(b_mn ? launch2(tf32x3_gemm_2cta_kernel<true, false, 256>, sp)
+                   : launch2(tf32x3_gemm_2cta_kernel<false, false, 256>, sp));
     }
     note_launch(PATH_TCGEN05);
     PGB_CUDA(cudaGetLastError());
@@ -1396,10 +1499,20 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
                                              tiles, chunk, bhi_blk, rt->status_dev);
     return PGB200_OK;
   };
-  if (b_mn && bn == 256) PGB_TRY(launch(tf32x3_gemm_kernel<true, 256>, bhi_blocked ? 1 : 0));
-  if (b_mn && bn == 64) PGB_TRY(launch(tf32x3_gemm_kernel<true, 64>, bhi_blocked ? 1 : 0));
-  if (!b_mn && bn == 256) PGB_TRY(launch(tf32x3_gemm_kernel<false, 256>, 0));
-  if (!b_mn && bn == 64) PGB_TRY(launch(tf32x3_gemm_kernel<false, 64>, 0));
+  if (splits > 1) {
+    PGB_TRY(b_mn ? launch(tf32x3_gemm_kernel<true, 256, true>, bhi_blocked ? 1 : 0)
+                 : launch(tf32x3_gemm_kernel<false, 256, true>, 0));
+    const int64_t items = M * (ldp / 4);
+    splitk_reduce_kernel<<<(unsigned)((items + 127) / 128), 128, 0, s>>>(partial, ldp, splits, M, N,
+                                                                         alpha, beta, C, ldc);
+    note_launch(PATH_TCGEN05);
+  } else if (b_mn) {
+    PGB_TRY(bn == 256 ? launch(tf32x3_gemm_kernel<true, 256, false>, bhi_blocked ? 1 : 0)
+                      : launch(tf32x3_gemm_kernel<true, 64, false>, bhi_blocked ? 1 : 0));
+  } else {
+    PGB_TRY(bn == 256 ? launch(tf32x3_gemm_kernel<false, 256, false>, 0)
+                      : launch(tf32x3_gemm_kernel<false, 64, false>, 0));
+  }
   note_launch(PATH_TCGEN05);
   PGB_CUDA(cudaGetLastError());
   return PGB200_OK;

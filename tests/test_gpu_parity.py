@@ -239,6 +239,39 @@ def test_sgemm_matches_oracle(M, N, K):
     assert elementwise_rel(got, seq) <= 1e-5
 
 
+@pytest.mark.parametrize("M,N,K,beta", [(512, 512, 2048, 1.2), (256, 384, 1000, 0.0),
+                                         (1000, 1100, 1200, 1.2), (130, 250, 4100, 1.2)])
+def test_sgemm_split_k(M, N, K, beta):
+    """Few tiles, long K: the K-blocks of each tile are dealt to several CTAs and
+    the partial products are added in a fixed order (split, product, reduce: 3
+    launches).  Ragged edges in all three extents; beta == 0 must not read C;
+    two runs give the same bits; the result agrees with the unsplit kernel."""
+    l0 = pgb.launch_count()
+    got, truth, seq = _sgemm_case(M, N, K, beta)
+    # 3 input fills + operand planes (one launch, two when B has to be transposed)
+    # + split-K product + reduce
+    assert pgb.launch_count() - l0 in (6, 7)
+    assert pgb.last_path() == pgb.PATH_TCGEN05
+    assert elementwise_rel(got, truth) <= 1e-5
+    if K <= 2048:
+        assert elementwise_rel(got, seq) <= 1e-5
+    again, _, _ = _sgemm_case(M, N, K, beta)
+    assert np.array_equal(got, again)
+    if beta == 0.0:
+        A = dev_fill(M, K, torch.float32, 1, 0.0, 1.0)
+        B = dev_fill(K, N, torch.float32, 2, 0.0, 1.0)
+        Cn = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+        pgb.gemm(1.5, A, B, 0.0, Cn)
+        sync_ok()
+        assert np.array_equal(Cn.cpu().numpy(), got)
+    pgb.init(sgemm_two_cta=4)   # split-K off
+    try:
+        unsplit, _, _ = _sgemm_case(M, N, K, beta)
+    finally:
+        pgb.init()
+    assert elementwise_rel(got, unsplit) <= 1e-5
+
+
 def test_sgemm_config0_1024():
     """configs[0]: fp32 M=N=K=1024, uniform [0,1), alpha=1.5, beta=1.2."""
     got, truth, seq = _sgemm_case(1024, 1024, 1024)
