@@ -96,6 +96,13 @@ struct TileMap {
   // A is upper triangular (zero left of its diagonal): the K loop of tile row
   // tm starts at the diagonal block instead of 0.
   int a_upper;
+  // Split-K (problems with few tiles): the K-blocks of a tile are dealt to
+  // `splits` CTAs, `kper` each; work item w = tile * splits + sp writes its raw
+  // partial product to partial[sp][M][ldp], added up by a second kernel.
+  int splits;
+  int64_t kper;
+  double *partial;
+  int64_t ldp;
   __host__ __device__ int64_t first_kblock(int64_t tm) const {
     return a_upper ? (tm * BM) / BK : 0;
   }
@@ -132,20 +139,20 @@ struct TileMap {
 // false when the CTA is done; *t < 0 means "no tile in this turn".
 template <bool SCHED>
 __device__ __forceinline__ bool next_tile(const TileMap &tiles, const TileSchedule *sched,
-                                          int64_t turn, int64_t *t) {
+                                          int64_t work, int64_t turn, int64_t *t) {
   if (SCHED) {
     const int64_t i = (int64_t)sched->off[blockIdx.x] + turn;
     if (i >= (int64_t)sched->off[blockIdx.x + 1]) return false;
     *t = sched->idx[i];
     return true;
   }
-  if (turn * gridDim.x >= tiles.total) return false;
+  if (turn * gridDim.x >= work) return false;
   const int64_t x = tiles.index(turn, blockIdx.x, gridDim.x);
-  *t = x < tiles.total ? x : -1;
+  *t = x < work ? x : -1;
   return true;
 }
 
-template <bool TRANSB, bool SCHED>
+template <bool TRANSB, bool SCHED, bool SPLITK>
 __device__ __forceinline__ void dmma_gemm_body(const CUtensorMap *mapA, const CUtensorMap *mapB,
                                                int64_t M, int64_t N, int64_t K, double alpha,
                                                double beta, double *__restrict__ C, int64_t ldc,
@@ -169,6 +176,7 @@ __device__ __forceinline__ void dmma_gemm_body(const CUtensorMap *mapA, const CU
   __syncthreads();
 
   const int64_t nkb = (K + BK - 1) / BK;
+  const int64_t work = SPLITK ? tiles.total * tiles.splits : tiles.total;  // (tile, K range) items
 
   if (warp == CONSUMER_WARPS) {
     // ------------------------------ producer ------------------------------
@@ -176,12 +184,14 @@ __device__ __forceinline__ void dmma_gemm_body(const CUtensorMap *mapA, const CU
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int64_t turn = 0; ok; turn++) {
-        int64_t t;
-        if (!next_tile<SCHED>(tiles, sched, turn, &t)) break;
-        if (t < 0) continue;
+        int64_t w;
+        if (!next_tile<SCHED>(tiles, sched, work, turn, &w)) break;
+        if (w < 0) continue;
         int64_t tm, tn;
-        tiles.get(t, &tm, &tn);
-        for (int64_t kb = tiles.first_kblock(tm); kb < nkb; kb++) {
+        tiles.get(SPLITK ? w / tiles.splits : w, &tm, &tn);
+        const int64_t kb_lo = SPLITK ? (w % tiles.splits) * tiles.kper : tiles.first_kblock(tm);
+        const int64_t kb_hi = SPLITK ? (kb_lo + tiles.kper < nkb ? kb_lo + tiles.kper : nkb) : nkb;
+        for (int64_t kb = kb_lo; kb < kb_hi; kb++) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) {
             report_status(status, 1, (int32_t)blockIdx.x);
             ok = false;
@@ -210,11 +220,15 @@ __device__ __forceinline__ void dmma_gemm_body(const CUtensorMap *mapA, const CU
   const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps -> 64 x 32 sub-tiles
   uint32_t stage = 0, phase = 0;
   for (int64_t turn = 0;; turn++) {
-    int64_t t;
-    if (!next_tile<SCHED>(tiles, sched, turn, &t)) break;
-    if (t < 0) continue;
+    int64_t w;
+    if (!next_tile<SCHED>(tiles, sched, work, turn, &w)) break;
+    if (w < 0) continue;
     int64_t tm, tn;
-    tiles.get(t, &tm, &tn);
+    tiles.get(SPLITK ? w / tiles.splits : w, &tm, &tn);
+    const int sp = SPLITK ? (int)(w % tiles.splits) : 0;
+    const int kb_lo = SPLITK ? sp * (int)tiles.kper : (int)tiles.first_kblock(tm);
+    const int kb_hi = SPLITK ? (kb_lo + (int)tiles.kper < (int)nkb ? kb_lo + (int)tiles.kper : (int)nkb)
+                             : (int)nkb;
     double acc[4][4][4];
 #pragma unroll
     for (int i = 0; i < 4; i++)
@@ -223,7 +237,7 @@ __device__ __forceinline__ void dmma_gemm_body(const CUtensorMap *mapA, const CU
 #pragma unroll
         for (int r = 0; r < 4; r++) acc[i][j][r] = 0.0;
 
-    for (int64_t kb = tiles.first_kblock(tm); kb < nkb; kb++) {
+    for (int kb = kb_lo; kb < kb_hi; kb++) {
       if (!mbar_wait(full0 + 8 * stage, phase)) {
         report_status(status, 2, (int32_t)blockIdx.x);
         return;
@@ -261,10 +275,14 @@ __device__ __forceinline__ void dmma_gemm_body(const CUtensorMap *mapA, const CU
       }
     }
 
-    // Epilogue: C = alpha*acc + beta*C; each thread owns pairs of adjacent
-    // columns (16-byte accesses when C allows it).
+    // Epilogue: C = alpha*acc + beta*C (split-K: the raw partial product to
+    // scratch); each thread owns pairs of adjacent columns (16-byte accesses
+    // when the destination allows it).
+    double *const Cw = SPLITK ? tiles.partial + (int64_t)sp * M * tiles.ldp : C;
+    const int64_t ldw = SPLITK ? tiles.ldp : ldc;
+    const double aw = SPLITK ? 1.0 : alpha, bw = SPLITK ? 0.0 : beta;
     const int64_t m_base = tm * BM + wm * 64, n_base = tn * BN + wn * 32;
-    const bool vec_ok = ((ldc & 1) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+    const bool vec_ok = ((ldw & 1) == 0) && ((reinterpret_cast<uintptr_t>(Cw) & 15) == 0);
 #pragma unroll
     for (int mt = 0; mt < 4; mt++)
 #pragma unroll
@@ -278,26 +296,26 @@ __device__ __forceinline__ void dmma_gemm_body(const CUtensorMap *mapA, const CU
           // lower: columns beyond the diagonal of this row are not touched.
           const int64_t lim = tiles.lower ? (r < N - 1 ? r : N - 1) : N - 1;
           if (c > lim) continue;
-          double v0 = alpha * acc[mt][nt][2 * h], v1 = alpha * acc[mt][nt][2 * h + 1];
-          double *dst = C + r * ldc + c;
+          double v0 = aw * acc[mt][nt][2 * h], v1 = aw * acc[mt][nt][2 * h + 1];
+          double *dst = Cw + r * ldw + c;
           if (c + 1 <= lim) {
             if (vec_ok) {
-              if (beta != 0.0) {
+              if (bw != 0.0) {
                 const double2 old = *reinterpret_cast<const double2 *>(dst);
-                v0 = fma(beta, old.x, v0);
-                v1 = fma(beta, old.y, v1);
+                v0 = fma(bw, old.x, v0);
+                v1 = fma(bw, old.y, v1);
               }
               *reinterpret_cast<double2 *>(dst) = make_double2(v0, v1);
             } else {
-              if (beta != 0.0) {
-                v0 = fma(beta, dst[0], v0);
-                v1 = fma(beta, dst[1], v1);
+              if (bw != 0.0) {
+                v0 = fma(bw, dst[0], v0);
+                v1 = fma(bw, dst[1], v1);
               }
               dst[0] = v0;
               dst[1] = v1;
             }
           } else {
-            if (beta != 0.0) v0 = fma(beta, dst[0], v0);
+            if (bw != 0.0) v0 = fma(bw, dst[0], v0);
             dst[0] = v0;
           }
         }
@@ -310,7 +328,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  int64_t M, int64_t N, int64_t K, double alpha, double beta,
                  double *__restrict__ C, int64_t ldc, TileMap tiles, int32_t *status) {
-  dmma_gemm_body<TRANSB, false>(&mapA, &mapB, M, N, K, alpha, beta, C, ldc, tiles, nullptr, status);
+  dmma_gemm_body<TRANSB, false, false>(&mapA, &mapB, M, N, K, alpha, beta, C, ldc, tiles, nullptr,
+                                       status);
 }
 
 // Same kernel with its tiles taken from a host-built schedule (triangular A).
@@ -320,7 +339,52 @@ dmma_gemm_sched_kernel(const __grid_constant__ CUtensorMap mapA,
                        double alpha, double beta, double *__restrict__ C, int64_t ldc,
                        TileMap tiles, const __grid_constant__ TileSchedule sched,
                        int32_t *status) {
-  dmma_gemm_body<false, true>(&mapA, &mapB, M, N, K, alpha, beta, C, ldc, tiles, &sched, status);
+  dmma_gemm_body<false, true, false>(&mapA, &mapB, M, N, K, alpha, beta, C, ldc, tiles, &sched,
+                                     status);
+}
+
+// Same kernel over (tile, K range) work items; partial products go to scratch.
+template <bool TRANSB>
+__global__ void __launch_bounds__(THREADS, 1)
+dmma_gemm_splitk_kernel(const __grid_constant__ CUtensorMap mapA,
+                        const __grid_constant__ CUtensorMap mapB, int64_t M, int64_t N, int64_t K,
+                        TileMap tiles, int32_t *status) {
+  dmma_gemm_body<TRANSB, false, true>(&mapA, &mapB, M, N, K, 1.0, 0.0, nullptr, 0, tiles, nullptr,
+                                      status);
+}
+
+// C = beta*C + alpha*(P[0] + P[1] + ...) in split order, two columns per thread.
+constexpr int MAX_SPLITS = 16;
+__global__ void dsplitk_reduce_kernel(const double *__restrict__ P, int64_t ldp, int splits,
+                                      int64_t M, int64_t N, double alpha, double beta,
+                                      double *__restrict__ C, int64_t ldc) {
+  const int64_t pairs = ldp / 2;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * pairs) return;
+  const int64_t r = i / pairs, c = (i - r * pairs) * 2;
+  if (c >= N) return;
+  double2 v[MAX_SPLITS];
+  const double *src = P + r * ldp + c;
+#pragma unroll
+  for (int sp = 0; sp < MAX_SPLITS; sp++)
+    if (sp < splits) v[sp] = __ldcs(reinterpret_cast<const double2 *>(src + (int64_t)sp * M * ldp));
+  double *dst = C + r * ldc + c;
+  const bool two = c + 1 < N;
+  double old0 = 0.0, old1 = 0.0;
+  if (beta != 0.0) {
+    old0 = dst[0];
+    if (two) old1 = dst[1];
+  }
+  double2 sum = v[0];
+#pragma unroll
+  for (int sp = 1; sp < MAX_SPLITS; sp++)
+    if (sp < splits) {
+      sum.x += v[sp].x;
+      sum.y += v[sp].y;
+    }
+  const double o0 = alpha * sum.x, o1 = alpha * sum.y;
+  dst[0] = (beta != 0.0) ? fma(beta, old0, o0) : o0;
+  if (two) dst[1] = (beta != 0.0) ? fma(beta, old1, o1) : o1;
 }
 
 }  // namespace
@@ -365,6 +429,10 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
   tiles.tiles_n = (N + BN - 1) / BN;
   tiles.lower = lower ? 1 : 0;
   tiles.a_upper = a_upper ? 1 : 0;
+  tiles.splits = 1;
+  tiles.kper = 0;
+  tiles.partial = nullptr;
+  tiles.ldp = 0;
   if (lower) {
     // Square lower-triangular update only (row0 == 0, M == N).
     if (M != N) return PGB200_ERR_UNSUPPORTED;
@@ -375,6 +443,45 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
   int64_t ctas = rt->num_sms - (rt->cfg.reserve_sms > 0 ? rt->cfg.reserve_sms : 0);
   if (ctas < 1) ctas = 1;
   const unsigned grid = (unsigned)(tiles.total < ctas ? tiles.total : ctas);
+  // Few tiles (less than half of the SMs would get one): deal the K-blocks of
+  // every tile to several CTAs (at least 8 K-blocks each) and add the partial
+  // products afterwards in split order.  A tile's time is K / (one SM's DMMA
+  // rate) however many SMs idle beside it.
+  if (!lower && !a_upper && tiles.total * 2 <= ctas && rt->cfg.reserved[0] != 4) {
+    const int64_t nkb = (K + BK - 1) / BK;
+    int64_t sp = ctas / tiles.total;
+    if (sp > nkb / 8) sp = nkb / 8;
+    if (sp > MAX_SPLITS) sp = MAX_SPLITS;
+    if (sp >= 2) {
+      const int64_t kper = (nkb + sp - 1) / sp;
+      const int splits = (int)((nkb + kper - 1) / kper);
+      const int64_t ldp = (N + 1) / 2 * 2;
+      void *ws = nullptr;
+      PGB_TRY(get_workspace(s, (size_t)splits * M * ldp * sizeof(double), &ws));
+      tiles.splits = splits;
+      tiles.kper = kper;
+      tiles.partial = static_cast<double *>(ws);
+      tiles.ldp = ldp;
+      const int64_t work = tiles.total * splits;
+      const unsigned g2 = (unsigned)(work < ctas ? work : ctas);
+      if (transB) {
+        PGB_TRY(ensure_dynamic_smem((const void *)dmma_gemm_splitk_kernel<true>, SMEM_BYTES));
+        dmma_gemm_splitk_kernel<true><<<g2, THREADS, SMEM_BYTES, s>>>(mapA, mapB, M, N, K, tiles,
+                                                                       rt->status_dev);
+      } else {
+        PGB_TRY(ensure_dynamic_smem((const void *)dmma_gemm_splitk_kernel<false>, SMEM_BYTES));
+        dmma_gemm_splitk_kernel<false><<<g2, THREADS, SMEM_BYTES, s>>>(mapA, mapB, M, N, K, tiles,
+                                                                        rt->status_dev);
+      }
+      PGB_CUDA(cudaGetLastError());
+      const int64_t items = M * (ldp / 2);
+      dsplitk_reduce_kernel<<<(unsigned)((items + 127) / 128), 128, 0, s>>>(
+          tiles.partial, ldp, splits, M, N, alpha, beta, C, ldc);
+      PGB_CUDA(cudaGetLastError());
+      note_launch(PATH_DMMA, 2);
+      return PGB200_OK;
+    }
+  }
   // Triangular A: tiles differ in length.  With few tiles per CTA a static
   // round-robin leaves SMs idle at the end (13 % at 4096 x 4096), so the tiles
   // are handed out longest-first on the host when the table fits.
@@ -389,8 +496,7 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
     }
     TileSchedule sched;
     if (build_lpt_schedule(cost.data(), tiles.total, (int)grid, &sched)) {
-      PGB_CUDA(cudaFuncSetAttribute(dmma_gemm_sched_kernel,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      PGB_TRY(ensure_dynamic_smem((const void *)dmma_gemm_sched_kernel, SMEM_BYTES));
       dmma_gemm_sched_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(mapA, mapB, M, N, K, alpha, beta, C,
                                                                ldc, tiles, sched, rt->status_dev);
       note_launch(PATH_DMMA);
@@ -399,13 +505,11 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
     }
   }
   if (transB) {
-    PGB_CUDA(cudaFuncSetAttribute(dmma_gemm_kernel<true>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    PGB_TRY(ensure_dynamic_smem((const void *)dmma_gemm_kernel<true>, SMEM_BYTES));
     dmma_gemm_kernel<true><<<grid, THREADS, SMEM_BYTES, s>>>(mapA, mapB, M, N, K, alpha, beta, C,
                                                               ldc, tiles, rt->status_dev);
   } else {
-    PGB_CUDA(cudaFuncSetAttribute(dmma_gemm_kernel<false>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    PGB_TRY(ensure_dynamic_smem((const void *)dmma_gemm_kernel<false>, SMEM_BYTES));
     dmma_gemm_kernel<false><<<grid, THREADS, SMEM_BYTES, s>>>(mapA, mapB, M, N, K, alpha, beta, C,
                                                                ldc, tiles, rt->status_dev);
   }

@@ -84,6 +84,10 @@ struct TileSchedule {
 // Returns false when the problem does not fit the fixed-size table.
 bool build_lpt_schedule(const int64_t *cost, int64_t tiles, int workers, TileSchedule *out);
 
+// Raises a kernel's dynamic shared-memory limit once per (device, kernel); the
+// attribute call is not free and the kernels are launched many times.
+int32_t ensure_dynamic_smem(const void *kernel, int bytes);
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // A caller array that may live on the host: staged to the device on demand.

@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <functional>
 #include <queue>
+#include <set>
 #include <vector>
 
 #include "pgb200_internal.h"
@@ -151,6 +152,19 @@ int32_t encode_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank,
     set_error("'cuTensorMapEncodeTiled' failed with 'CUresult %d'", (int)r);
     return PGB200_ERR_CUDA;
   }
+  return PGB200_OK;
+}
+
+static std::mutex g_attr_mu;
+static std::set<std::pair<int, const void *>> g_attr_done;
+
+int32_t ensure_dynamic_smem(const void *kernel, int bytes) {
+  int dev = 0;
+  PGB_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(g_attr_mu);
+  if (g_attr_done.count({dev, kernel})) return PGB200_OK;
+  PGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  g_attr_done.insert({dev, kernel});
   return PGB200_OK;
 }
 
@@ -328,6 +342,10 @@ int32_t pgb200Shutdown(void) {
     delete kv.second;
   }
   g_rt.clear();
+  {
+    std::lock_guard<std::mutex> lk2(g_attr_mu);
+    g_attr_done.clear();
+  }
   cudaSetDevice(cur);
   return PGB200_OK;
 }

@@ -1458,7 +1458,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     lc.attrs = attr;
     lc.numAttrs = 1;
     auto launch2 = [&](auto kernel, const auto &sp) -> int32_t {
-      PGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      PGB_TRY(ensure_dynamic_smem((const void *)kernel, SMEM_BYTES));
       PGB_CUDA(cudaLaunchKernelEx(&lc, kernel, mAhi, mAlo, m2Bhi, m2Blo, M, N, K, alpha, beta, C, ldc,
                                   t2, chunk, sp, rt->status_dev));
       return PGB200_OK;
@@ -1494,7 +1494,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     return PGB200_OK;
   }
   auto launch = [&](auto kernel, int bhi_blk) -> int32_t {
-    PGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    PGB_TRY(ensure_dynamic_smem((const void *)kernel, SMEM_BYTES));
     kernel<<<grid, THREADS, SMEM_BYTES, s>>>(mAhi, mAlo, mBhi, mBlo, M, N, K, alpha, beta, C, ldc,
                                              tiles, chunk, bhi_blk, rt->status_dev);
     return PGB200_OK;

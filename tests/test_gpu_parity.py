@@ -85,6 +85,39 @@ def test_dgemm_matches_oracle(M, N, K, pa, pb, pc, fast, beta):
         assert torch.isnan(Cm._base[:, N:]).all(), "padding columns must keep their NaN fill"
 
 
+@pytest.mark.parametrize("M,N,K,beta", [(512, 512, 512, 1.2), (1000, 1100, 1200, 1.2),
+                                         (256, 384, 4096, 0.0), (130, 252, 1028, 1.2)])
+def test_dgemm_split_k(M, N, K, beta):
+    """Few tiles: the K-blocks of every tile are dealt to several CTAs and the
+    partial products added in split order (two launches).  Checked against the
+    loop nest, for bit-identical repeats, and against the unsplit kernel."""
+    A = dev_fill(M, K, torch.float64, 1, -1.0, 1.0)
+    B = dev_fill(K, N, torch.float64, 2, -1.0, 1.0)
+    C0 = dev_fill(M, N, torch.float64, 3, -1.0, 1.0)
+    hA, hB, hC = (np.ascontiguousarray(t.cpu().numpy()) for t in (A, B, C0))
+
+    def run():
+        Cm = C0.clone() if beta != 0.0 else torch.full_like(C0, float("nan"))
+        l0 = pgb.launch_count()
+        pgb.gemm(1.5, A, B, beta, Cm)
+        sync_ok()
+        return Cm.cpu().numpy(), pgb.launch_count() - l0
+
+    got, launches = run()
+    assert pgb.last_path() == pgb.PATH_DMMA and launches == 2
+    ref = pbo.gemm(1.5, beta, hC.copy(), hA, hB)
+    assert normwise(got, ref) <= 1e-12
+    assert backward_gemm(got, ref, 1.5, beta, hA, hB, hC) <= 1e-13
+    again, _ = run()
+    assert np.array_equal(got, again)
+    pgb.init(sgemm_two_cta=4)   # split-K off
+    try:
+        unsplit, launches = run()
+    finally:
+        pgb.init()
+    assert launches == 1 and normwise(got, unsplit) <= 1e-13
+
+
 def test_dgemm_empty_and_k0():
     A = torch.zeros((4, 0), dtype=torch.float64, device=DEV)
     B = torch.zeros((0, 8), dtype=torch.float64, device=DEV)
