@@ -353,23 +353,24 @@ dmma_gemm_splitk_kernel(const __grid_constant__ CUtensorMap mapA,
                                       status);
 }
 
-// C = beta*C + alpha*(P[0] + P[1] + ...) in split order, two columns per thread.
+// C = beta*C + alpha*(P[0] + P[1] + ...) in split order, two columns per thread
+// (lower: only columns up to the diagonal).
 constexpr int MAX_SPLITS = 16;
 __global__ void dsplitk_reduce_kernel(const double *__restrict__ P, int64_t ldp, int splits,
                                       int64_t M, int64_t N, double alpha, double beta,
-                                      double *__restrict__ C, int64_t ldc) {
+                                      double *__restrict__ C, int64_t ldc, int lower) {
   const int64_t pairs = ldp / 2;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= M * pairs) return;
   const int64_t r = i / pairs, c = (i - r * pairs) * 2;
-  if (c >= N) return;
+  if (c >= N || (lower && c > r)) return;  // lower: nothing right of the diagonal is touched
   double2 v[MAX_SPLITS];
   const double *src = P + r * ldp + c;
 #pragma unroll
   for (int sp = 0; sp < MAX_SPLITS; sp++)
     if (sp < splits) v[sp] = __ldcs(reinterpret_cast<const double2 *>(src + (int64_t)sp * M * ldp));
   double *dst = C + r * ldc + c;
-  const bool two = c + 1 < N;
+  const bool two = c + 1 < N && (!lower || c + 1 <= r);
   double old0 = 0.0, old1 = 0.0;
   if (beta != 0.0) {
     old0 = dst[0];
@@ -447,7 +448,7 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
   // every tile to several CTAs (at least 8 K-blocks each) and add the partial
   // products afterwards in split order.  A tile's time is K / (one SM's DMMA
   // rate) however many SMs idle beside it.
-  if (!lower && !a_upper && tiles.total * 2 <= ctas && rt->cfg.reserved[0] != 4) {
+  if (!a_upper && tiles.total * 2 <= ctas && rt->cfg.reserved[0] != 4) {
     const int64_t nkb = (K + BK - 1) / BK;
     int64_t sp = ctas / tiles.total;
     if (sp > nkb / 8) sp = nkb / 8;
@@ -476,7 +477,7 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
       PGB_CUDA(cudaGetLastError());
       const int64_t items = M * (ldp / 2);
       dsplitk_reduce_kernel<<<(unsigned)((items + 127) / 128), 128, 0, s>>>(
-          tiles.partial, ldp, splits, M, N, alpha, beta, C, ldc);
+          tiles.partial, ldp, splits, M, N, alpha, beta, C, ldc, lower ? 1 : 0);
       PGB_CUDA(cudaGetLastError());
       note_launch(PATH_DMMA, 2);
       return PGB200_OK;

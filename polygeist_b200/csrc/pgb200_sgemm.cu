@@ -616,11 +616,14 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
 constexpr int MAX_SPLITS = 8;
 __global__ void splitk_reduce_kernel(const float *__restrict__ P, int64_t ldp, int splits, int64_t M,
                                      int64_t N, float alpha, float beta, float *__restrict__ C,
-                                     int64_t ldc) {
+                                     int64_t ldc, int lower, int64_t row0) {
   const int64_t quads = ldp / 4;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= M * quads) return;
   const int64_t r = i / quads, c = (i - r * quads) * 4;
+  // lower: row r is absolute row r + row0 and owns columns up to it.
+  const int64_t lim = lower ? (r + row0 < N - 1 ? r + row0 : N - 1) : N - 1;
+  if (c > lim) return;
   // All loads first (independent, up to MAX_SPLITS of them in flight), then the
   // sum in split order.
   float4 v[MAX_SPLITS];
@@ -633,7 +636,7 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ P, int64_t ldp, i
   if (beta != 0.0f) {
 #pragma unroll
     for (int j = 0; j < 4; j++)
-      if (c + j < N) old[j] = dst[j];
+      if (c + j <= lim) old[j] = dst[j];
   }
   float4 sum = v[0];
 #pragma unroll
@@ -647,7 +650,7 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ P, int64_t ldp, i
   const float part[4] = {sum.x, sum.y, sum.z, sum.w};
 #pragma unroll
   for (int j = 0; j < 4; j++) {
-    if (c + j >= N) break;
+    if (c + j > lim) break;
     const float o = alpha * part[j];
     dst[j] = (beta != 0.0f) ? fmaf(beta, old[j], o) : o;
   }
@@ -1280,7 +1283,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   int bn = (tiles256 * 2 <= rt->num_sms) ? 64 : 256;
   int splits = 1;
   int64_t kper = nkb_all;
-  if (bn == 64 && !lower && rt->cfg.reserved[0] != 4) {
+  if (bn == 64 && rt->cfg.reserved[0] != 4) {
     int64_t sp = rt->num_sms / tiles256;       // CTAs available per tile
     const int64_t by_k = nkb_all / (2 * chunk);  // at least two chunks per split
     if (sp > by_k) sp = by_k;
@@ -1503,8 +1506,8 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     PGB_TRY(b_mn ? launch(tf32x3_gemm_kernel<true, 256, true>, bhi_blocked ? 1 : 0)
                  : launch(tf32x3_gemm_kernel<false, 256, true>, 0));
     const int64_t items = M * (ldp / 4);
-    splitk_reduce_kernel<<<(unsigned)((items + 127) / 128), 128, 0, s>>>(partial, ldp, splits, M, N,
-                                                                         alpha, beta, C, ldc);
+    splitk_reduce_kernel<<<(unsigned)((items + 127) / 128), 128, 0, s>>>(
+        partial, ldp, splits, M, N, alpha, beta, C, ldc, lower ? 1 : 0, row0);
     note_launch(PATH_TCGEN05);
   } else if (b_mn) {
     PGB_TRY(bn == 256 ? launch(tf32x3_gemm_kernel<true, 256, false>, bhi_blocked ? 1 : 0)

@@ -234,7 +234,8 @@ def test_mvt_large_row_subset():
 
 # --------------------------------------------------------------------------- syrk
 @pytest.mark.parametrize("n,k,pa,pc", [(128, 64, 0, 0), (300, 100, 0, 0), (257, 36, 2, 4),
-                                        (45, 33, 0, 0), (1, 4, 0, 0)])
+                                        (45, 33, 0, 0), (1, 4, 0, 0),
+                                        (384, 1024, 0, 0), (1200, 1000, 0, 0)])  # split-K
 def test_dsyrk_matches_oracle(n, k, pa, pc):
     A = dev_fill(n, k, torch.float64, 1, -1.0, 1.0, ld=k + pa)
     Cm = dev_fill(n, n, torch.float64, 2, -1.0, 1.0, ld=n + pc)
@@ -312,7 +313,7 @@ def test_sgemm_config0_1024():
     assert elementwise_rel(got, seq) <= 1e-5
 
 
-@pytest.mark.parametrize("n,k", [(128, 64), (300, 100), (45, 33), (512, 1024)])
+@pytest.mark.parametrize("n,k", [(128, 64), (300, 100), (45, 33), (512, 1024), (1200, 1000)])
 def test_ssyrk_matches_oracle(n, k):
     A = dev_fill(n, k, torch.float32, 1, 0.0, 1.0)
     Cm = dev_fill(n, n, torch.float32, 2, 0.0, 1.0)
