@@ -46,7 +46,7 @@ enum {
  * defaults.  A zero field means "default". */
 typedef struct pgb200Config {
   int32_t log_level;          /* 0 quiet (errors only), 1 info, 2 per call   */
-  int32_t sgemm_chunk_kblocks;/* 3xTF32: K-blocks (of 32) accumulated in the
+  int32_t sgemm_chunk_kblocks;/* 3xTF32: K-blocks (of 16) accumulated in the
                                  tensor-core accumulator before it is drained
                                  into fp32 registers; bounds the truncation
                                  bias of tensor-core accumulation             */
@@ -58,7 +58,12 @@ typedef struct pgb200Config {
                                  of the next operand chunk) can run beside them */
   int32_t reserved[3];        /* [0] == 2: never use the two-CTA (cta_group::2)
                                  fp32 kernel (default: whenever a product has
-                                 >= 512 rows and enough tiles)               */
+                                 >= 512 rows and enough tiles);
+                                 [0] == 4: never split K over several CTAs
+                                 (default: whenever fewer than half of the SMs
+                                 would get a tile and K is long enough);
+                                 [1] == 1: fp32 row-major B always used in
+                                 place, whatever M                            */
 } pgb200Config;
 
 /* Runtime life cycle.  Replaces nothing in the reference one-to-one; plays the
