@@ -65,6 +65,14 @@ def test_polybench_mirror_rejects_wrong_extents():
     with pytest.raises(ValueError):
         polybench.kernel_mvt(4, np.zeros(4), np.zeros(4), np.zeros(4), np.zeros(4),
                              np.zeros((4, 4), dtype=np.float32))
+    with pytest.raises(ValueError):   # A of symm is m x m
+        polybench.kernel_symm(4, 6, 1.5, 1.2, np.zeros((4, 6)), np.zeros((4, 6)), np.zeros((4, 6)))
+    with pytest.raises(ValueError):   # B of trmm is m x n, passed transposed
+        polybench.kernel_trmm(4, 6, 1.5, np.zeros((4, 4)), np.zeros((6, 4)))
+    with pytest.raises(ValueError):   # a strided view is not the C array
+        polybench.kernel_trmm(4, 6, 1.5, np.zeros((4, 4)), np.zeros((4, 12))[:, ::2])
+    with pytest.raises(ValueError):   # doitgen: A is nr x nq x np
+        polybench.kernel_doitgen(2, 3, 4, np.zeros((6, 4)), np.zeros((4, 4)), np.zeros(4))
 
 
 def build_c_caller(tmp_path):
