@@ -334,6 +334,7 @@ def test_ssyrk_matches_oracle(n, k):
 @pytest.mark.parametrize("n,k,blocks", [
     (384, 128, [(0, 100), (100, 256), (256, 384)]),            # one-CTA kernel, 128x64 tiles
     (2048, 256, [(0, 640), (640, 1408), (1408, 2048)]),        # two-CTA kernel, row0 != 0
+    (640, 1024, [(0, 200), (200, 640)]),                       # split-K with row0 != 0, ragged block
 ])
 def test_ssyrk_row_block_equals_rows_of_full_update(n, k, blocks):
     A = dev_fill(n, k, torch.float32, 1, 0.0, 1.0)
