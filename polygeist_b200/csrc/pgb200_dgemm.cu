@@ -166,6 +166,10 @@ __device__ __forceinline__ void dmma_gemm_body(const CUtensorMap *mapA, const CU
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  if (threadIdx.x == 32) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(mapA) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(mapB) : "memory");
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
       mbar_init(full0 + 8 * s, 1);

@@ -118,6 +118,10 @@ __device__ __forceinline__ void report_status(int32_t *status, int32_t code, int
   s[0] = code;
   __threadfence_system();
 }
+// Pulls a tensor map into the descriptor cache ahead of its first use.
+__device__ __forceinline__ void prefetch_tensor_map(const CUtensorMap *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
                                             int c0, int c1) {
   asm volatile(
@@ -388,6 +392,12 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
   const uint32_t accf0 = smem_u32(&bars[2 * STAGES]), acce0 = smem_u32(&bars[2 * STAGES + 2]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  if (threadIdx.x == 64) {  // an otherwise idle warp
+    prefetch_tensor_map(&mapAhi);
+    prefetch_tensor_map(&mapAlo);
+    prefetch_tensor_map(&mapBhi);
+    prefetch_tensor_map(&mapBlo);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
       mbar_init(full0 + 8 * s, 1);
@@ -985,6 +995,12 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
   const int64_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
   const int64_t total = tiles.total;  // pair tiles of 256 x PN (tiles.bm == 256, tiles.bn == PN)
 
+  if (threadIdx.x == 64) {  // an otherwise idle warp
+    prefetch_tensor_map(&mapAhi);
+    prefetch_tensor_map(&mapAlo);
+    prefetch_tensor_map(&mapBhi);
+    prefetch_tensor_map(&mapBlo);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < P2_STAGES; s++) {
       mbar_init(full0 + 8 * s, 1);   // the leader's arrive.expect_tx (bytes of both CTAs)
