@@ -308,7 +308,7 @@ struct Tiles {
 };
 
 // Columns tiles of tile-row tm that intersect j <= i (lower) or all of them.
-__device__ __forceinline__ int64_t row_tiles(const Tiles &t, int64_t tm) {
+__host__ __device__ __forceinline__ int64_t row_tiles(const Tiles &t, int64_t tm) {
   if (!t.lower) return t.tiles_n;
   const int64_t last_col = t.row0 + tm * t.bm + t.bm - 1;  // largest j of the tile row
   const int64_t c = last_col / t.bn + 1;
@@ -326,7 +326,8 @@ __device__ __forceinline__ int64_t row_tiles(const Tiles &t, int64_t tm) {
 struct TileCursor {
   static constexpr int64_t G = 16;
   int64_t band = 0, before = 0;  // tiles in bands < band (lower only)
-  __device__ __forceinline__ void seek(const Tiles &t, int64_t idx, int64_t *otm, int64_t *otn) {
+  __host__ __device__ __forceinline__ void seek(const Tiles &t, int64_t idx, int64_t *otm,
+                                                int64_t *otn) {
     if (!t.lower) {
       const int64_t per_group = G * t.tiles_n;
       const int64_t grp = idx / per_group;
@@ -365,6 +366,14 @@ struct TileCursor {
     }
   }
 };
+
+// Number of tiles the cursor enumerates (host side; the kernels get it in
+// Tiles::total).
+inline int64_t count_tiles(const Tiles &t) {
+  int64_t total = 0;
+  for (int64_t tm = 0; tm < t.tiles_m; tm++) total += row_tiles(t, tm);
+  return total;
+}
 
 template <bool B_MN, int TBN, bool SPLITK>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -1415,16 +1424,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   tiles.kper = kper;
   tiles.partial = partial;
   tiles.ldp = ldp;
-  if (lower) {
-    int64_t total = 0;
-    for (int64_t tm = 0; tm < tiles.tiles_m; tm++) {
-      const int64_t c = (row0 + tm * BM + BM - 1) / bn + 1;
-      total += c < tiles.tiles_n ? c : tiles.tiles_n;
-    }
-    tiles.total = total;
-  } else {
-    tiles.total = tiles.tiles_m * tiles.tiles_n;
-  }
+  tiles.total = count_tiles(tiles);
   int64_t ctas = rt->num_sms - (rt->cfg.reserve_sms > 0 ? rt->cfg.reserve_sms : 0);
   if (ctas < 1) ctas = 1;
   const int64_t work = tiles.total * splits;
@@ -1451,16 +1451,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     t2.tiles_m = (M + 255) / 256;
     t2.tiles_n = (N + pn - 1) / pn;
     t2.a_upper = (a_upper && !lower) ? 1 : 0;
-    if (lower) {
-      int64_t tot = 0;
-      for (int64_t tm = 0; tm < t2.tiles_m; tm++) {
-        const int64_t c = (row0 + tm * 256 + 255) / 256 + 1;
-        tot += c < t2.tiles_n ? c : t2.tiles_n;
-      }
-      t2.total = tot;
-    } else {
-      t2.total = t2.tiles_m * t2.tiles_n;
-    }
+    t2.total = count_tiles(t2);
     int64_t pairs = t2.total;
     const int64_t max_pairs = ctas / 2 > 0 ? ctas / 2 : 1;
     if (pairs > max_pairs) pairs = max_pairs;
@@ -1535,6 +1526,26 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   note_launch(PATH_TCGEN05);
   PGB_CUDA(cudaGetLastError());
   return PGB200_OK;
+}
+
+// Test hook (host only): the (tile row, tile column) sequence the fp32 kernels
+// walk for an M x N output with the given tile shape, as TileCursor yields it.
+// Returns the number of tiles, or -1 when `cap` pairs do not hold them.
+int64_t enumerate_tiles_for_test(int64_t M, int64_t N, int bm, int bn, int lower, int64_t row0,
+                                 int64_t *tm_out, int64_t *tn_out, int64_t cap) {
+  Tiles t = {};
+  t.tiles_m = (M + bm - 1) / bm;
+  t.tiles_n = (N + bn - 1) / bn;
+  t.bm = bm;
+  t.bn = bn;
+  t.lower = lower;
+  t.row0 = row0;
+  t.splits = 1;
+  t.total = count_tiles(t);
+  if (t.total > cap) return -1;
+  TileCursor cur;
+  for (int64_t i = 0; i < t.total; i++) cur.seek(t, i, &tm_out[i], &tn_out[i]);
+  return t.total;
 }
 
 }  // namespace pgb200

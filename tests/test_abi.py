@@ -102,13 +102,8 @@ def test_longest_first_tile_schedule():
     """The host-built schedule of the triangular products (an internal C++
     function, reached through its exported symbol): every tile exactly once,
     loads within one tile of each other, oversize problems refused."""
-    import subprocess
     lib = pgb.load()
-    out = subprocess.run(["nm", "-D", "--defined-only", pgb.LIB_PATH], check=True,
-                         capture_output=True, text=True).stdout
-    names = [ln.split()[-1] for ln in out.splitlines() if "build_lpt_schedule" in ln]
-    assert len(names) == 1
-    fn = getattr(lib, names[0])
+    fn = _internal(lib, "build_lpt_schedule")
     fn.restype = C.c_bool
     fn.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
     MAX_TILES, MAX_WORKERS = 1408, 160
@@ -135,3 +130,45 @@ def test_longest_first_tile_schedule():
     big = np.ones(MAX_TILES + 1, dtype=np.int64)
     assert not fn(big.ctypes.data, MAX_TILES + 1, 148, C.addressof(Sched()))
     assert not fn(big.ctypes.data, 10, MAX_WORKERS + 1, C.addressof(Sched()))
+
+
+def _internal(lib, fragment):
+    """An internal C++ function of the library, by a fragment of its mangled name."""
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", pgb.LIB_PATH], check=True,
+                         capture_output=True, text=True).stdout
+    names = [ln.split()[-1] for ln in out.splitlines() if fragment in ln]
+    assert len(names) == 1, names
+    return getattr(lib, names[0])
+
+
+@pytest.mark.parametrize("M,N,bm,bn,lower,row0", [
+    (1024, 1024, 128, 256, 0, 0), (1000, 1100, 128, 64, 0, 0), (4096, 2048, 256, 256, 0, 0),
+    (130, 70, 128, 256, 0, 0),                       # fewer tile rows than a band
+    (2048, 2048, 128, 256, 1, 0), (1200, 1200, 128, 64, 1, 0), (2048, 2048, 256, 256, 1, 0),
+    (768, 1408, 128, 256, 1, 640), (200, 640, 128, 64, 1, 440), (768, 1408, 256, 256, 1, 640),
+    (2100, 2100, 128, 256, 1, 0),                    # more than one band of 16 tile rows
+])
+def test_fp32_tile_walk_covers_every_tile_once(M, N, bm, bn, lower, row0):
+    """The band-ordered walk of the fp32 kernels: every tile that holds an
+    element with j <= i + row0 (or every tile, for a full product) is visited
+    exactly once, and the host-side count agrees with the walk."""
+    lib = pgb.load()
+    fn = _internal(lib, "enumerate_tiles_for_test")
+    fn.restype = C.c_int64
+    fn.argtypes = [C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_void_p,
+                   C.c_void_p, C.c_int64]
+    cap = 1 << 16
+    tm = np.zeros(cap, dtype=np.int64)
+    tn = np.zeros(cap, dtype=np.int64)
+    n = fn(M, N, bm, bn, lower, row0, tm.ctypes.data, tn.ctypes.data, cap)
+    assert n >= 0
+    got = list(zip(tm[:n].tolist(), tn[:n].tolist()))
+    want = set()
+    for r in range(-(-M // bm)):
+        for c in range(-(-N // bn)):
+            # lower: the tile row's last row (r*bm + bm - 1, absolute + row0) reaches column c*bn
+            if not lower or c * bn <= r * bm + bm - 1 + row0:
+                want.add((r, c))
+    assert len(got) == len(set(got)), "a tile is visited twice"
+    assert set(got) == want
