@@ -523,4 +523,19 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
   return PGB200_OK;
 }
 
+// Test hook (host only): the (tile row, tile column) of every linear tile
+// index of the fp64 kernel, as TileMap::get yields them.  Returns the count,
+// or -1 when `cap` pairs do not hold them.
+int64_t enumerate_dmma_tiles_for_test(int64_t tiles_m, int64_t tiles_n, int lower, int64_t *tm_out,
+                                      int64_t *tn_out, int64_t cap) {
+  TileMap t = {};
+  t.tiles_m = tiles_m;
+  t.tiles_n = tiles_n;
+  t.lower = lower;
+  t.total = lower ? tiles_m * (tiles_m + 1) / 2 : tiles_m * tiles_n;
+  if (t.total > cap) return -1;
+  for (int64_t i = 0; i < t.total; i++) t.get(i, &tm_out[i], &tn_out[i]);
+  return t.total;
+}
+
 }  // namespace pgb200

@@ -172,3 +172,25 @@ def test_fp32_tile_walk_covers_every_tile_once(M, N, bm, bn, lower, row0):
                 want.add((r, c))
     assert len(got) == len(set(got)), "a tile is visited twice"
     assert set(got) == want
+
+
+@pytest.mark.parametrize("tiles_m,tiles_n,lower", [(32, 32, 0), (7, 3, 0), (1, 9, 0), (19, 5, 0),
+                                                   (1, 1, 1), (10, 10, 1), (64, 64, 1), (181, 181, 1)])
+def test_fp64_tile_map_is_a_bijection(tiles_m, tiles_n, lower):
+    """Linear tile index -> (row, column) of the fp64 kernel: groups of 8 tile
+    rows for a full product, the packed lower triangle (square-root inverse)
+    for the triangular update."""
+    lib = pgb.load()
+    fn = _internal(lib, "enumerate_dmma_tiles_for_test")
+    fn.restype = C.c_int64
+    fn.argtypes = [C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64]
+    cap = 1 << 16
+    tm = np.zeros(cap, dtype=np.int64)
+    tn = np.zeros(cap, dtype=np.int64)
+    n = fn(tiles_m, tiles_n, lower, tm.ctypes.data, tn.ctypes.data, cap)
+    got = list(zip(tm[:n].tolist(), tn[:n].tolist()))
+    if lower:
+        want = {(r, c) for r in range(tiles_m) for c in range(r + 1)}
+    else:
+        want = {(r, c) for r in range(tiles_m) for c in range(tiles_n)}
+    assert n == len(want) and len(set(got)) == n and set(got) == want
