@@ -35,3 +35,25 @@ def test_reference_arm_prints_one_contract_line(workload):
     assert e["value"] == d["value"] and e["unit"] == d["unit"]
     assert e["h2d_bytes_per_step"] == 0 and e["d2h_bytes_per_step"] == 0
     assert d["unit"] == ("GB/s" if workload.startswith("mvt") else "GFLOP/s")
+
+
+def test_workload_tables():
+    """Algorithmic units and operand sizes the roofline arithmetic rests on."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    w = bench.WORKLOADS
+    assert bench.algorithmic_work("dgemm4096", w["dgemm4096"]) == 2 * 4096 ** 3
+    assert bench.algorithmic_work("sgemm32768", w["sgemm32768"]) == 2 * 32768 ** 3
+    assert bench.algorithmic_work("ssyrk16384", w["ssyrk16384"]) == 16384 * 16385 * 8192
+    assert bench.algorithmic_work("mvt32768", w["mvt32768"]) == 32768 * 32768 * 8 + 6 * 32768 * 8
+    assert bench.algorithmic_work("chain2mm", w["chain2mm"]) == \
+        2 * 4096 * 5120 * 6144 + 2 * 4096 * 8192 * 5120
+    assert bench.operand_bytes("dgemm4096", w["dgemm4096"]) == 3 * 4096 * 4096 * 8
+    # only the workloads below twice the L2 size take the flushed, step-by-step timing
+    small = sorted(n for n in w if bench.operand_bytes(n, w[n]) < 2 * bench.L2_BYTES)
+    assert small == ["sgemm1024", "sgemm4096"]
+    for name in w:
+        metric, unit, scale = bench.metric_of(name)
+        assert unit == ("GB/s" if name.startswith("mvt") else "GFLOP/s") and scale == 1e9
