@@ -306,6 +306,23 @@ def test_sgemm_split_k(M, N, K, beta):
     assert elementwise_rel(got, unsplit) <= 1e-5
 
 
+@pytest.mark.parametrize("M,N,K,beta", [(200, 300, 400, 1.0), (100, 300, 200, 0.0)])
+def test_sgemm_plain_matmul_nests(M, N, K, beta):
+    """The two fp32 matmul nests of the reference's raise-to-affine test
+    (tools/cgeist/Test/Verification/raiseToAffine.c:12-27 `C += A*B`, and :30-51
+    `C = 0; C += A*B`), through the drop-in with alpha = 1 and beta = 1 / 0."""
+    A = pbo.fill(M, K, np.float32, SEED, 1, 0.0, 1.0)
+    B = pbo.fill(K, N, np.float32, SEED, 2, 0.0, 1.0)
+    C0 = pbo.fill(M, N, np.float32, SEED, 3, 0.0, 1.0)
+    got = C0.copy() if beta else np.full((M, N), np.nan, dtype=np.float32)
+    polybench.kernel_gemm(M, N, K, 1.0, beta, got, A, B)
+    # the nest itself, sequential fp32 (alpha = 1 and beta = 1 are exact factors)
+    seq = pbo.gemm(1.0, beta, C0.copy() if beta else np.zeros((M, N), np.float32), A, B)
+    truth = pbo.gemm_acc64(1.0, beta, C0, A, B)
+    assert elementwise_rel(got, truth) <= 1e-5
+    assert elementwise_rel(got, seq) <= 1e-5
+
+
 def test_sgemm_config0_1024():
     """configs[0]: fp32 M=N=K=1024, uniform [0,1), alpha=1.5, beta=1.2."""
     got, truth, seq = _sgemm_case(1024, 1024, 1024)
