@@ -164,6 +164,30 @@ def test_oracle_matches_compiled_reference_symm_trmm_doitgen(tname, dtype):
     assert np.max(np.abs(A3 - A4)) <= tol * np.max(np.abs(A4))
 
 
+def test_symm_trmm_doitgen_closed_forms():
+    """What the three nests compute, stated as matrix algebra (the device code
+    implements these forms, the oracle the loop nests): they must agree."""
+    rng = np.random.default_rng(11)
+    m, n = 37, 29
+    A = rng.uniform(0, 1, (m, m))
+    B = rng.uniform(0, 1, (m, n))
+    Cm = rng.uniform(0, 1, (m, n))
+    L = np.tril(A)
+    S = L + np.tril(A, -1).T                       # symmetric, from the lower triangle
+    got = pbo.symm(1.5, 1.2, Cm.copy(), np.where(np.tri(m, dtype=bool), A, np.nan), B)
+    assert np.allclose(got, 1.2 * Cm + 1.5 * S @ B, rtol=1e-13, atol=0)
+    U = np.eye(m) + np.tril(A, -1).T               # unit upper triangular
+    got = pbo.trmm(1.5, np.where(np.tri(m, k=-1, dtype=bool), A, np.nan), B.copy())
+    assert np.allclose(got, 1.5 * U @ B, rtol=1e-13, atol=0)
+    nr, nq, np_ = 4, 5, 13
+    A3 = rng.uniform(-1, 1, (nr, nq, np_))
+    C4 = rng.uniform(-1, 1, (np_, np_))
+    s_ = np.zeros(np_)
+    got = pbo.doitgen(A3.copy(), C4, s_)
+    assert np.allclose(got, A3 @ C4, rtol=1e-12, atol=1e-14)
+    assert np.array_equal(s_, got[-1, -1])
+
+
 def test_row_restricted_oracle_is_bit_identical():
     n, m = 40, 24
     A, C = _rand((n, m), np.float64, 1), _rand((n, n), np.float64, 2)
