@@ -164,6 +164,63 @@ def test_oracle_matches_compiled_reference_symm_trmm_doitgen(tname, dtype):
     assert np.max(np.abs(A3 - A4)) <= tol * np.max(np.abs(A4))
 
 
+@needs_ref
+@pytest.mark.parametrize("tname,dtype", TYPES)
+def test_oracle_matches_compiled_reference_widened_nests(tname, dtype):
+    """3mm, atax, bicg, gesummv, syr2k and gemver on seeded random inputs against
+    the reference's own compiled kernels (FMA contraction may differ, no more)."""
+    tol = 1e-13 if dtype == np.float64 else 2e-5
+
+    def close(a, b):
+        return np.max(np.abs(a - b)) <= tol * max(np.max(np.abs(b)), 1e-30)
+
+    ni, nj, nk, nl, nm = 13, 17, 19, 23, 11
+    A, B = _rand((ni, nk), dtype, 31), _rand((nk, nj), dtype, 32)
+    Cm, D = _rand((nj, nm), dtype, 33), _rand((nm, nl), dtype, 34)
+    out1 = [np.zeros(s_, dtype) for s_ in ((ni, nj), (nj, nl), (ni, nl))]
+    out2 = [o.copy() for o in out1]
+    pbo.mm3(out1[0], A, B, out1[1], Cm, D, out1[2])
+    ref.kernel_3mm(ni, nj, nk, nl, nm, out2[0], A, B, out2[1], Cm, D, out2[2])
+    assert all(close(a, b) for a, b in zip(out1, out2))
+
+    m, n = 21, 27
+    Am, x = _rand((m, n), dtype, 35), pbo.fill_vec(n, dtype, SEED, 36, 0.0, 1.0)
+    y1, t1, y2, t2 = (np.zeros(k, dtype) for k in (n, m, n, m))
+    pbo.atax(Am, x, y1, t1)
+    ref.kernel_atax(m, n, Am, x, y2, t2)
+    assert close(y1, y2) and close(t1, t2)
+
+    Ab = _rand((n, m), dtype, 37)                       # bicg: A is n x m
+    p_, r_ = pbo.fill_vec(m, dtype, SEED, 38, 0.0, 1.0), pbo.fill_vec(n, dtype, SEED, 39, 0.0, 1.0)
+    s1, q1, s2, q2 = (np.zeros(k, dtype) for k in (m, n, m, n))
+    pbo.bicg(Ab, s1, q1, p_, r_)
+    ref.kernel_bicg(m, n, Ab, s2, q2, p_, r_)
+    assert close(s1, s2) and close(q1, q2)
+
+    n = 31
+    Ag, Bg = _rand((n, n), dtype, 40), _rand((n, n), dtype, 41)
+    xg = pbo.fill_vec(n, dtype, SEED, 42, 0.0, 1.0)
+    ya, ta, yb, tb = (np.zeros(n, dtype) for _ in range(4))
+    pbo.gesummv(1.5, 1.2, Ag, Bg, ta, xg, ya)
+    ref.kernel_gesummv(n, 1.5, 1.2, Ag, Bg, tb, xg, yb)
+    assert close(ya, yb) and close(ta, tb)
+
+    n, m = 26, 18
+    As, Bs, Cs = _rand((n, m), dtype, 43), _rand((n, m), dtype, 44), _rand((n, n), dtype, 45)
+    Cs2 = Cs.copy()
+    pbo.syr2k(1.5, 1.2, Cs, As, Bs)
+    ref.kernel_syr2k(n, m, 1.5, 1.2, Cs2, As, Bs)
+    assert close(Cs, Cs2)
+
+    n = 33
+    Av = _rand((n, n), dtype, 46)
+    vec = [pbo.fill_vec(n, dtype, SEED, 47 + k, 0.0, 1.0) for k in range(8)]
+    Av2, vec2 = Av.copy(), [v.copy() for v in vec]
+    pbo.gemver(1.5, 1.2, Av, *vec)
+    ref.kernel_gemver(n, 1.5, 1.2, Av2, *vec2)
+    assert close(Av, Av2) and all(close(a, b) for a, b in zip(vec, vec2))
+
+
 def test_symm_trmm_doitgen_closed_forms():
     """What the three nests compute, stated as matrix algebra (the device code
     implements these forms, the oracle the loop nests): they must agree."""
