@@ -84,6 +84,19 @@ int32_t symm_device(cudaStream_t s, int64_t M, int64_t N, T alpha, const T *A, i
   return gemm_device<T>(s, M, N, M, alpha, S, lds, B, ldb, false, beta, C, ldc, false, 0);
 }
 
+// B = alpha * U * Bold on the tensor-core kernel of the element type, with the
+// hint that U is upper triangular.
+inline int32_t triangular_product(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
+                                  const double *U, int64_t ldu, const double *Bold, int64_t ldo,
+                                  double *B, int64_t ldb) {
+  return dmma_gemm(s, M, N, K, alpha, U, ldu, Bold, ldo, false, 0.0, B, ldb, false, true);
+}
+inline int32_t triangular_product(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha,
+                                  const float *U, int64_t ldu, const float *Bold, int64_t ldo,
+                                  float *B, int64_t ldb) {
+  return tf32x3_gemm(s, M, N, K, alpha, U, ldu, Bold, ldo, false, 0.0f, B, ldb, false, 0, true);
+}
+
 template <typename T>
 int32_t trmm_device(Runtime *rt, cudaStream_t s, int64_t M, int64_t N, T alpha, const T *A,
                     int64_t lda, T *B, int64_t ldb) {
@@ -106,14 +119,7 @@ int32_t trmm_device(Runtime *rt, cudaStream_t s, int64_t M, int64_t N, T alpha, 
   // One launch on the tensor-core kernels, which start each tile row's K loop
   // at its diagonal block: the zero half of U is neither loaded nor multiplied.
   int32_t st = PGB200_ERR_UNSUPPORTED;
-  if (!rt->cfg.force_generic) {
-    if (sizeof(T) == 8)
-      st = dmma_gemm(s, M, N, Kp, (double)alpha, (const double *)U, ldu, (const double *)Bold, ldo,
-                     false, 0.0, (double *)B, ldb, false, true);
-    else
-      st = tf32x3_gemm(s, M, N, Kp, (float)alpha, (const float *)U, ldu, (const float *)Bold, ldo,
-                       false, 0.0f, (float *)B, ldb, false, 0, true);
-  }
+  if (!rt->cfg.force_generic) st = triangular_product(s, M, N, Kp, alpha, U, ldu, Bold, ldo, B, ldb);
   if (st == PGB200_ERR_UNSUPPORTED) {
     // Generic kernels (operands that miss the tensor-core alignment rules):
     // row block [r0, r1) of U is zero left of column r0, so its product starts
