@@ -45,7 +45,13 @@ enum {
 /* Optional tuning knobs; pgb200Init(NULL) and lazy initialisation use the
  * defaults.  A zero field means "default". */
 typedef struct pgb200Config {
-  int32_t log_level;          /* 0 quiet (errors only), 1 info, 2 per call   */
+  int32_t log_level;          /* stderr verbosity: 0 errors only, 1 also one line
+                                 per initialised device and per Pin/Unpin, 2 also
+                                 one line per compute call (entry, sizes, kernel
+                                 family).  The environment variable PGB200_LOG,
+                                 when set, takes precedence.  Errors always have
+                                 the "'<expr>' failed with '<msg>'" form of
+                                 CudaRuntimeWrappers.cpp:29-50.                 */
   int32_t sgemm_chunk_kblocks;/* 3xTF32: K-blocks (of 16) accumulated in the
                                  tensor-core accumulator before it is drained
                                  into fp32 registers; bounds the truncation
@@ -56,14 +62,15 @@ typedef struct pgb200Config {
   int32_t reserve_sms;        /* SMs the persistent GEMM kernels leave free, so
                                  that a concurrent collective (NCCL broadcast
                                  of the next operand chunk) can run beside them */
-  int32_t reserved[3];        /* [0] == 2: never use the two-CTA (cta_group::2)
-                                 fp32 kernel (default: whenever a product has
-                                 >= 512 rows and enough tiles);
-                                 [0] == 4: never split K over several CTAs
-                                 (default: whenever fewer than half of the SMs
-                                 would get a tile and K is long enough);
-                                 [1] == 1: fp32 row-major B always used in
-                                 place, whatever M                            */
+  int32_t no_two_cta;         /* 1: never use the two-CTA (cta_group::2) fp32
+                                 kernel (default: whenever a product has >= 512
+                                 rows and enough tiles)                        */
+  int32_t no_split_k;         /* 1: never split K over several CTAs (default:
+                                 whenever fewer than half of the SMs would get
+                                 a tile and K is long enough)                  */
+  int32_t sgemm_b_in_place;   /* 1: fp32 row-major B always used in place,
+                                 whatever M (default: transposed once into
+                                 K-major planes for tall products)             */
 } pgb200Config;
 
 /* Runtime life cycle.  Replaces nothing in the reference one-to-one; plays the
@@ -242,10 +249,55 @@ int32_t pgb200Dmvt(void *stream, int64_t N, const double *A, int64_t lda,
  *    each call overwrites every entry before reading it (nothing has to start
  *    at zero).  Two calls that overlap on the GPU - different streams, or two
  *    host threads - would overwrite each other's partial sums: serialise them.
- * The result is the same as pgb200Dmvt's (same kernels, same summation order). */
+ *  - The looked-up address is remembered per device for the life of the
+ *    process; after a cudaDeviceReset() it is stale, so do not reset a device
+ *    between calls of this entry point.
+ * The result equals pgb200Dmvt's bit for bit (same two kernels, same summation
+ * order). */
 int32_t pgb200DmvtNoAlloc(void *stream, int64_t N, const double *A, int64_t lda,
                           const double *y1, const double *y2, double *x1,
                           double *x2);
+
+/* Device residency across calls.  pgb200Pin registers the host range
+ * [host, host + bytes) and keeps a device copy of it (uploaded once, now);
+ * until pgb200Unpin every entry point that is handed a pointer inside the
+ * range computes on the device copy and moves nothing over PCIe, and a call
+ * whose arrays are all registered (or device memory) is asynchronous on its
+ * stream like a call on device arrays.  The device copy is the current one
+ * while the range is registered: the host array is stale after a call that
+ * wrote into it, until pgb200PinSync (download if a call wrote to it, stay
+ * registered) or pgb200Unpin (download if written, then release).  Host
+ * writes to a registered range are not seen by the device copy; unpin, write,
+ * pin again.  Ranges must not overlap; `host` given to Unpin / PinSync is the
+ * pointer that was registered.  The downloads synchronise the device.
+ * This is how the reference's own CUDA variant of the kernels keeps operands
+ * in cudaMalloc buffers across the kernel call and copies only the result
+ * back (tools/cgeist/Test/CUDA/polybench-cuda/gemm/gemm.cu:89-100); here the
+ * generated host code keeps its host arrays and brackets the calls instead. */
+int32_t pgb200Pin(const void *host, uint64_t bytes);
+int32_t pgb200PinSync(const void *host);
+int32_t pgb200Unpin(const void *host);
+
+/* Bytes this library has copied host->device and device->host so far in this
+ * process (staging of host arrays, row-block pipeline, Pin/PinSync/Unpin, the
+ * multi-GPU scatter and gather).  Either pointer may be null.  No counterpart
+ * in the reference. */
+int32_t pgb200TransferCounters(int64_t *h2d_bytes, int64_t *d2h_bytes);
+
+/* Per-call device timing.  With the environment variable PGB200_PROFILE=1 (or
+ * after pgb200ProfileEnable(1)) every compute entry point brackets its work on
+ * the stream with a pair of CUDA events taken from a ring of 512; the oldest
+ * pair is resolved and added to its entry's totals when the ring wraps.
+ * pgb200ProfileDump synchronises the device, resolves what is pending and
+ * writes one line per entry point - name, calls, total and mean milliseconds -
+ * to `path`, or to stderr when path is null; it is also called at
+ * pgb200Shutdown when PGB200_PROFILE_FILE names a file.  Plays the role of the
+ * reference's profile-guided timing runtime, which brackets a region with
+ * device synchronisations and clock_gettime and appends the elapsed time to a
+ * file per kernel id at exit
+ * (lib/polygeist/ExecutionEngine/PGORuntime.h:58-113). */
+int32_t pgb200ProfileEnable(int32_t on);
+int32_t pgb200ProfileDump(const char *path);
 
 /* Counter-based uniform generator used by the test and benchmark harness
  * (device pointer only).  Element (r,c) of the logical rows x cols array, for

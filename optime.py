@@ -1,7 +1,7 @@
 """Time one libpgb200 entry point on device-resident operands.
 
-    python -m polygeist_b200.optime --op dsymm --m 4096 --n 4096
-    python -m polygeist_b200.optime --op dtrmm --m 8192 --n 4096 --iters 10
+    python optime.py --op dsymm --m 4096 --n 4096
+    python optime.py --op dtrmm --m 8192 --n 4096 --iters 10
 
 Operands are filled on the device by the library's seeded generator; every
 iteration is timed with CUDA events on the launching stream after a write
@@ -11,7 +11,11 @@ number of kernels launched per call).
 """
 import argparse
 import json
+import os
 import statistics
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 OPS = {
     # name: (dtype, operand shapes as functions of (m, n, k), useful flop)

@@ -21,7 +21,10 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("PGB200_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+# The reference tree: PGB200_REFERENCE_ROOT, else a checkout named `reference`
+# beside this repository.
+REF_ROOT = os.environ.get("PGB200_REFERENCE_ROOT",
+                          os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 PB = os.path.join(REF_ROOT, "tools/cgeist/Test/polybench")
 REF_OUT = os.path.join(HERE, "_ref")
 

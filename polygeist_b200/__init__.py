@@ -34,7 +34,8 @@ class PGB200Error(RuntimeError):
 class Config(C.Structure):
     _fields_ = [("log_level", C.c_int32), ("sgemm_chunk_kblocks", C.c_int32),
                 ("force_generic", C.c_int32), ("sgemm_planes_only", C.c_int32),
-                ("reserve_sms", C.c_int32), ("reserved", C.c_int32 * 3)]
+                ("reserve_sms", C.c_int32), ("no_two_cta", C.c_int32),
+                ("no_split_k", C.c_int32), ("sgemm_b_in_place", C.c_int32)]
 
 
 _i32, _i64, _vp, _f64, _f32 = C.c_int32, C.c_int64, C.c_void_p, C.c_double, C.c_float
@@ -65,6 +66,12 @@ SIGNATURES = {
     "pgb200DmvtNoAlloc": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp]),
     "pgb200FillUniformF64": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, C.c_uint64, C.c_uint32, _f64, _f64]),
     "pgb200FillUniformF32": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, C.c_uint64, C.c_uint32, _f32, _f32]),
+    "pgb200Pin": (_i32, [_vp, C.c_uint64]),
+    "pgb200PinSync": (_i32, [_vp]),
+    "pgb200Unpin": (_i32, [_vp]),
+    "pgb200TransferCounters": (_i32, [C.POINTER(_i64), C.POINTER(_i64)]),
+    "pgb200ProfileEnable": (_i32, [_i32]),
+    "pgb200ProfileDump": (_i32, [C.c_char_p]),
     "pgb200LastPath": (_i32, []),
     "pgb200PollDeviceStatus": (_i32, []),
     "pgb200SelfTestWaitTimeout": (_i32, [_vp, _i64]),
@@ -124,11 +131,39 @@ def check(status):
 
 
 def init(log_level=0, sgemm_chunk_kblocks=0, force_generic=0, sgemm_planes_only=0, reserve_sms=0,
-         sgemm_two_cta=0, sgemm_b_in_place=0):
-    cfg = Config(log_level, sgemm_chunk_kblocks, force_generic, sgemm_planes_only, reserve_sms)
-    cfg.reserved[0] = sgemm_two_cta
-    cfg.reserved[1] = sgemm_b_in_place
+         no_two_cta=0, no_split_k=0, sgemm_b_in_place=0):
+    cfg = Config(log_level, sgemm_chunk_kblocks, force_generic, sgemm_planes_only, reserve_sms,
+                 no_two_cta, no_split_k, sgemm_b_in_place)
     check(load().pgb200Init(C.byref(cfg)))
+
+
+def pin(a):
+    """Register the host array `a` (numpy): a device copy is made now and used by
+    every call that is handed `a` (or a view into it) until unpin(a)."""
+    check(load().pgb200Pin(C.c_void_p(a.ctypes.data), C.c_uint64(a.nbytes)))
+
+
+def pin_sync(a):
+    check(load().pgb200PinSync(C.c_void_p(a.ctypes.data)))
+
+
+def unpin(a):
+    check(load().pgb200Unpin(C.c_void_p(a.ctypes.data)))
+
+
+def transfer_counters():
+    """(host->device bytes, device->host bytes) copied by the library so far."""
+    h, d = _i64(0), _i64(0)
+    check(load().pgb200TransferCounters(C.byref(h), C.byref(d)))
+    return h.value, d.value
+
+
+def profile_enable(on=True):
+    check(load().pgb200ProfileEnable(1 if on else 0))
+
+
+def profile_dump(path=None):
+    check(load().pgb200ProfileDump(None if path is None else os.fsencode(path)))
 
 
 def last_path():

@@ -392,6 +392,18 @@ __global__ void dsplitk_reduce_kernel(const double *__restrict__ P, int64_t ldp,
   if (two) dst[1] = (beta != 0.0) ? fma(beta, old1, o1) : o1;
 }
 
+// dst[rows][ldp] = src[rows][cols] followed by zeros up to column colsP: the
+// repacking pass for operands that break a TMA rule.
+__global__ void pad_rows_kernel(const double *__restrict__ src, int64_t ld, int64_t rows,
+                                int64_t cols, double *__restrict__ dst, int64_t colsP) {
+  const int64_t total = rows * colsP;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / colsP, c = i - r * colsP;
+    dst[i] = c < cols ? src[r * ld + c] : 0.0;
+  }
+}
+
 }  // namespace
 
 int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha, const double *A,
@@ -399,14 +411,53 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
                   int64_t ldc, bool lower, bool a_upper) {
   Runtime *rt = nullptr;
   PGB_TRY(get_runtime(&rt));
-  // TMA rules: 16-byte aligned bases and row pitches; the 3-D views need K
-  // (and N for a row-major B) to be multiples of 4 elements.
-  if (K == 0 || (K % 4) != 0 || (lda % 2) != 0 || (ldb % 2) != 0 || !aligned16(A) ||
-      !aligned16(B))
-    return PGB200_ERR_UNSUPPORTED;
-  if (!transB && (N % 4) != 0) return PGB200_ERR_UNSUPPORTED;
+  if (K == 0) return PGB200_ERR_UNSUPPORTED;  // nothing to contract: the SIMT path scales C
   if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31))
     return PGB200_ERR_UNSUPPORTED;
+  if (lower && M != N) return PGB200_ERR_UNSUPPORTED;  // square lower-triangular update only
+  // TMA rules: 16-byte aligned bases and row pitches; the 3-D views need the
+  // inner extent (K; N for a row-major B) to be a multiple of 4 elements.  An
+  // operand that breaks one is repacked once into scratch with its inner extent
+  // padded to a multiple of 4 by zero columns (an O(M*K + K*N) pass beside the
+  // O(M*N*K) product), so every shape runs on the tensor-core kernel.
+  const int64_t K4 = (K + 3) / 4 * 4, N4 = (N + 3) / 4 * 4;
+  const bool a_ok = K == K4 && (lda % 2) == 0 && aligned16(A);
+  const bool b_ok = (ldb % 2) == 0 && aligned16(B) && (transB ? K == K4 : N == N4);
+  const bool b_is_a = transB && B == A && ldb == lda && N <= M;  // the rank-k update
+  PoolBuffer a_pack, b_pack;
+  const int64_t pad_cap = (int64_t)rt->num_sms * 16;
+  auto pad_grid = [&](int64_t total) {
+    const int64_t g = (total + 255) / 256;
+    return (unsigned)(g < 1 ? 1 : (g > pad_cap ? pad_cap : g));
+  };
+  if (!a_ok) {
+    PGB_CUDA(a_pack.alloc((size_t)M * K4 * sizeof(double), s));
+    pad_rows_kernel<<<pad_grid(M * K4), 256, 0, s>>>(A, lda, M, K, a_pack.as<double>(), K4);
+    note_launch(PATH_DMMA);
+    if (b_is_a) {
+      B = a_pack.as<double>();
+      ldb = K4;
+    }
+    A = a_pack.as<double>();
+    lda = K4;
+  }
+  if (!(b_is_a ? a_ok : b_ok)) {
+    if (!b_is_a) {
+      const int64_t rows = transB ? N : K, cols = transB ? K : N, colsP = transB ? K4 : N4;
+      PGB_CUDA(b_pack.alloc((size_t)rows * colsP * sizeof(double), s));
+      pad_rows_kernel<<<pad_grid(rows * colsP), 256, 0, s>>>(B, ldb, rows, cols, b_pack.as<double>(),
+                                                             colsP);
+      note_launch(PATH_DMMA);
+      B = b_pack.as<double>();
+      ldb = colsP;
+    }
+  }
+  PGB_CUDA(cudaGetLastError());
+  // From here on K is the padded inner extent (the added columns of A are zero;
+  // rows of a row-major B past the true K are zero-filled by TMA).
+  const int64_t n_map = N4;   // columns of a row-major B the tensor map may address
+  const int64_t k_rows = K;  // rows a row-major B really has
+  K = K4;
 
   CUtensorMap mapA, mapB;
   {
@@ -423,7 +474,7 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
     PGB_TRY(encode_tensor_map(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 3, B, dims, str, box,
                               CU_TENSOR_MAP_SWIZZLE_NONE));
   } else {
-    const uint64_t dims[3] = {4, (uint64_t)K, (uint64_t)(N / 4)};
+    const uint64_t dims[3] = {4, (uint64_t)k_rows, (uint64_t)(n_map / 4)};
     const uint64_t str[2] = {(uint64_t)ldb * 8, 32};
     const uint32_t box[3] = {4, BK, BN / 4};
     PGB_TRY(encode_tensor_map(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 3, B, dims, str, box,
@@ -439,8 +490,6 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
   tiles.partial = nullptr;
   tiles.ldp = 0;
   if (lower) {
-    // Square lower-triangular update only (row0 == 0, M == N).
-    if (M != N) return PGB200_ERR_UNSUPPORTED;
     tiles.total = tiles.tiles_m * (tiles.tiles_m + 1) / 2;
   } else {
     tiles.total = tiles.tiles_m * tiles.tiles_n;
@@ -452,7 +501,7 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
   // every tile to several CTAs (at least 8 K-blocks each) and add the partial
   // products afterwards in split order.  A tile's time is K / (one SM's DMMA
   // rate) however many SMs idle beside it.
-  if (!a_upper && tiles.total * 2 <= ctas && rt->cfg.reserved[0] != 4) {
+  if (!a_upper && tiles.total * 2 <= ctas && !rt->cfg.no_split_k) {
     const int64_t nkb = (K + BK - 1) / BK;
     int64_t sp = ctas / tiles.total;
     if (sp > nkb / 8) sp = nkb / 8;
@@ -461,8 +510,9 @@ int32_t dmma_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, double alpha,
       const int64_t kper = (nkb + sp - 1) / sp;
       const int splits = (int)((nkb + kper - 1) / kper);
       const int64_t ldp = (N + 1) / 2 * 2;
-      void *ws = nullptr;
-      PGB_TRY(get_workspace(s, (size_t)splits * M * ldp * sizeof(double), &ws));
+      PoolBuffer scratch;  // this call's own partial products, released in stream order
+      PGB_CUDA(scratch.alloc((size_t)splits * M * ldp * sizeof(double), s));
+      void *ws = scratch.ptr;
       tiles.splits = splits;
       tiles.kper = kper;
       tiles.partial = static_cast<double *>(ws);

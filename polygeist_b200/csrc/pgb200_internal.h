@@ -59,9 +59,46 @@ int32_t get_runtime(Runtime **rt);
 void note_launch(Path p, int n = 1);
 int log_level();
 
-// Per-(device,stream) scratch memory, grown on demand and kept until
-// pgb200Shutdown().  Contents are undefined between calls.
-int32_t get_workspace(cudaStream_t stream, size_t bytes, void **ptr);
+// stderr logging by level (pgb200Config.log_level / PGB200_LOG): errors are
+// always printed; level 1 adds life-cycle lines, level 2 one line per call.
+void log_line(int level, const char *fmt, ...);
+
+// Waits for `s`, then reads the device status word: an expired device-side
+// wait becomes PGB200_ERR_TIMEOUT here (word cleared, message set).  Every
+// path that copies results back to a host array calls this before the copy,
+// so a kernel that gave up never hands a half-written result to the caller.
+int32_t sync_check(Runtime *rt, cudaStream_t s);
+int32_t take_device_status(Runtime *rt);
+
+// Transfer accounting behind pgb200TransferCounters().
+void count_h2d(size_t bytes);
+void count_d2h(size_t bytes);
+
+// Device-residency registry (pgb200Pin): when `p` lies inside a registered host
+// range owned by the current device, *dev receives the matching address in the
+// device copy; `written` marks the device copy as newer than the host array.
+bool registry_lookup(const void *p, void **dev, bool written);
+
+// One of these at the top of every exported compute entry: per-call event
+// timing when profiling is on (outermost entry only), and the level-2 log line
+// when the call returns.
+struct EntryScope {
+  const char *name;
+  cudaStream_t stream;
+  int slot;  // ring slot holding this call's event pair, -1 when not timed
+  bool outer;
+  EntryScope(const char *name, void *stream);
+  ~EntryScope();
+  EntryScope(const EntryScope &) = delete;
+  EntryScope &operator=(const EntryScope &) = delete;
+};
+#define PGB_ENTRY(stream) ::pgb200::EntryScope entry_scope__(__func__, (stream))
+void profile_enable(bool on);
+int32_t profile_dump(const char *path);  // null: stderr
+void profile_reset();                    // drops events and totals (shutdown)
+
+// Destroys the communicators and streams of the multi-GPU entry points.
+void mg_shutdown();
 
 // cuTensorMapEncodeTiled looked up through the runtime (no link against
 // libcuda).  `dims`/`box` innermost first; `strides_bytes` for dims 1..rank-1.
@@ -111,26 +148,38 @@ struct Staged {
   }
 };
 
-// Scratch from the stream-ordered pool, released (in stream order) when the
-// holder goes out of scope.
+// Scratch memory of one call: hi/lo planes, split-K partial products, mat-vec
+// partial sums.  No two calls that can run at the same time ever share a block:
+//  * small requests (<= 32 MiB) come from a cache private to the calling host
+//    thread, one block per (device, stream): a thread's calls on one stream are
+//    ordered on that stream, so reusing its block is safe, and other threads -
+//    on the same stream or another - have blocks of their own.  No driver call
+//    at all after the first use, which matters for products of a few
+//    microseconds;
+//  * larger requests come from the stream-ordered pool and go back to it (in
+//    stream order) when the holder goes out of scope; the pool keeps freed
+//    blocks (release threshold: never), so this costs no device allocation
+//    after the first call of a size either.
+// Cached blocks are released by pgb200Shutdown().
 struct PoolBuffer {
   void *ptr = nullptr;
   cudaStream_t stream = nullptr;
+  bool owned = false;  // from the pool: returned by the destructor
   PoolBuffer() = default;
   PoolBuffer(const PoolBuffer &) = delete;
   PoolBuffer &operator=(const PoolBuffer &) = delete;
   ~PoolBuffer() {
-    if (ptr) cudaFreeAsync(ptr, stream);
+    if (ptr && owned) cudaFreeAsync(ptr, stream);
   }
-  cudaError_t alloc(size_t bytes, cudaStream_t s) {
-    stream = s;
-    return cudaMallocAsync(&ptr, bytes, s);
-  }
+  cudaError_t alloc(size_t bytes, cudaStream_t s);
   template <typename T>
   T *as() const { return static_cast<T *>(ptr); }
 };
 
 bool is_host_pointer(const void *p);
+// Host memory that is not covered by a pgb200Pin registration: has to be
+// staged through the device for the duration of the call.
+bool needs_staging(const void *p);
 
 // in: copy host->device when staged; out: copy device->host in finish().
 template <typename T>

@@ -93,7 +93,7 @@ matvec_tile_kernel(const double *__restrict__ A, int64_t lda, int64_t M, int64_t
 #pragma unroll
             for (int e = 0; e < 2; e++) {
               if (rok && c + e < N) {
-                double v = row[c + e];
+                double v = r2.Aw[r * lda + c + e];  // not through the restrict/const view of A
                 v = __dadd_rn(__dadd_rn(v, __dmul_rn(u1r, v1v[q][e])), __dmul_rn(u2r, v2v[q][e]));
                 r2.Aw[r * lda + c + e] = v;
                 a[u][q][e] = v;
@@ -222,8 +222,9 @@ int32_t stream_matvec(cudaStream_t s, int64_t M, int64_t N, const double *A, int
   }
   const int64_t tiles_r = (M + MV_TR - 1) / MV_TR, tiles_c = (N + MV_TC - 1) / MV_TC;
   const size_t n1 = y1 ? (size_t)tiles_c * M : 0, n2 = y2 ? (size_t)tiles_r * N : 0;
-  void *ws = nullptr;
-  PGB_TRY(get_workspace(s, (n1 + n2) * sizeof(double), &ws));
+  PoolBuffer scratch;  // this call's own partial sums, released in stream order
+  PGB_CUDA(scratch.alloc((n1 + n2) * sizeof(double), s));
+  void *ws = scratch.ptr;
   double *p1 = y1 ? static_cast<double *>(ws) : nullptr;
   double *p2 = y2 ? static_cast<double *>(ws) + n1 : nullptr;
   const int64_t ntiles = tiles_r * tiles_c;
@@ -281,8 +282,9 @@ int32_t stream_gemver(cudaStream_t s, int64_t N, double alpha, double beta, doub
   PGB_TRY(get_runtime(&rt));
   if (N == 0) return PGB200_OK;
   const int64_t tiles_r = (N + MV_TR - 1) / MV_TR, tiles_c = (N + MV_TC - 1) / MV_TC;
-  void *ws = nullptr;
-  PGB_TRY(get_workspace(s, (size_t)tiles_r * N * sizeof(double), &ws));
+  PoolBuffer scratch;
+  PGB_CUDA(scratch.alloc((size_t)tiles_r * N * sizeof(double), s));
+  void *ws = scratch.ptr;
   double *p2 = static_cast<double *>(ws);
   const int64_t ntiles = tiles_r * tiles_c, cap = (int64_t)rt->num_sms * 2;
   const unsigned grid = (unsigned)(ntiles < cap ? ntiles : cap);
@@ -396,9 +398,12 @@ extern "C" int32_t pgb200DmvtNoAlloc(void *stream, int64_t N, const double *A, i
   else
     matvec_tile_kernel<false><<<grid, MV_WARPS * 32, 0, s>>>(A, lda, N, N, y1, y2, p1, p2,
                                                              tiles_r, tiles_c);
-  matvec_reduce_kernel<<<(unsigned)((N + 255) / 256), 256, 0, s>>>(x1, p1, tiles_c, N, 1.0, 1.0);
-  matvec_reduce_kernel<<<(unsigned)((N + 255) / 256), 256, 0, s>>>(x2, p2, tiles_r, N, 1.0, 1.0);
-  note_launch(PATH_STREAM, 3);
+  // The same second pass as pgb200Dmvt (one launch for both vectors, the same
+  // four interleaved partial sums), so the two entry points agree bit for bit.
+  const int blocks = (int)((N + 255) / 256);
+  matvec_reduce_pair_kernel<<<(unsigned)(2 * blocks), 256, 0, s>>>(x1, p1, tiles_c, N, blocks, x2,
+                                                                   p2, tiles_r, N, 1.0, 1.0);
+  note_launch(PATH_STREAM, 2);
   PGB_CUDA(cudaGetLastError());
   return PGB200_OK;
 }

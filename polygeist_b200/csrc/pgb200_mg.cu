@@ -10,8 +10,12 @@
 #include <dlfcn.h>
 #include <math.h>
 #include <nccl.h>
+#include <stdlib.h>
+#include <string.h>
 
+#include <chrono>
 #include <mutex>
+#include <thread>
 #include <vector>
 
 #include "pgb200_internal.h"
@@ -27,8 +31,22 @@ struct NcclApi {
   ncclResult_t (*GroupStart)() = nullptr;
   ncclResult_t (*GroupEnd)() = nullptr;
   const char *(*GetErrorString)(ncclResult_t) = nullptr;
+  // Optional (failure detection): absent from very old libraries.
+  ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
+  ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
   bool ok = false;
 };
+
+// Host-side failure injection for tests: the table entries are replaced by
+// stubs that report a failure without touching any GPU.
+ncclResult_t failing_broadcast(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t,
+                               cudaStream_t) {
+  return ncclSystemError;
+}
+ncclResult_t failing_async_error(ncclComm_t, ncclResult_t *out) {
+  *out = ncclSystemError;
+  return ncclSuccess;
+}
 
 struct MgState {
   int ndev = 0;
@@ -59,8 +77,34 @@ int32_t load_nccl() {
     set_error("multi-GPU entry: libnccl.so.2 lacks a required symbol");
     return PGB200_ERR_NCCL;
   }
+  g_nccl.CommGetAsyncError =
+      (decltype(g_nccl.CommGetAsyncError))dlsym(h, "ncclCommGetAsyncError");
+  g_nccl.CommAbort = (decltype(g_nccl.CommAbort))dlsym(h, "ncclCommAbort");
+  // PGB200_FAULT_NCCL=broadcast | async (read when the library is bound): every
+  // broadcast call fails / every asynchronous-error poll reports a failure.
+  if (const char *f = getenv("PGB200_FAULT_NCCL")) {
+    if (!strcmp(f, "broadcast")) g_nccl.Broadcast = failing_broadcast;
+    if (!strcmp(f, "async")) g_nccl.CommGetAsyncError = failing_async_error;
+  }
   g_nccl.ok = true;
   return PGB200_OK;
+}
+
+// Releases the streams and communicators; `abort` after a failed or overdue
+// collective (ncclCommAbort also ends kernels that still wait for a peer).
+void mg_destroy(bool abort) {
+  for (int d = 0; d < g_mg.ndev; d++) {
+    cudaSetDevice(d);
+    if (!g_mg.comm.empty() && g_mg.comm[d]) {
+      if (abort && g_nccl.CommAbort)
+        g_nccl.CommAbort(g_mg.comm[d]);
+      else
+        g_nccl.CommDestroy(g_mg.comm[d]);
+    }
+    if (g_mg.compute[d]) cudaStreamDestroy(g_mg.compute[d]);
+    if (g_mg.link[d]) cudaStreamDestroy(g_mg.link[d]);
+  }
+  g_mg = MgState();
 }
 
 #define PGB_NCCL(expr)                                                             \
@@ -82,15 +126,7 @@ int32_t mg_state(int ndev, MgState **out) {
   PGB_CUDA(cudaGetDeviceCount(&count));
   PGB_REQUIRE(ndev >= 1 && ndev <= count, "multi-GPU entry: ndev = %d but %d device(s) visible",
               ndev, count);
-  if (g_mg.ndev != 0) {  // different device count than last time: rebuild
-    for (int d = 0; d < g_mg.ndev; d++) {
-      cudaSetDevice(d);
-      if (!g_mg.comm.empty()) g_nccl.CommDestroy(g_mg.comm[d]);
-      cudaStreamDestroy(g_mg.compute[d]);
-      cudaStreamDestroy(g_mg.link[d]);
-    }
-    g_mg = MgState();
-  }
+  if (g_mg.ndev != 0) mg_destroy(false);  // different device count than last time: rebuild
   MgState st;
   st.compute.resize(ndev);
   st.link.resize(ndev);
@@ -155,11 +191,54 @@ cudaError_t copy_block(T *dst, int64_t dst_ld, const T *src, int64_t src_ld, int
 template <typename T>
 int32_t bcast(MgState *st, std::vector<T *> &bufs, size_t offset, size_t count) {
   PGB_NCCL(g_nccl.GroupStart());
-  for (int d = 0; d < st->ndev; d++)
-    PGB_NCCL(g_nccl.Broadcast(bufs[0] + offset, bufs[d] + offset, count, nccl_type<T>(), 0,
-                              st->comm[d], st->link[d]));
-  PGB_NCCL(g_nccl.GroupEnd());
+  // A failing call must not leave the group open: close it, then report.
+  ncclResult_t first = ncclSuccess;
+  for (int d = 0; d < st->ndev && first == ncclSuccess; d++)
+    first = g_nccl.Broadcast(bufs[0] + offset, bufs[d] + offset, count, nccl_type<T>(), 0,
+                             st->comm[d], st->link[d]);
+  const ncclResult_t end = g_nccl.GroupEnd();
+  if (first == ncclSuccess) first = end;
+  if (first != ncclSuccess) {
+    set_error("'ncclBroadcast' failed with '%s'", g_nccl.GetErrorString(first));
+    return PGB200_ERR_NCCL;
+  }
   return PGB200_OK;
+}
+
+// Waits for the link stream of device d with a host deadline, polling the
+// communicator's asynchronous error state meanwhile (a peer that died, a
+// network error).  False: the collective failed or is overdue.
+bool drain_link(MgState *st, int d) {
+  static const double limit_s = [] {
+    const char *e = getenv("PGB200_NCCL_TIMEOUT_S");
+    const double v = e ? atof(e) : 0.0;
+    return v > 0.0 ? v : 300.0;
+  }();
+  const auto t0 = std::chrono::steady_clock::now();
+  for (;;) {
+    if (!st->comm.empty() && g_nccl.CommGetAsyncError) {
+      ncclResult_t r = ncclSuccess;
+      if (g_nccl.CommGetAsyncError(st->comm[d], &r) != ncclSuccess ||
+          (r != ncclSuccess && r != ncclInProgress)) {
+        set_error("'ncclCommGetAsyncError' reported '%s' on device %d",
+                  g_nccl.GetErrorString(r), d);
+        return false;
+      }
+    }
+    const cudaError_t q = cudaStreamQuery(st->link[d]);
+    if (q == cudaSuccess) return true;
+    if (q != cudaErrorNotReady) {
+      report_cuda(q, "cudaStreamQuery(link stream)");
+      return false;
+    }
+    const double el =
+        std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    if (el > limit_s) {
+      set_error("the broadcast on device %d did not finish within %.0f s", d, limit_s);
+      return false;
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
 }
 
 // Common exit of the multi-GPU entries, also taken after a failure: drain both
@@ -173,19 +252,68 @@ int32_t mg_release(MgState *st, int entry_dev, int32_t status,
   auto note = [&](cudaError_t e) {
     if (e != cudaSuccess && drain == cudaSuccess) drain = e;
   };
+  // Link streams first: when a collective failed or is overdue the
+  // communicators are aborted, which also ends kernels still waiting on a peer,
+  // so the synchronisations below cannot hang.
+  bool comm_ok = true;
+  if (st->ndev > 1)
+    for (int d = 0; d < st->ndev && comm_ok; d++) {
+      note(cudaSetDevice(d));
+      comm_ok = drain_link(st, d);
+    }
+  if (!comm_ok && status == PGB200_OK) status = PGB200_ERR_NCCL;
+  if (!comm_ok && g_nccl.CommAbort) {
+    for (int d = 0; d < st->ndev; d++) {
+      cudaSetDevice(d);
+      if (st->comm[d]) g_nccl.CommAbort(st->comm[d]);
+      st->comm[d] = nullptr;
+    }
+  }
   for (int d = 0; d < st->ndev; d++) {
     note(cudaSetDevice(d));
     note(cudaStreamSynchronize(st->compute[d]));
     note(cudaStreamSynchronize(st->link[d]));
+    Runtime *rt = nullptr;
+    if (get_runtime(&rt) == PGB200_OK) {
+      const int32_t dst = take_device_status(rt);
+      if (status == PGB200_OK) status = dst;
+    }
     for (void *p : bufs[d])
       if (p) note(cudaFreeAsync(p, st->compute[d]));
     for (auto e : ev[d])
       if (e) cudaEventDestroy(e);
     note(cudaStreamSynchronize(st->compute[d]));
   }
+  if (!comm_ok) mg_destroy(false);  // communicators are gone: rebuilt by the next call
   note(cudaSetDevice(entry_dev));
   if (status == PGB200_OK && drain != cudaSuccess) return report_cuda(drain, "multi-GPU drain");
   return status;
+}
+
+// Before the results travel back: wait for every device's products and read
+// its status word, so a kernel that gave up is reported instead of copied.
+int32_t mg_products_done(MgState *st) {
+  int32_t status = PGB200_OK;
+  for (int d = 0; d < st->ndev; d++) {
+    PGB_CUDA(cudaSetDevice(d));
+    PGB_CUDA(cudaStreamSynchronize(st->compute[d]));
+    Runtime *rt = nullptr;
+    PGB_TRY(get_runtime(&rt));
+    const int32_t dst = take_device_status(rt);
+    if (status == PGB200_OK) status = dst;
+  }
+  return status;
+}
+
+// Arrays in device-0 memory may still be being written by work the caller
+// queued on its own streams; the entry's private non-blocking streams are not
+// ordered after that work by anything else.
+template <typename T>
+int32_t mg_wait_for_caller(const T *a, const T *b, const T *c) {
+  if (is_host_pointer(a) && is_host_pointer(b) && is_host_pointer(c)) return PGB200_OK;
+  PGB_CUDA(cudaSetDevice(0));
+  PGB_CUDA(cudaDeviceSynchronize());
+  return PGB200_OK;
 }
 
 // C = alpha*A*B + beta*C, rows of A and C split over ndev GPUs, B broadcast in
@@ -217,6 +345,13 @@ int32_t gemm_mg(int ndev, int64_t M, int64_t N, int64_t K, T alpha, const T *A, 
   std::vector<std::vector<cudaEvent_t>> ev(ndev);
   int32_t status = PGB200_OK;
   auto run = [&]() -> int32_t {
+    PGB_TRY(mg_wait_for_caller<T>(A, B, C));
+    if (is_host_pointer(A)) count_h2d((size_t)M * K * sizeof(T));
+    if (is_host_pointer(B)) count_h2d((size_t)K * N * sizeof(T));
+    if (is_host_pointer(C)) {
+      if (beta != (T)0) count_h2d((size_t)M * N * sizeof(T));
+      count_d2h((size_t)M * N * sizeof(T));
+    }
     // Stage: every device takes its rows of A and C; device 0 takes B.
     for (int d = 0; d < ndev; d++) {
       PGB_CUDA(cudaSetDevice(d));
@@ -265,6 +400,7 @@ int32_t gemm_mg(int ndev, int64_t M, int64_t N, int64_t K, T alpha, const T *A, 
                                 false, 0);
       }
     }
+    if (status == PGB200_OK) status = mg_products_done(st);
     for (int d = 0; d < ndev; d++) {
       PGB_CUDA(cudaSetDevice(d));
       const int64_t rows = b[d + 1] - b[d];
@@ -314,6 +450,12 @@ int32_t ssyrk_mg(int ndev, int64_t N, int64_t K, float alpha, const float *A, in
   }
   int32_t status = PGB200_OK;
   auto run = [&]() -> int32_t {
+    PGB_TRY(mg_wait_for_caller<float>(A, A, C));
+    if (is_host_pointer(A)) count_h2d((size_t)N * K * sizeof(float));
+    if (is_host_pointer(C)) {
+      count_h2d((size_t)N * N * sizeof(float));
+      count_d2h((size_t)N * N * sizeof(float));
+    }
     for (int d = 0; d < ndev; d++) {
       PGB_CUDA(cudaSetDevice(d));
       const int64_t rows = b[d + 1] - b[d];
@@ -355,6 +497,7 @@ int32_t ssyrk_mg(int ndev, int64_t N, int64_t K, float alpha, const float *A, in
                                     true, r0);
       }
     }
+    if (status == PGB200_OK) status = mg_products_done(st);
     for (int d = 0; d < ndev; d++) {
       PGB_CUDA(cudaSetDevice(d));
       const int64_t rows = b[d + 1] - b[d];
@@ -370,6 +513,12 @@ int32_t ssyrk_mg(int ndev, int64_t N, int64_t K, float alpha, const float *A, in
 }
 
 }  // namespace
+
+void mg_shutdown() {
+  std::lock_guard<std::mutex> lk(g_mg_mu);
+  if (g_mg.ndev != 0) mg_destroy(false);
+}
+
 }  // namespace pgb200
 
 using namespace pgb200;
@@ -379,17 +528,20 @@ extern "C" {
 int32_t pgb200DgemmMg(int32_t ndev, int64_t M, int64_t N, int64_t K, double alpha, const double *A,
                       int64_t lda, const double *B, int64_t ldb, double beta, double *C,
                       int64_t ldc) {
+  PGB_ENTRY(nullptr);
   return gemm_mg<double>(ndev, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
 }
 
 int32_t pgb200SgemmMg(int32_t ndev, int64_t M, int64_t N, int64_t K, float alpha, const float *A,
                       int64_t lda, const float *B, int64_t ldb, float beta, float *C,
                       int64_t ldc) {
+  PGB_ENTRY(nullptr);
   return gemm_mg<float>(ndev, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
 }
 
 int32_t pgb200SsyrkMg(int32_t ndev, int64_t N, int64_t K, float alpha, const float *A, int64_t lda,
                       float beta, float *C, int64_t ldc) {
+  PGB_ENTRY(nullptr);
   return ssyrk_mg(ndev, N, K, alpha, A, lda, beta, C, ldc);
 }
 

@@ -120,11 +120,13 @@ extern "C" int32_t pgb200ProbePeak(void *stream, int32_t kind, double *out) {
   PGB_TRY(get_runtime(&rt));
   PGB_REQUIRE(out, "ProbePeak: out is null");
   cudaStream_t s = (cudaStream_t)stream;
+  PoolBuffer scratch;
   void *ws = nullptr;
   const int grid = rt->num_sms * 2, threads = 512, iters = 2048;
   float ms = 0;
   if (kind == 0 || kind == 10 || kind == 11 || kind == 12 || kind == 13) {
-    PGB_TRY(get_workspace(s, 4096, &ws));
+    PGB_CUDA(scratch.alloc(4096, s));
+    ws = scratch.ptr;
     double *sink = static_cast<double *>(ws);
     double best = 0;
     const int shapes[4] = {4, 8, 16, 0};
@@ -146,7 +148,8 @@ extern "C" int32_t pgb200ProbePeak(void *stream, int32_t kind, double *out) {
     return PGB200_OK;
   }
   if (kind == 1) {
-    PGB_TRY(get_workspace(s, 4096, &ws));
+    PGB_CUDA(scratch.alloc(4096, s));
+    ws = scratch.ptr;
     double *sink = static_cast<double *>(ws);
     PGB_TRY(time_best(s, 5, [&] { dfma_probe_kernel<<<grid, threads, 0, s>>>(sink, iters * 8, 1e-3); }, &ms));
     *out = 2.0 * 16 * iters * 8 * threads * (double)grid / (ms * 1e-3) * 1e-9;
@@ -154,7 +157,8 @@ extern "C" int32_t pgb200ProbePeak(void *stream, int32_t kind, double *out) {
   }
   if (kind == 2) {
     const size_t bytes = size_t(2) << 30;
-    PGB_TRY(get_workspace(s, bytes, &ws));
+    PGB_CUDA(scratch.alloc(bytes, s));
+    ws = scratch.ptr;
     PGB_CUDA(cudaMemsetAsync(ws, 0, bytes, s));
     double *sink = static_cast<double *>(ws);
     PGB_TRY(time_best(s, 5, [&] {

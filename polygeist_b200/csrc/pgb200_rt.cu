@@ -2,10 +2,13 @@
 // staging, scratch memory, tensor-map encoding, the harness generator, and the
 // exported C ABI that dispatches to the kernel families.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
+#include <string>
 #include <utility>
 
 #include <algorithm>
@@ -26,11 +29,18 @@ static std::mutex g_mu;
 static bool g_have_cfg = false;
 static pgb200Config g_cfg = {};
 static std::map<int, Runtime *> g_rt;  // per device
-struct Ws {
-  void *ptr = nullptr;
+static std::atomic<int64_t> g_h2d{0}, g_d2h{0};
+
+// pgb200Pin registry: host base address -> device copy.
+struct PinEntry {
   size_t bytes = 0;
+  void *dev = nullptr;
+  int device = 0;
+  bool written = false;  // a call wrote into the device copy since the last download
 };
-static std::map<std::pair<int, cudaStream_t>, Ws> g_ws;
+static std::mutex g_pin_mu;
+static std::map<uintptr_t, PinEntry> g_pins;
+static std::atomic<int> g_pin_count{0};
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -51,7 +61,174 @@ int32_t report_cuda(cudaError_t e, const char *expr) {
   return PGB200_ERR_CUDA;
 }
 
-int log_level() { return g_have_cfg ? g_cfg.log_level : 0; }
+int log_level() {
+  // PGB200_LOG, read once, takes precedence over the configured level.
+  static const int env = [] {
+    const char *e = getenv("PGB200_LOG");
+    return (e && *e) ? atoi(e) : -1;
+  }();
+  if (env >= 0) return env;
+  return g_have_cfg ? g_cfg.log_level : 0;
+}
+
+void log_line(int level, const char *fmt, ...) {
+  if (log_level() < level) return;
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  fprintf(stderr, "pgb200: %s\n", buf);
+}
+
+void count_h2d(size_t bytes) { g_h2d.fetch_add((int64_t)bytes, std::memory_order_relaxed); }
+void count_d2h(size_t bytes) { g_d2h.fetch_add((int64_t)bytes, std::memory_order_relaxed); }
+
+int32_t take_device_status(Runtime *rt) {
+  const int32_t v = rt->status_host[0];
+  if (v == 0) return PGB200_OK;
+  const int32_t detail = rt->status_host[1];
+  rt->status_host[0] = 0;
+  rt->status_host[1] = 0;
+  set_error("a device-side bounded wait expired (code %d, detail %d)", v, detail);
+  return PGB200_ERR_TIMEOUT;
+}
+
+int32_t sync_check(Runtime *rt, cudaStream_t s) {
+  PGB_CUDA(cudaStreamSynchronize(s));
+  return take_device_status(rt);
+}
+
+// ---------------------------------------------------------------------------
+// Per-call device timing (PGB200_PROFILE): a ring of event pairs; a pair is
+// resolved into its entry's totals when its slot comes round again or at dump.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr int PROF_RING = 512;
+struct ProfSlot {
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  int device = -1;
+  const char *name = nullptr;
+  bool pending = false;
+};
+struct ProfTotal {
+  int64_t calls = 0;
+  double ms = 0.0;
+};
+std::mutex g_prof_mu;
+ProfSlot g_prof_ring[PROF_RING];
+int64_t g_prof_next = 0;
+std::map<std::string, ProfTotal> g_prof_totals;
+std::atomic<int> g_prof_on{-1};  // -1: not decided yet (environment not read)
+thread_local int tls_entry_depth = 0;
+
+bool profile_on() {
+  int v = g_prof_on.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char *e = getenv("PGB200_PROFILE");
+    v = (e && *e && atoi(e) != 0) ? 1 : 0;
+    g_prof_on.store(v, std::memory_order_relaxed);
+  }
+  return v == 1;
+}
+
+// Caller holds g_prof_mu.
+void prof_resolve(ProfSlot &sl) {
+  if (!sl.pending) return;
+  sl.pending = false;
+  float ms = 0.0f;
+  if (cudaEventSynchronize(sl.e1) == cudaSuccess &&
+      cudaEventElapsedTime(&ms, sl.e0, sl.e1) == cudaSuccess) {
+    ProfTotal &t = g_prof_totals[sl.name];
+    t.calls++;
+    t.ms += ms;
+  } else {
+    cudaGetLastError();
+  }
+}
+}  // namespace
+
+void profile_enable(bool on) { g_prof_on.store(on ? 1 : 0, std::memory_order_relaxed); }
+
+void profile_reset() {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (ProfSlot &sl : g_prof_ring) {
+    if (sl.e0) cudaEventDestroy(sl.e0);
+    if (sl.e1) cudaEventDestroy(sl.e1);
+    sl = ProfSlot();
+  }
+  g_prof_totals.clear();
+  g_prof_next = 0;
+}
+
+int32_t profile_dump(const char *path) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (ProfSlot &sl : g_prof_ring) prof_resolve(sl);
+  FILE *f = path ? fopen(path, "a") : stderr;
+  if (!f) {
+    set_error("ProfileDump: cannot open '%s'", path);
+    return PGB200_ERR_INVALID;
+  }
+  for (auto &kv : g_prof_totals)
+    fprintf(f, "%s calls %lld total_ms %.6f mean_ms %.6f\n", kv.first.c_str(),
+            (long long)kv.second.calls, kv.second.ms, kv.second.ms / (double)kv.second.calls);
+  if (path) fclose(f);
+  return PGB200_OK;
+}
+
+EntryScope::EntryScope(const char *n, void *st)
+    : name(n), stream((cudaStream_t)st), slot(-1), outer(tls_entry_depth++ == 0) {
+  if (!outer || !profile_on()) return;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  const int i = (int)(g_prof_next++ % PROF_RING);
+  ProfSlot &sl = g_prof_ring[i];
+  prof_resolve(sl);
+  if (sl.device != dev) {  // events belong to the device they were created on
+    if (sl.e0) cudaEventDestroy(sl.e0);
+    if (sl.e1) cudaEventDestroy(sl.e1);
+    sl.e0 = sl.e1 = nullptr;
+    if (cudaEventCreate(&sl.e0) != cudaSuccess || cudaEventCreate(&sl.e1) != cudaSuccess) {
+      cudaGetLastError();
+      sl.device = -1;
+      return;
+    }
+    sl.device = dev;
+  }
+  sl.name = name;
+  if (cudaEventRecord(sl.e0, stream) == cudaSuccess) slot = i;
+}
+
+EntryScope::~EntryScope() {
+  tls_entry_depth--;
+  if (slot >= 0) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    ProfSlot &sl = g_prof_ring[slot];
+    if (cudaEventRecord(sl.e1, stream) == cudaSuccess) sl.pending = true;
+  }
+  if (outer && log_level() >= 2) {
+    static const char *const paths[] = {"none", "SIMT", "DMMA", "tcgen05 3xTF32", "HBM-streaming"};
+    const int32_t pth = tls_path;
+    log_line(2, "%s -> %s kernels, %lld launches by this thread so far", name,
+             paths[(pth >= 0 && pth <= 4) ? pth : 0], (long long)tls_launches);
+  }
+}
+
+bool registry_lookup(const void *p, void **dev, bool written) {
+  if (g_pin_count.load(std::memory_order_acquire) == 0 || !p) return false;
+  int cur = 0;
+  if (cudaGetDevice(&cur) != cudaSuccess) return false;
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  std::lock_guard<std::mutex> lk(g_pin_mu);
+  auto it = g_pins.upper_bound(a);
+  if (it == g_pins.begin()) return false;
+  --it;
+  if (a >= it->first + it->second.bytes || it->second.device != cur) return false;
+  *dev = static_cast<char *>(it->second.dev) + (a - it->first);
+  if (written) it->second.written = true;
+  return true;
+}
 
 void note_launch(Path p, int n) {
   tls_path = p;
@@ -109,28 +286,82 @@ int32_t get_runtime(Runtime **out) {
   }
   g_rt[dev] = rt;
   *out = rt;
+  log_line(1, "device %d: %s, %d SMs, runtime initialised", dev, prop.name, prop.multiProcessorCount);
   return PGB200_OK;
 }
 
-int32_t get_workspace(cudaStream_t stream, size_t bytes, void **ptr) {
-  int dev = 0;
-  PGB_CUDA(cudaGetDevice(&dev));
-  std::lock_guard<std::mutex> lk(g_mu);
-  Ws &w = g_ws[std::make_pair(dev, stream)];
-  if (w.bytes < bytes) {
-    if (w.ptr) {
-      // The old block may still be in use by work queued on `stream`.
-      PGB_CUDA(cudaStreamSynchronize(stream));
-      PGB_CUDA(cudaFree(w.ptr));
-      w.ptr = nullptr;
-      w.bytes = 0;
-    }
-    size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
-    PGB_CUDA(cudaMalloc(&w.ptr, want));
-    w.bytes = want;
+// ---------------------------------------------------------------------------
+// Per-call scratch (see PoolBuffer in pgb200_internal.h).
+// ---------------------------------------------------------------------------
+namespace {
+constexpr size_t SMALL_SCRATCH = size_t(32) << 20;
+struct CachedBlock {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+  int device = 0;
+};
+// Every cached block is also listed here so that pgb200Shutdown can release the
+// blocks of all threads; a thread notices through the epoch that its cache is gone.
+std::mutex g_cache_mu;
+std::vector<CachedBlock *> g_cache_all;
+std::atomic<uint64_t> g_cache_epoch{1};
+struct ThreadCache {
+  uint64_t epoch = 0;
+  std::map<std::pair<int, cudaStream_t>, CachedBlock *> blocks;
+};
+thread_local ThreadCache tls_cache;
+}  // namespace
+
+cudaError_t PoolBuffer::alloc(size_t bytes, cudaStream_t s) {
+  stream = s;
+  if (bytes == 0) bytes = 16;
+  if (bytes > SMALL_SCRATCH) {
+    owned = true;
+    return cudaMallocAsync(&ptr, bytes, s);
   }
-  *ptr = w.ptr;
-  return PGB200_OK;
+  owned = false;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const uint64_t epoch = g_cache_epoch.load(std::memory_order_acquire);
+  if (tls_cache.epoch != epoch) {  // first use, or a shutdown released everything
+    tls_cache.blocks.clear();
+    tls_cache.epoch = epoch;
+  }
+  CachedBlock *&slot = tls_cache.blocks[std::make_pair(dev, s)];
+  if (!slot) {
+    slot = new CachedBlock();
+    slot->device = dev;
+    std::lock_guard<std::mutex> lk(g_cache_mu);
+    g_cache_all.push_back(slot);
+  }
+  if (slot->bytes < bytes) {
+    // The old block may still be read by this thread's earlier calls on `s`:
+    // release it in stream order.
+    if (slot->ptr) cudaFreeAsync(slot->ptr, s);
+    slot->ptr = nullptr;
+    slot->bytes = 0;
+    const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    e = cudaMallocAsync(&slot->ptr, want, s);
+    if (e != cudaSuccess) return e;
+    slot->bytes = want;
+  }
+  ptr = slot->ptr;
+  return cudaSuccess;
+}
+
+static void release_cached_scratch() {
+  std::lock_guard<std::mutex> lk(g_cache_mu);
+  for (CachedBlock *b : g_cache_all) {
+    if (b->ptr) {
+      cudaSetDevice(b->device);
+      cudaDeviceSynchronize();
+      cudaFree(b->ptr);
+    }
+    delete b;
+  }
+  g_cache_all.clear();
+  g_cache_epoch.fetch_add(1, std::memory_order_acq_rel);
 }
 
 int32_t encode_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank,
@@ -207,11 +438,24 @@ bool is_host_pointer(const void *p) {
   return a.type == cudaMemoryTypeUnregistered || a.type == cudaMemoryTypeHost;
 }
 
+bool needs_staging(const void *p) {
+  void *d = nullptr;
+  return is_host_pointer(p) && !registry_lookup(p, &d, false);
+}
+
 template <typename T>
 int32_t stage(cudaStream_t s, const T *p, int64_t rows, int64_t cols, int64_t ld, bool in,
               bool out, Staged<T> *st) {
   st->rows = rows;
   st->cols = cols;
+  void *resident = nullptr;
+  if (rows > 0 && cols > 0 && registry_lookup(p, &resident, out)) {
+    // Inside a pgb200Pin range: the device copy is the array, same layout.
+    st->dev = static_cast<T *>(resident);
+    st->ld = ld;
+    st->host = nullptr;
+    return PGB200_OK;
+  }
   if (rows == 0 || cols == 0 || !is_host_pointer(p)) {
     st->dev = const_cast<T *>(p);
     st->ld = ld;
@@ -236,6 +480,7 @@ int32_t stage(cudaStream_t s, const T *p, int64_t rows, int64_t cols, int64_t ld
     else
       PGB_CUDA(cudaMemcpy2DAsync(st->dev, st->ld * sizeof(T), p, ld * sizeof(T), cols * sizeof(T),
                                  rows, cudaMemcpyHostToDevice, s));
+    count_h2d((size_t)rows * cols * sizeof(T));
   }
   return PGB200_OK;
 }
@@ -250,6 +495,7 @@ int32_t finish(cudaStream_t s, Staged<T> *st) {
     else
       PGB_CUDA(cudaMemcpy2DAsync(st->host, st->host_ld * sizeof(T), st->dev, st->ld * sizeof(T),
                                  st->cols * sizeof(T), st->rows, cudaMemcpyDeviceToHost, s));
+    count_d2h((size_t)st->rows * st->cols * sizeof(T));
   }
   T *d = st->dev;
   st->host = nullptr;  // released below, whatever cudaFreeAsync answers
@@ -328,14 +574,25 @@ int32_t pgb200Shutdown(void) {
   std::lock_guard<std::mutex> lk(g_mu);
   int cur = 0;
   cudaGetDevice(&cur);
-  for (auto &kv : g_ws) {
-    cudaSetDevice(kv.first.first);
-    cudaDeviceSynchronize();
-    if (kv.second.ptr) cudaFree(kv.second.ptr);
+  if (const char *f = getenv("PGB200_PROFILE_FILE")) profile_dump(f);
+  mg_shutdown();
+  release_cached_scratch();
+  profile_reset();
+  {
+    // Registered ranges that were never unpinned: their device copies go,
+    // nothing is downloaded (pgb200Unpin is the call that brings data back).
+    std::lock_guard<std::mutex> pl(g_pin_mu);
+    for (auto &kv : g_pins) {
+      cudaSetDevice(kv.second.device);
+      cudaDeviceSynchronize();
+      cudaFree(kv.second.dev);
+    }
+    g_pins.clear();
+    g_pin_count.store(0, std::memory_order_release);
   }
-  g_ws.clear();
   for (auto &kv : g_rt) {
     cudaSetDevice(kv.first);
+    cudaDeviceSynchronize();
     cudaFreeHost(const_cast<int32_t *>(kv.second->status_host));
     cudaStreamDestroy(kv.second->copy_in);
     cudaStreamDestroy(kv.second->copy_out);
@@ -358,15 +615,99 @@ int64_t pgb200LaunchCount(void) { return tls_launches; }
 int32_t pgb200PollDeviceStatus(void) {
   Runtime *rt = nullptr;
   PGB_TRY(get_runtime(&rt));
-  int32_t v = rt->status_host[0];
-  if (v != 0) {
-    set_error("a device-side bounded wait expired (code %d, detail %d)", v, rt->status_host[1]);
-    rt->status_host[0] = 0;
-    rt->status_host[1] = 0;
-    return PGB200_ERR_TIMEOUT;
-  }
+  return take_device_status(rt);
+}
+
+int32_t pgb200TransferCounters(int64_t *h2d_bytes, int64_t *d2h_bytes) {
+  if (h2d_bytes) *h2d_bytes = g_h2d.load(std::memory_order_relaxed);
+  if (d2h_bytes) *d2h_bytes = g_d2h.load(std::memory_order_relaxed);
   return PGB200_OK;
 }
+
+int32_t pgb200Pin(const void *host, uint64_t bytes) {
+  Runtime *rt = nullptr;
+  PGB_TRY(get_runtime(&rt));
+  PGB_REQUIRE(host && bytes > 0, "Pin: null pointer or empty range");
+  PGB_REQUIRE(is_host_pointer(host), "Pin: the range must be host memory");
+  const uintptr_t a = reinterpret_cast<uintptr_t>(host);
+  int dev = 0;
+  PGB_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lk(g_pin_mu);
+    auto it = g_pins.upper_bound(a);
+    const bool hits_next = it != g_pins.end() && it->first < a + bytes;
+    bool hits_prev = false;
+    if (it != g_pins.begin()) {
+      auto pv = std::prev(it);
+      hits_prev = a < pv->first + pv->second.bytes;
+    }
+    PGB_REQUIRE(!hits_next && !hits_prev, "Pin: the range overlaps a registered range");
+  }
+  PinEntry e;
+  e.bytes = (size_t)bytes;
+  e.device = dev;
+  PGB_CUDA(cudaMalloc(&e.dev, e.bytes));
+  cudaError_t ce = cudaMemcpy(e.dev, host, e.bytes, cudaMemcpyHostToDevice);
+  if (ce != cudaSuccess) {
+    cudaFree(e.dev);
+    return report_cuda(ce, "cudaMemcpy(Pin upload)");
+  }
+  count_h2d(e.bytes);
+  {
+    std::lock_guard<std::mutex> lk(g_pin_mu);
+    g_pins[a] = e;
+    g_pin_count.store((int)g_pins.size(), std::memory_order_release);
+  }
+  log_line(1, "Pin %p: %llu bytes resident on device %d", host, (unsigned long long)bytes, dev);
+  return PGB200_OK;
+}
+
+static int32_t pin_download(const void *host, bool release) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(host);
+  PinEntry e;
+  {
+    std::lock_guard<std::mutex> lk(g_pin_mu);
+    auto it = g_pins.find(a);
+    PGB_REQUIRE(it != g_pins.end(), "%s: %p is not the start of a registered range",
+                release ? "Unpin" : "PinSync", host);
+    e = it->second;
+    it->second.written = false;
+    if (release) {
+      g_pins.erase(it);
+      g_pin_count.store((int)g_pins.size(), std::memory_order_release);
+    }
+  }
+  int cur = 0;
+  PGB_CUDA(cudaGetDevice(&cur));
+  if (cur != e.device) PGB_CUDA(cudaSetDevice(e.device));
+  int32_t st = PGB200_OK;
+  cudaError_t ce = cudaDeviceSynchronize();  // every call that used the copy has finished
+  if (ce == cudaSuccess) {
+    Runtime *rt = nullptr;
+    st = get_runtime(&rt);
+    if (st == PGB200_OK) st = take_device_status(rt);
+  }
+  if (ce == cudaSuccess && st == PGB200_OK && e.written) {
+    ce = cudaMemcpy(const_cast<void *>(host), e.dev, e.bytes, cudaMemcpyDeviceToHost);
+    if (ce == cudaSuccess) count_d2h(e.bytes);
+  }
+  if (release) cudaFree(e.dev);
+  if (cur != e.device) cudaSetDevice(cur);
+  if (ce != cudaSuccess) return report_cuda(ce, release ? "Unpin download" : "PinSync download");
+  if (st == PGB200_OK)
+    log_line(1, "%s %p: %s", release ? "Unpin" : "PinSync", host,
+             e.written ? "downloaded" : "host copy was current");
+  return st;
+}
+
+int32_t pgb200PinSync(const void *host) { return pin_download(host, false); }
+int32_t pgb200Unpin(const void *host) { return pin_download(host, true); }
+
+int32_t pgb200ProfileEnable(int32_t on) {
+  profile_enable(on != 0);
+  return PGB200_OK;
+}
+int32_t pgb200ProfileDump(const char *path) { return profile_dump(path); }
 
 int32_t pgb200SelfTestWaitTimeout(void *stream, int64_t limit_cycles) {
   return wait_timeout_selftest((cudaStream_t)stream, (long long)limit_cycles);
@@ -488,6 +829,8 @@ static int32_t gemm_host_pipelined(Runtime *rt, cudaStream_t s, int64_t M, int64
     PGB_CUDA(cudaStreamWaitEvent(rt->copy_in, ev_start, 0));
     PGB_CUDA(cudaStreamWaitEvent(rt->copy_out, ev_start, 0));
     PGB_CUDA(copy_rows(dB, dldb, B, ldb, b_rows, b_cols, cudaMemcpyHostToDevice, rt->copy_in));
+    count_h2d((size_t)(b_rows * b_cols + M * K + (beta != (T)0 ? M * N : 0)) * sizeof(T));
+    count_d2h((size_t)M * N * sizeof(T));
     for (int i = 0; i < nb; i++) {
       const int64_t r0 = i * rows_per, rows = (M - r0 < rows_per) ? (M - r0) : rows_per;
       PGB_CUDA(copy_rows(dA + r0 * dlda, dlda, A + r0 * lda, lda, rows, K, cudaMemcpyHostToDevice,
@@ -521,7 +864,9 @@ static int32_t gemm_host_pipelined(Runtime *rt, cudaStream_t s, int64_t M, int64
   PGB_CUDA(e1);
   PGB_CUDA(e2);
   PGB_CUDA(e3);
-  return PGB200_OK;
+  // Row blocks are downloaded as they finish, so a block whose kernel gave up
+  // may already be in C: the status tells the caller that C is not valid.
+  return take_device_status(rt);
 }
 
 template <typename T>
@@ -539,8 +884,8 @@ static int32_t gemm_entry(void *stream, int64_t M, int64_t N, int64_t K, T alpha
               "gemm: A/B null or lda (%lld) < K (%lld) or ldb (%lld) too small for N (%lld)",
               (long long)lda, (long long)K, (long long)ldb, (long long)N);
   cudaStream_t s = (cudaStream_t)stream;
-  if (K > 0 && M >= 1024 && (double)M * (double)N * (double)K >= 1e9 && is_host_pointer(A) &&
-      is_host_pointer(B) && is_host_pointer(C))
+  if (K > 0 && M >= 1024 && (double)M * (double)N * (double)K >= 1e9 && needs_staging(A) &&
+      needs_staging(B) && needs_staging(C))
     return gemm_host_pipelined<T>(rt, s, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, transB);
   Staged<T> sa, sb, sc;
   PGB_TRY(stage<T>(s, A, M, K, lda, true, false, &sa));
@@ -553,6 +898,7 @@ static int32_t gemm_entry(void *stream, int64_t M, int64_t N, int64_t K, T alpha
   int32_t st = gemm_device<T>(s, M, N, K, alpha, sa.dev, sa.ld, sb.dev, sb.ld, transB, beta,
                               sc.dev, sc.ld, false, 0);
   if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
+  if (staged) PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sc));
@@ -585,6 +931,7 @@ static int32_t syrk_entry(void *stream, int64_t N, int64_t K, int64_t row0, int6
   int32_t st = gemm_device<T>(s, row1 - row0, row1, K, alpha, sa.dev + row0 * sa.ld, sa.ld,
                               sa.dev, sa.ld, true, beta, sc.dev, sc.ld, true, row0);
   if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
+  if (staged) PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sc));
   if (staged) PGB_CUDA(cudaStreamSynchronize(s));
@@ -615,6 +962,7 @@ static int32_t syr2k_entry(void *stream, int64_t N, int64_t K, T alpha, const T 
     st = gemm_device<T>(s, N, N, K, alpha, sa.dev, sa.ld, sb.dev, sb.ld, true, (T)1, sc.dev, sc.ld,
                         true, 0);
   if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
+  if (staged) PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sc));
@@ -647,6 +995,7 @@ static int32_t matvec_entry(void *stream, int64_t M, int64_t N, const double *A,
                              y1 ? sy1.dev : nullptr, y2 ? sx2.dev : nullptr,
                              y2 ? sy2.dev : nullptr);
   if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
+  if (staged) PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sx1));
   PGB_TRY(finish(s, &sy1));
@@ -663,55 +1012,65 @@ extern "C" {
 int32_t pgb200Dgemm(void *stream, int64_t M, int64_t N, int64_t K, double alpha, const double *A,
                     int64_t lda, const double *B, int64_t ldb, double beta, double *C,
                     int64_t ldc) {
+  PGB_ENTRY(stream);
   return gemm_entry<double>(stream, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
 }
 
 int32_t pgb200Sgemm(void *stream, int64_t M, int64_t N, int64_t K, float alpha, const float *A,
                     int64_t lda, const float *B, int64_t ldb, float beta, float *C, int64_t ldc) {
+  PGB_ENTRY(stream);
   return gemm_entry<float>(stream, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
 }
 
 int32_t pgb200DgemmNT(void *stream, int64_t M, int64_t N, int64_t K, double alpha,
                       const double *A, int64_t lda, const double *B, int64_t ldb, double beta,
                       double *C, int64_t ldc) {
+  PGB_ENTRY(stream);
   return gemm_entry<double>(stream, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, true);
 }
 
 int32_t pgb200SgemmNT(void *stream, int64_t M, int64_t N, int64_t K, float alpha, const float *A,
                       int64_t lda, const float *B, int64_t ldb, float beta, float *C,
                       int64_t ldc) {
+  PGB_ENTRY(stream);
   return gemm_entry<float>(stream, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, true);
 }
 
 int32_t pgb200Dsyr2k(void *stream, int64_t N, int64_t K, double alpha, const double *A,
                      int64_t lda, const double *B, int64_t ldb, double beta, double *C,
                      int64_t ldc) {
+  PGB_ENTRY(stream);
   return syr2k_entry<double>(stream, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
 }
 
 int32_t pgb200Ssyr2k(void *stream, int64_t N, int64_t K, float alpha, const float *A, int64_t lda,
                      const float *B, int64_t ldb, float beta, float *C, int64_t ldc) {
+  PGB_ENTRY(stream);
   return syr2k_entry<float>(stream, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
 }
 
 int32_t pgb200Dsyrk(void *stream, int64_t N, int64_t K, double alpha, const double *A,
                     int64_t lda, double beta, double *C, int64_t ldc) {
+  PGB_ENTRY(stream);
   return syrk_entry<double>(stream, N, K, 0, N, alpha, A, lda, beta, C, ldc);
 }
 
 int32_t pgb200Ssyrk(void *stream, int64_t N, int64_t K, float alpha, const float *A, int64_t lda,
                     float beta, float *C, int64_t ldc) {
+  PGB_ENTRY(stream);
   return syrk_entry<float>(stream, N, K, 0, N, alpha, A, lda, beta, C, ldc);
 }
 
 int32_t pgb200SsyrkRows(void *stream, int64_t N, int64_t K, int64_t row0, int64_t row1,
                         float alpha, const float *A, int64_t lda, float beta, float *C,
                         int64_t ldc) {
+  PGB_ENTRY(stream);
   return syrk_entry<float>(stream, N, K, row0, row1, alpha, A, lda, beta, C, ldc);
 }
 
 int32_t pgb200Dgemv(void *stream, int32_t transA, int64_t M, int64_t N, double alpha,
                     const double *A, int64_t lda, const double *x, double beta, double *y) {
+  PGB_ENTRY(stream);
   PGB_REQUIRE(y || (transA ? N : M) == 0, "gemv: y is null");
   if (transA) return matvec_entry(stream, M, N, A, lda, alpha, beta, nullptr, nullptr, x, y);
   return matvec_entry(stream, M, N, A, lda, alpha, beta, x, y, nullptr, nullptr);
@@ -720,6 +1079,7 @@ int32_t pgb200Dgemv(void *stream, int32_t transA, int64_t M, int64_t N, double a
 int32_t pgb200DgemvPair(void *stream, int64_t M, int64_t N, double alpha, const double *A,
                         int64_t lda, const double *x1, const double *x2, double beta, double *y1,
                         double *y2) {
+  PGB_ENTRY(stream);
   PGB_REQUIRE((y1 || M == 0) && (y2 || N == 0), "gemv pair: null output vector");
   return matvec_entry(stream, M, N, A, lda, alpha, beta, x1, y1, x2, y2);
 }
@@ -727,6 +1087,7 @@ int32_t pgb200DgemvPair(void *stream, int64_t M, int64_t N, double alpha, const 
 int32_t pgb200Dgemver(void *stream, int64_t N, double alpha, double beta, double *A, int64_t lda,
                       const double *u1, const double *v1, const double *u2, const double *v2,
                       double *w, double *x, const double *y, const double *z) {
+  PGB_ENTRY(stream);
   Runtime *rt = nullptr;
   PGB_TRY(get_runtime(&rt));
   PGB_REQUIRE(N >= 0, "gemver: negative size");
@@ -749,6 +1110,7 @@ int32_t pgb200Dgemver(void *stream, int64_t N, double alpha, double beta, double
   int32_t st = stream_gemver(s, N, alpha, beta, sa.dev, sa.ld, su1.dev, sv1.dev, su2.dev, sv2.dev,
                              sw.dev, sx.dev, sy.dev, sz.dev);
   if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
+  if (staged) PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &su1));
   PGB_TRY(finish(s, &sv1));
@@ -764,6 +1126,7 @@ int32_t pgb200Dgemver(void *stream, int64_t N, double alpha, double beta, double
 
 int32_t pgb200Dmvt(void *stream, int64_t N, const double *A, int64_t lda, const double *y1,
                    const double *y2, double *x1, double *x2) {
+  PGB_ENTRY(stream);
   PGB_REQUIRE(N == 0 || (x1 && x2 && y1 && y2), "mvt: null vector");
   return matvec_entry(stream, N, N, A, lda, 1.0, 1.0, y1, x1, y2, x2);
 }
@@ -772,16 +1135,19 @@ int32_t pgb200Dmvt(void *stream, int64_t N, const double *A, int64_t lda, const 
 
 int32_t pgb200_kernel_gemm(int ni, int nj, int nk, double alpha, double beta, double *C,
                            const double *A, const double *B) {
+  PGB_ENTRY(nullptr);
   return pgb200Dgemm(nullptr, ni, nj, nk, alpha, A, nk, B, nj, beta, C, nj);
 }
 
 int32_t pgb200_kernel_gemm_f32(int ni, int nj, int nk, float alpha, float beta, float *C,
                                const float *A, const float *B) {
+  PGB_ENTRY(nullptr);
   return pgb200Sgemm(nullptr, ni, nj, nk, alpha, A, nk, B, nj, beta, C, nj);
 }
 
 int32_t pgb200_kernel_2mm(int ni, int nj, int nk, int nl, double alpha, double beta, double *tmp,
                           const double *A, const double *B, const double *C, double *D) {
+  PGB_ENTRY(nullptr);
   // tmp = alpha*A*B stays in HBM between the two contractions; it is copied
   // back once because the C source leaves it as a live-out array.
   Runtime *rt = nullptr;
@@ -798,6 +1164,7 @@ int32_t pgb200_kernel_2mm(int ni, int nj, int nk, int nl, double alpha, double b
   if (r == PGB200_OK)
     r = pgb200Dgemm(s, ni, nl, nj, 1.0, st.dev, st.ld, sc.dev, sc.ld, beta, sd.dev, sd.ld);
   if (r != PGB200_OK) return r;  // staged copies are released, nothing is copied back
+  PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sc));
@@ -809,12 +1176,14 @@ int32_t pgb200_kernel_2mm(int ni, int nj, int nk, int nl, double alpha, double b
 
 int32_t pgb200_kernel_mvt(int n, double *x1, double *x2, const double *y_1, const double *y_2,
                           const double *A) {
+  PGB_ENTRY(nullptr);
   return pgb200Dmvt(nullptr, n, A, n, y_1, y_2, x1, x2);
 }
 
 int32_t pgb200_kernel_3mm(int ni, int nj, int nk, int nl, int nm, double *E, const double *A,
                           const double *B, double *F, const double *C, const double *D,
                           double *G) {
+  PGB_ENTRY(nullptr);
   // E = A*B and F = C*D stay in HBM for G = E*F; all three are copied back
   // because the C source leaves them as live-out arrays.
   Runtime *rt = nullptr;
@@ -835,6 +1204,7 @@ int32_t pgb200_kernel_3mm(int ni, int nj, int nk, int nl, int nm, double *E, con
   if (r == PGB200_OK)
     r = pgb200Dgemm(s, ni, nl, nj, 1.0, se.dev, se.ld, sf.dev, sf.ld, 0.0, sg.dev, sg.ld);
   if (r != PGB200_OK) return r;  // staged copies are released, nothing is copied back
+  PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sc));
@@ -848,6 +1218,7 @@ int32_t pgb200_kernel_3mm(int ni, int nj, int nk, int nl, int nm, double *E, con
 
 int32_t pgb200_kernel_atax(int m, int n, const double *A, const double *x, double *y,
                            double *tmp) {
+  PGB_ENTRY(nullptr);
   // tmp = A x, then y = A^T tmp.  A is staged once and read twice on the GPU.
   Runtime *rt = nullptr;
   PGB_TRY(get_runtime(&rt));
@@ -861,6 +1232,7 @@ int32_t pgb200_kernel_atax(int m, int n, const double *A, const double *x, doubl
   int32_t r = pgb200Dgemv(s, 0, m, n, 1.0, sa.dev, sa.ld, sx.dev, 0.0, st.dev);
   if (r == PGB200_OK) r = pgb200Dgemv(s, 1, m, n, 1.0, sa.dev, sa.ld, st.dev, 0.0, sy.dev);
   if (r != PGB200_OK) return r;  // staged copies are released, nothing is copied back
+  PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sx));
   PGB_TRY(finish(s, &sy));
@@ -871,12 +1243,14 @@ int32_t pgb200_kernel_atax(int m, int n, const double *A, const double *x, doubl
 
 int32_t pgb200_kernel_bicg(int m, int n, const double *A, double *s_out, double *q,
                            const double *p, const double *r) {
+  PGB_ENTRY(nullptr);
   // A is n x m: q = A p (n entries), s = A^T r (m entries), one pass.
   return pgb200DgemvPair(nullptr, n, m, 1.0, A, m, p, r, 0.0, q, s_out);
 }
 
 int32_t pgb200_kernel_gesummv(int n, double alpha, double beta, const double *A, const double *B,
                               double *tmp, const double *x, double *y) {
+  PGB_ENTRY(nullptr);
   Runtime *rt = nullptr;
   PGB_TRY(get_runtime(&rt));
   PGB_REQUIRE(n >= 0, "kernel_gesummv: negative size");
@@ -891,6 +1265,7 @@ int32_t pgb200_kernel_gesummv(int n, double alpha, double beta, const double *A,
   if (r == PGB200_OK) r = pgb200Dgemv(s, 0, n, n, 1.0, sb.dev, sb.ld, sx.dev, 0.0, sy.dev);  // y = B x
   if (r == PGB200_OK) r = stream_axpby(s, n, alpha, st.dev, beta, sy.dev);  // y = alpha*tmp + beta*y
   if (r != PGB200_OK) return r;  // staged copies are released, nothing is copied back
+  PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sx));
@@ -901,26 +1276,31 @@ int32_t pgb200_kernel_gesummv(int n, double alpha, double beta, const double *A,
 }
 
 int32_t pgb200_kernel_syrk(int n, int m, double alpha, double beta, double *C, const double *A) {
+  PGB_ENTRY(nullptr);
   return pgb200Dsyrk(nullptr, n, m, alpha, A, m, beta, C, n);
 }
 
 int32_t pgb200_kernel_gemver(int n, double alpha, double beta, double *A, const double *u1,
                              const double *v1, const double *u2, const double *v2, double *w,
                              double *x, const double *y, const double *z) {
+  PGB_ENTRY(nullptr);
   return pgb200Dgemver(nullptr, n, alpha, beta, A, n, u1, v1, u2, v2, w, x, y, z);
 }
 
 int32_t pgb200_kernel_syr2k(int n, int m, double alpha, double beta, double *C, const double *A,
                             const double *B) {
+  PGB_ENTRY(nullptr);
   return pgb200Dsyr2k(nullptr, n, m, alpha, A, m, B, m, beta, C, n);
 }
 
 int32_t pgb200_kernel_syr2k_f32(int n, int m, float alpha, float beta, float *C, const float *A,
                                 const float *B) {
+  PGB_ENTRY(nullptr);
   return pgb200Ssyr2k(nullptr, n, m, alpha, A, m, B, m, beta, C, n);
 }
 
 int32_t pgb200_kernel_syrk_f32(int n, int m, float alpha, float beta, float *C, const float *A) {
+  PGB_ENTRY(nullptr);
   return pgb200Ssyrk(nullptr, n, m, alpha, A, m, beta, C, n);
 }
 

@@ -1294,7 +1294,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   // layout several percent slower (measured: 398 vs 372 ms at 32768^3).  The
   // pre-pass is paid once per call, the slowdown per row of A: for tall
   // products transpose B once, otherwise use it in place.
-  const bool b_mn = !transB && b_raw && (M < 12288 || rt->cfg.reserved[1] == 1);
+  const bool b_mn = !transB && b_raw && (M < 12288 || rt->cfg.sgemm_b_in_place);
 
   // Tile width: 256 columns normally.  When 256-wide tiles would leave more
   // than half of the SMs without a tile, either the K range of every tile is
@@ -1308,7 +1308,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   int bn = (tiles256 * 2 <= rt->num_sms) ? 64 : 256;
   int splits = 1;
   int64_t kper = nkb_all;
-  if (bn == 64 && rt->cfg.reserved[0] != 4) {
+  if (bn == 64 && !rt->cfg.no_split_k) {
     int64_t sp = rt->num_sms / tiles256;       // CTAs available per tile
     const int64_t by_k = nkb_all / (2 * chunk);  // at least two chunks per split
     if (sp > by_k) sp = by_k;
@@ -1331,8 +1331,9 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   const size_t b_hi_n = b_inplace ? 0 : (size_t)N * Kp;
   const size_t a_lo_n = shared_planes ? 0 : (size_t)M * Kp;
   const size_t a_hi_n = (shared_planes || a_raw) ? 0 : (size_t)M * Kp;
-  void *ws = nullptr;
-  PGB_TRY(get_workspace(s, (b_lo_n + b_hi_n + a_lo_n + a_hi_n + part_n) * sizeof(float), &ws));
+  PoolBuffer scratch;  // this call's own planes and partial products, released in stream order
+  PGB_CUDA(scratch.alloc((b_lo_n + b_hi_n + a_lo_n + a_hi_n + part_n) * sizeof(float), s));
+  void *ws = scratch.ptr;
   float *Blo = static_cast<float *>(ws);
   float *Bhi_pl = Blo + b_lo_n;
   float *Alo_pl = Bhi_pl + b_hi_n;
@@ -1432,10 +1433,10 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   // Large full products: the two-CTA kernel (256x256 tiles on SM pairs).
   // Measured against the one-CTA kernel: 8192^3 4.01-4.18 vs 4.45 ms, 16384^3
   // 36.7-38.1 vs 40.5-40.8 ms, 32768^3 354-356 vs 423-443 ms (same GPU, back to
-  // back).  reserved[0] == 2 switches it off.
+  // back).  pgb200Config.no_two_cta switches it off.
   const int pn = 256;  // pair tile width (128 also works: measured slower than split-K where it applied)
   const bool two_cta = bn == 256 && splits == 1 && M >= 512 && (!b_mn || bhi_blocked) &&
-                       rt->cfg.reserved[0] != 2;
+                       !rt->cfg.no_two_cta;
   if (two_cta) {
     CUtensorMap m2Bhi, m2Blo;
     if (b_mn) {

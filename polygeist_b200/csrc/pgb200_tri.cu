@@ -155,6 +155,7 @@ int32_t symm_entry(void *stream, int64_t M, int64_t N, T alpha, const T *A, int6
   const int32_t st =
       symm_device<T>(s, M, N, alpha, sa.dev, sa.ld, sb.dev, sb.ld, beta, sc.dev, sc.ld);
   if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
+  if (staged) PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   PGB_TRY(finish(s, &sc));
@@ -179,6 +180,7 @@ int32_t trmm_entry(void *stream, int64_t M, int64_t N, T alpha, const T *A, int6
   const bool staged = sa.host || sb.host;
   const int32_t st = trmm_device<T>(rt, s, M, N, alpha, sa.dev, sa.ld, sb.dev, sb.ld);
   if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
+  if (staged) PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sb));
   if (staged) PGB_CUDA(cudaStreamSynchronize(s));
@@ -196,9 +198,13 @@ int32_t doitgen_entry(void *stream, int64_t R, int64_t P, double *A, int64_t lda
   PGB_REQUIRE(A && C4 && lda >= P && ldc4 >= P, "doitgen: null pointer or lda/ldc4 < NP (%lld)",
               (long long)P);
   cudaStream_t s = (cudaStream_t)stream;
-  Staged<double> sa, sc;
-  PGB_TRY(stage<double>(s, A, R, P, lda, true, false, &sa));
+  Staged<double> sa, sc, ss;
+  // `out` = true only marks a registered (pgb200Pin) A as written; a staged A
+  // receives the result by the explicit copy below instead of finish().
+  PGB_TRY(stage<double>(s, A, R, P, lda, true, true, &sa));
+  sa.copy_back = false;
   PGB_TRY(stage<double>(s, C4, P, P, ldc4, true, false, &sc));
+  if (sum) PGB_TRY(stage<double>(s, sum, 1, P, P, false, true, &ss));
   // The product cannot be formed in place; the result goes to a second buffer
   // and from there to the caller's A (host array: by the copy-back itself).
   const int64_t ldo = round_up(P, 2);
@@ -207,16 +213,23 @@ int32_t doitgen_entry(void *stream, int64_t R, int64_t P, double *A, int64_t lda
   double *out = obuf.as<double>();
   const int32_t st = gemm_device<double>(s, R, P, P, 1.0, sa.dev, sa.ld, sc.dev, sc.ld, false, 0.0,
                                          out, ldo, false, 0);
-  if (st == PGB200_OK) {
-    PGB_CUDA(cudaMemcpy2DAsync(A, lda * sizeof(double), out, ldo * sizeof(double),
-                               P * sizeof(double), R, cudaMemcpyDefault, s));
-    if (sum)
-      PGB_CUDA(cudaMemcpyAsync(sum, out + (R - 1) * ldo, P * sizeof(double), cudaMemcpyDefault, s));
-  }
-  const bool staged = sa.host || sc.host || is_host_pointer(sum);
+  const bool staged = sa.host || sc.host || ss.host;
   if (st != PGB200_OK) return st;  // staged copies are released, nothing is copied back
+  if (staged) PGB_TRY(sync_check(rt, s));  // a kernel that gave up: nothing is copied back either
+  if (sa.host) {
+    PGB_CUDA(cudaMemcpy2DAsync(A, lda * sizeof(double), out, ldo * sizeof(double),
+                               P * sizeof(double), R, cudaMemcpyDeviceToHost, s));
+    count_d2h((size_t)R * P * sizeof(double));
+  } else {
+    PGB_CUDA(cudaMemcpy2DAsync(sa.dev, sa.ld * sizeof(double), out, ldo * sizeof(double),
+                               P * sizeof(double), R, cudaMemcpyDeviceToDevice, s));
+  }
+  if (sum)
+    PGB_CUDA(cudaMemcpyAsync(ss.dev, out + (R - 1) * ldo, P * sizeof(double),
+                             cudaMemcpyDeviceToDevice, s));
   PGB_TRY(finish(s, &sa));
   PGB_TRY(finish(s, &sc));
+  PGB_TRY(finish(s, &ss));
   if (staged) PGB_CUDA(cudaStreamSynchronize(s));
   return st;
 }
@@ -230,48 +243,58 @@ extern "C" {
 
 int32_t pgb200Dsymm(void *stream, int64_t M, int64_t N, double alpha, const double *A, int64_t lda,
                     const double *B, int64_t ldb, double beta, double *C, int64_t ldc) {
+  PGB_ENTRY(stream);
   return symm_entry<double>(stream, M, N, alpha, A, lda, B, ldb, beta, C, ldc);
 }
 
 int32_t pgb200Ssymm(void *stream, int64_t M, int64_t N, float alpha, const float *A, int64_t lda,
                     const float *B, int64_t ldb, float beta, float *C, int64_t ldc) {
+  PGB_ENTRY(stream);
   return symm_entry<float>(stream, M, N, alpha, A, lda, B, ldb, beta, C, ldc);
 }
 
 int32_t pgb200Dtrmm(void *stream, int64_t M, int64_t N, double alpha, const double *A, int64_t lda,
                     double *B, int64_t ldb) {
+  PGB_ENTRY(stream);
   return trmm_entry<double>(stream, M, N, alpha, A, lda, B, ldb);
 }
 
 int32_t pgb200Strmm(void *stream, int64_t M, int64_t N, float alpha, const float *A, int64_t lda,
                     float *B, int64_t ldb) {
+  PGB_ENTRY(stream);
   return trmm_entry<float>(stream, M, N, alpha, A, lda, B, ldb);
 }
 
 int32_t pgb200Ddoitgen(void *stream, int64_t R, int64_t P, double *A, int64_t lda,
                        const double *C4, int64_t ldc4, double *sum) {
+  PGB_ENTRY(stream);
   return doitgen_entry(stream, R, P, A, lda, C4, ldc4, sum);
 }
 
 int32_t pgb200_kernel_symm(int m, int n, double alpha, double beta, double *C, const double *A,
                            const double *B) {
+  PGB_ENTRY(nullptr);
   return pgb200Dsymm(nullptr, m, n, alpha, A, m, B, n, beta, C, n);
 }
 
 int32_t pgb200_kernel_symm_f32(int m, int n, float alpha, float beta, float *C, const float *A,
                                const float *B) {
+  PGB_ENTRY(nullptr);
   return pgb200Ssymm(nullptr, m, n, alpha, A, m, B, n, beta, C, n);
 }
 
 int32_t pgb200_kernel_trmm(int m, int n, double alpha, const double *A, double *B) {
+  PGB_ENTRY(nullptr);
   return pgb200Dtrmm(nullptr, m, n, alpha, A, m, B, n);
 }
 
 int32_t pgb200_kernel_trmm_f32(int m, int n, float alpha, const float *A, float *B) {
+  PGB_ENTRY(nullptr);
   return pgb200Strmm(nullptr, m, n, alpha, A, m, B, n);
 }
 
 int32_t pgb200_kernel_doitgen(int nr, int nq, int np, double *A, const double *C4, double *sum) {
+  PGB_ENTRY(nullptr);
   PGB_REQUIRE(nr >= 0 && nq >= 0 && np >= 0, "kernel_doitgen: negative size");
   return pgb200Ddoitgen(nullptr, (int64_t)nr * nq, np, A, np, C4, np, sum);
 }

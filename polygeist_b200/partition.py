@@ -187,6 +187,7 @@ class PartitionedSyrk:
         self.group = group
         self.align = align
         self._packed = None
+        self._packed_key = None
 
     def blocks(self, N):
         return syrk_row_blocks(N, self.dist.get_world_size(self.group), self.align)
@@ -202,8 +203,11 @@ class PartitionedSyrk:
             self.compute(alpha, A_local, beta, C_block, (r0, r1))
             return C_block
         chunks = k_chunks(K, self.kchunk)
-        if self._packed is None or len(self._packed) != len(chunks):
+        key = (N, tuple(chunks), A_local.dtype, A_local.device)
+        if self._packed is None or self._packed_key != key:
+            # The packed K-slices are kept between calls of the same shape only.
             self._packed = [A_local.new_empty((N, k1 - k0)) for k0, k1 in chunks]
+            self._packed_key = key
         works = []
         for (k0, k1), buf in zip(chunks, self._packed):
             if rank == self.src:

@@ -37,12 +37,43 @@ def test_reference_arm_prints_one_contract_line(workload):
     assert d["unit"] == ("GB/s" if workload.startswith("mvt") else "GFLOP/s")
 
 
-def test_workload_tables():
-    """Algorithmic units and operand sizes the roofline arithmetic rests on."""
+def _bench_module():
     import importlib.util
     spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
     bench = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(bench)
+    return bench
+
+
+def test_default_workload_is_the_largest_single_gpu_config_and_steps_are_honoured():
+    """No --workload: configs[4]b (fp32 GEMM 32768^3), strong scaling; the
+    reference arm runs exactly the steps it is asked for and prints the same
+    `config` object as the GPU arm for the same --gpus."""
+    bench = _bench_module()
+    assert bench.DEFAULT_WORKLOAD == "sgemm32768"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference",
+                        "--gpus", "2", "--steps", "7", "--warmup", "1"],
+                       capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    d = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][0])
+    assert d["steps"] == 7 and d["warmup"] == 1 and d["n_gpus"] == 2 and d["scaling"] == "strong"
+    assert d["config"] == bench.config_of("sgemm32768", bench.WORKLOADS["sgemm32768"], 2)
+    assert "configs[4]b" in d["config"]["workload"] and d["dtype"] == "f32"
+
+
+def test_trimmed_mean_protocol():
+    """5 runs, fastest and slowest dropped, mean of the middle three and their
+    largest deviation from it (the reference's time_benchmark.sh)."""
+    bench = _bench_module()
+    mean, dev = bench.trimmed([5.0, 1.0, 2.0, 3.0, 100.0])
+    assert mean == pytest.approx(10.0 / 3.0) and dev == pytest.approx((5.0 - 10.0 / 3.0) / (10.0 / 3.0) * 100)
+    labels = [c for c, _ in bench.PER_CONFIG]
+    assert labels == ["configs[0]", "configs[1]", "configs[2]", "configs[3]", "configs[4]a", "configs[4]b"]
+
+
+def test_workload_tables():
+    """Algorithmic units and operand sizes the roofline arithmetic rests on."""
+    bench = _bench_module()
     w = bench.WORKLOADS
     assert bench.algorithmic_work("dgemm4096", w["dgemm4096"]) == 2 * 4096 ** 3
     assert bench.algorithmic_work("sgemm32768", w["sgemm32768"]) == 2 * 32768 ** 3

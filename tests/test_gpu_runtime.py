@@ -1,0 +1,358 @@
+"""GPU tests of the runtime around the kernels, all through the C ABI: host
+threads sharing a stream, expired device-side waits on the host-array paths,
+device residency across calls (pgb200Pin), stream ordering and injected NCCL
+failures of the single-process multi-GPU entries, logging and per-call timing.
+No test faults, traps or hangs a GPU: failures are made on the host.
+"""
+import os
+import subprocess
+import sys
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+import polygeist_b200 as pgb
+from helpers import SEED, elementwise_rel, normwise
+from oracle import pbo
+from polygeist_b200 import polybench
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run_py(code, env=None, timeout=600):
+    e = dict(os.environ)
+    e.update(env or {})
+    return subprocess.run([sys.executable, "-c", code, ROOT], capture_output=True, text=True,
+                          timeout=timeout, env=e)
+
+
+# --------------------------------------------------------------------------- host threads, one stream
+@pytest.mark.parametrize("nthreads", [2, 8])
+def test_host_threads_calling_the_drop_ins_at_once(nthreads):
+    """Generated code may call from OpenMP worker threads
+    (tools/cgeist/driver.cc:967-977), and the host-array drop-ins all run on the
+    default stream.  Every call owns its scratch (3xTF32 lo planes and split-K
+    partial products, mat-vec partial sums), so threads that call at the same
+    time with different data must each get the loop nest's result, every time."""
+    ni = nj = 256
+    nk = 2048                      # 2 tiles of 128x256: the split-K path with its partial products
+    n_mvt, n_syrk, m_syrk = 700, 200, 1500
+    errs = []
+
+    def worker(tid):
+        try:
+            torch.cuda.set_device(0)
+            A = pbo.fill(ni, nk, np.float32, SEED, 100 + tid, 0.0, 1.0)
+            B = pbo.fill(nk, nj, np.float32, SEED, 200 + tid, 0.0, 1.0)
+            C0 = pbo.fill(ni, nj, np.float32, SEED, 300 + tid, 0.0, 1.0)
+            truth = pbo.gemm_acc64(1.5, 1.2, C0, A, B)
+            Am = pbo.fill(n_mvt, n_mvt, np.float64, SEED, 400 + tid, 0.0, 1.0)
+            v = [pbo.fill_vec(n_mvt, np.float64, SEED, 500 + 4 * tid + k, 0.0, 1.0) for k in range(4)]
+            r = [x.copy() for x in v]
+            pbo.mvt(r[0], r[1], r[2], r[3], Am)
+            As = pbo.fill(n_syrk, m_syrk, np.float64, SEED, 600 + tid, -1.0, 1.0)
+            Cs0 = pbo.fill(n_syrk, n_syrk, np.float64, SEED, 700 + tid, -1.0, 1.0)
+            rs = pbo.syrk(1.5, 1.2, Cs0.copy(), As)
+            first = None
+            for it in range(50):
+                Cg = C0.copy()
+                polybench.kernel_gemm(ni, nj, nk, 1.5, 1.2, Cg, A, B)
+                assert elementwise_rel(Cg, truth) <= 1e-5, f"gemm_f32 thread {tid} iteration {it}"
+                if first is None:
+                    first = Cg.copy()
+                assert np.array_equal(Cg, first), f"gemm_f32 not repeatable, thread {tid} it {it}"
+                x1, x2 = v[0].copy(), v[1].copy()
+                polybench.kernel_mvt(n_mvt, x1, x2, v[2], v[3], Am)
+                assert elementwise_rel(x1, r[0]) <= 1e-12 and elementwise_rel(x2, r[1]) <= 1e-12, \
+                    f"mvt thread {tid} iteration {it}"
+                Cs = Cs0.copy()
+                polybench.kernel_syrk(n_syrk, m_syrk, 1.5, 1.2, Cs, As)
+                assert normwise(Cs, rs) <= 1e-12, f"syrk thread {tid} iteration {it}"
+        except Exception as e:  # surfaced in the main thread
+            errs.append((tid, repr(e)))
+
+    ts = [threading.Thread(target=worker, args=(t,)) for t in range(nthreads)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    assert not errs, errs[:3]
+    pgb.poll_device_status()
+
+
+# --------------------------------------------------------------------------- expired waits on the host-array paths
+def test_host_array_call_returns_timeout_and_leaves_the_output_alone():
+    """An expired device-side wait must come back from the host-array call
+    itself (the C caller never polls), and the caller's array must not receive a
+    half-written result.  The expiry is the library's own short-limit self-test
+    kernel (a wait on a barrier nothing signals, ~1 ms): no fault is injected."""
+    lib = pgb.load()
+    A = pbo.fill(64, 48, np.float64, SEED, 1, -1.0, 1.0)
+    B = pbo.fill(48, 32, np.float64, SEED, 2, -1.0, 1.0)
+    C0 = pbo.fill(64, 32, np.float64, SEED, 3, -1.0, 1.0)
+    Cm = C0.copy()
+    assert lib.pgb200SelfTestWaitTimeout(None, 2_000_000) == pgb.OK
+    st = lib.pgb200_kernel_gemm(64, 32, 48, 1.5, 1.2, Cm.ctypes.data, A.ctypes.data, B.ctypes.data)
+    assert st == pgb.ERR_TIMEOUT
+    assert b"bounded wait expired" in lib.pgb200GetLastErrorString()
+    assert np.array_equal(Cm, C0), "a failed call must not copy anything back"
+    # the word was cleared by that report, and the context still computes
+    st = lib.pgb200_kernel_gemm(64, 32, 48, 1.5, 1.2, Cm.ctypes.data, A.ctypes.data, B.ctypes.data)
+    assert st == pgb.OK
+    assert normwise(Cm, pbo.gemm(1.5, 1.2, C0.copy(), A, B)) <= 1e-12
+    # same for the fused mat-vec drop-in
+    n = 300
+    Am = pbo.fill(n, n, np.float64, SEED, 4, 0.0, 1.0)
+    v = [pbo.fill_vec(n, np.float64, SEED, 5 + k, 0.0, 1.0) for k in range(4)]
+    x1, x2 = v[0].copy(), v[1].copy()
+    assert lib.pgb200SelfTestWaitTimeout(None, 2_000_000) == pgb.OK
+    st = lib.pgb200_kernel_mvt(n, x1.ctypes.data, x2.ctypes.data, v[2].ctypes.data, v[3].ctypes.data,
+                               Am.ctypes.data)
+    assert st == pgb.ERR_TIMEOUT and np.array_equal(x1, v[0]) and np.array_equal(x2, v[1])
+    assert lib.pgb200PollDeviceStatus() == pgb.OK
+
+
+# --------------------------------------------------------------------------- device residency (pgb200Pin)
+def test_pinned_ranges_chain_calls_without_pcie_round_trips():
+    """gemm -> gemm chained through a registered intermediate, and the mat-vec
+    pair repeated 10 times on registered arrays: the loop nests' results, with
+    every operand crossing PCIe once (the library's own byte counters)."""
+    ni, nj, nk, nl = 300, 260, 200, 340
+    A = pbo.fill(ni, nk, np.float64, SEED, 1, -1.0, 1.0)
+    B = pbo.fill(nk, nj, np.float64, SEED, 2, -1.0, 1.0)
+    Cc = pbo.fill(nj, nl, np.float64, SEED, 3, -1.0, 1.0)
+    D = pbo.fill(ni, nl, np.float64, SEED, 4, -1.0, 1.0)
+    tmp = np.full((ni, nj), np.nan)
+    rtmp = np.zeros((ni, nj))
+    rD = pbo.mm2(1.5, 1.2, rtmp, A, B, Cc, D.copy())
+    arrays = (A, B, Cc, D, tmp)
+    h0, d0 = pgb.transfer_counters()
+    for a in arrays:
+        pgb.pin(a)
+    h1, d1 = pgb.transfer_counters()
+    assert h1 - h0 == sum(a.nbytes for a in arrays) and d1 == d0
+    polybench.kernel_gemm(ni, nj, nk, 1.5, 0.0, tmp, A, B)      # tmp = alpha*A*B
+    polybench.kernel_gemm(ni, nl, nj, 1.0, 1.2, D, tmp, Cc)     # D = tmp*C + beta*D
+    h2, d2 = pgb.transfer_counters()
+    assert (h2, d2) == (h1, d1), "calls on registered arrays must not touch PCIe"
+    assert np.isnan(tmp).all(), "the host array is stale until PinSync/Unpin"
+    pgb.pin_sync(D)
+    assert normwise(D, rD) <= 1e-12
+    for a in arrays:
+        pgb.unpin(a)
+    h3, d3 = pgb.transfer_counters()
+    assert h3 == h1 and d3 - d1 == D.nbytes + tmp.nbytes   # read-only arrays are not downloaded
+    assert normwise(tmp, rtmp) <= 1e-12
+    # a view inside a registered range resolves to the device copy as well
+    pgb.pin(A)
+    sub = A[100:200]
+    out = np.zeros((100, nj))
+    polybench.kernel_gemm(100, nj, nk, 1.5, 0.0, out, sub, B)   # B and out are staged as usual
+    pgb.unpin(A)
+    assert normwise(out, rtmp[100:200]) <= 1e-12
+
+    n = 900
+    Am = pbo.fill(n, n, np.float64, SEED, 5, 0.0, 1.0)
+    v = [pbo.fill_vec(n, np.float64, SEED, 6 + k, 0.0, 1.0) for k in range(4)]
+    r = [x.copy() for x in v]
+    for _ in range(10):
+        pbo.mvt(r[0], r[1], r[2], r[3], Am)
+    h0, d0 = pgb.transfer_counters()
+    for a in (Am, *v):
+        pgb.pin(a)
+    for _ in range(10):
+        polybench.kernel_mvt(n, v[0], v[1], v[2], v[3], Am)
+    for a in (Am, *v):
+        pgb.unpin(a)
+    h1, d1 = pgb.transfer_counters()
+    assert h1 - h0 == Am.nbytes + 4 * n * 8 and d1 - d0 == 2 * n * 8
+    assert elementwise_rel(v[0], r[0]) <= 1e-12 and elementwise_rel(v[1], r[1]) <= 1e-12
+    pgb.poll_device_status()
+
+
+def test_pin_rejects_overlap_and_unknown_pointers():
+    lib = pgb.load()
+    a = np.zeros(1024)
+    assert lib.pgb200Pin(a.ctypes.data, a.nbytes) == pgb.OK
+    assert lib.pgb200Pin(a.ctypes.data + 512, 1024) == pgb.ERR_INVALID
+    assert b"overlaps" in lib.pgb200GetLastErrorString()
+    assert lib.pgb200Unpin(a.ctypes.data + 8) == pgb.ERR_INVALID
+    assert lib.pgb200Unpin(a.ctypes.data) == pgb.OK
+    assert lib.pgb200Unpin(a.ctypes.data) == pgb.ERR_INVALID
+    assert lib.pgb200Pin(None, 8) == pgb.ERR_INVALID
+    d = torch.zeros(8, dtype=torch.float64, device=DEV)
+    assert lib.pgb200Pin(d.data_ptr(), 64) == pgb.ERR_INVALID
+
+
+# --------------------------------------------------------------------------- multi-GPU entries
+@pytest.mark.parametrize("ndev", [1, 2])
+def test_multi_gpu_entries_wait_for_the_callers_device_work(ndev):
+    """Arrays of device 0 that are still being produced on the caller's stream
+    when the entry is called: the entry's private streams must be ordered after
+    that work.  A chain of fills and updates is queued right before the call."""
+    if torch.cuda.device_count() < ndev:
+        pytest.skip(f"needs {ndev} GPUs")
+    torch.cuda.set_device(0)
+    M, N, K = 2048, 1024, 4096
+    A = torch.empty((M, K), dtype=torch.float32, device=DEV)
+    B = torch.empty((K, N), dtype=torch.float32, device=DEV)
+    Cm = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    big = torch.empty((8192, 8192), dtype=torch.float32, device=DEV)
+    for rep in range(3):
+        A.fill_(float("nan"))
+        B.fill_(float("nan"))
+        Cm.fill_(float("nan"))
+        torch.cuda.synchronize()
+        for _ in range(20):           # keep the stream busy ahead of the fills
+            big.mul_(1.0001)
+        pgb.fill_uniform(A, SEED, 1 + rep, 0.0, 1.0)
+        pgb.fill_uniform(B, SEED, 11 + rep, 0.0, 1.0)
+        pgb.fill_uniform(Cm, SEED, 21 + rep, 0.0, 1.0)
+        pgb.gemm_mg(ndev, 1.5, A, B, 1.2, Cm)     # no synchronisation in between
+        torch.cuda.set_device(0)
+        C0 = torch.empty_like(Cm)
+        pgb.fill_uniform(C0, SEED, 21 + rep, 0.0, 1.0)
+        truth = 1.5 * (A.double() @ B.double()) + 1.2 * C0.double()
+        assert not bool(torch.isnan(Cm).any())
+        assert float(((Cm.double() - truth).abs() / truth.abs()).max()) <= 1e-5
+    n, k = 1536, 2304
+    As = torch.empty((n, k), dtype=torch.float32, device=DEV)
+    Cs = torch.empty((n, n), dtype=torch.float32, device=DEV)
+    As.fill_(float("nan"))
+    Cs.fill_(float("nan"))
+    torch.cuda.synchronize()
+    for _ in range(20):
+        big.mul_(1.0001)
+    pgb.fill_uniform(As, SEED, 31, 0.0, 1.0)
+    pgb.fill_uniform(Cs, SEED, 32, 0.0, 1.0)
+    pgb.syrk_mg(ndev, 1.5, As, 1.2, Cs)
+    torch.cuda.set_device(0)
+    C0 = torch.empty_like(Cs)
+    pgb.fill_uniform(C0, SEED, 32, 0.0, 1.0)
+    truth = 1.5 * (As.double() @ As.double().T) + 1.2 * C0.double()
+    low = torch.tril(torch.ones((n, n), dtype=torch.bool, device=DEV))
+    assert float((((Cs.double() - truth).abs() / truth.abs())[low]).max()) <= 1e-5
+    assert torch.equal(Cs[~low], C0[~low])
+    pgb.poll_device_status()
+
+
+_NCCL_FAULT = r"""
+import sys
+import numpy as np
+import torch
+sys.path.insert(0, sys.argv[1])
+import polygeist_b200 as pgb
+lib = pgb.load()
+M, N, K = 512, 256, 4096
+rng = np.random.default_rng(7)
+A, B = rng.random((M, K)), rng.random((K, N))
+C0 = rng.random((M, N))
+Cm = C0.copy()
+st = lib.pgb200DgemmMg(2, M, N, K, 1.5, A.ctypes.data, K, B.ctypes.data, N, 1.2, Cm.ctypes.data, N)
+assert st == pgb.ERR_NCCL, st
+msg = lib.pgb200GetLastErrorString().decode()
+assert np.array_equal(Cm, C0), "the caller's C must be untouched after a failed call"
+# buffers were released and the devices still work: one GPU, no NCCL involved
+torch.cuda.synchronize()
+st = lib.pgb200DgemmMg(1, M, N, K, 1.5, A.ctypes.data, K, B.ctypes.data, N, 1.2, Cm.ctypes.data, N)
+assert st == 0, lib.pgb200GetLastErrorString()
+ref = 1.5 * (A @ B) + 1.2 * C0
+assert np.max(np.abs(Cm - ref)) / np.max(np.abs(ref)) <= 1e-12
+print("nccl-fault-ok:", msg)
+"""
+
+
+@pytest.mark.parametrize("fault", ["broadcast", "async"])
+def test_injected_nccl_failure_is_reported_and_cleaned_up(fault):
+    """The NCCL entry points sit in a function table; PGB200_FAULT_NCCL swaps one
+    for a host stub that reports ncclSystemError (the broadcast call itself, or
+    the asynchronous-error poll made while the link streams drain).  The call
+    must return PGB200_ERR_NCCL, leave C alone, release its buffers, abort the
+    communicators where needed, and the next call must work.  Nothing on any
+    GPU fails."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    out = _run_py(_NCCL_FAULT, env={"PGB200_FAULT_NCCL": fault, "NCCL_NVLS_ENABLE": "0"})
+    assert out.returncode == 0 and "nccl-fault-ok" in out.stdout, out.stdout + out.stderr
+    assert ("ncclBroadcast" in out.stdout) if fault == "broadcast" else ("ncclCommGetAsyncError" in out.stdout)
+
+
+# --------------------------------------------------------------------------- logging and per-call timing
+_LOGGED = r"""
+import sys
+import numpy as np
+sys.path.insert(0, sys.argv[1])
+import polygeist_b200 as pgb
+from polygeist_b200 import polybench
+A, B, Cm = np.ones((64, 32)), np.ones((32, 48)), np.zeros((64, 48))
+polybench.kernel_gemm(64, 48, 32, 1.0, 0.0, Cm, A, B)
+assert np.all(Cm == 32.0)
+lib = pgb.load()
+assert lib.pgb200Dgemm(None, 4, 4, 4, 1.0, A.ctypes.data, 2, B.ctypes.data, 4, 0.0, Cm.ctypes.data, 4) == 1
+pgb.profile_dump(sys.argv[2] if len(sys.argv) > 2 else None)
+"""
+
+
+def test_log_levels_and_error_format(tmp_path):
+    quiet = _run_py(_LOGGED, env={"PGB200_LOG": "0"})
+    assert quiet.returncode == 0, quiet.stderr
+    # level 0: the error line only
+    lines = [l for l in quiet.stderr.splitlines() if l.startswith("pgb200:")]
+    assert len(lines) == 1 and "lda" in lines[0]
+    loud = _run_py(_LOGGED, env={"PGB200_LOG": "2"})
+    assert loud.returncode == 0, loud.stderr
+    assert "runtime initialised" in loud.stderr                      # level 1
+    assert "pgb200_kernel_gemm -> DMMA kernels" in loud.stderr       # level 2, outermost entry only
+    assert "pgb200Dgemm -> " in loud.stderr
+
+
+def test_per_call_profile_ring(tmp_path):
+    """PGB200_PROFILE=1: every outermost entry is bracketed by CUDA events from a
+    ring; the dump has one line per entry point with calls and milliseconds."""
+    lib = pgb.load()
+    pgb.profile_enable(True)
+    try:
+        A = torch.rand((512, 512), dtype=torch.float64, device=DEV)
+        Cm = torch.zeros((512, 512), dtype=torch.float64, device=DEV)
+        x = torch.rand(512, dtype=torch.float64, device=DEV)
+        y = torch.zeros(512, dtype=torch.float64, device=DEV)
+        for _ in range(600):                      # more calls than the ring has slots
+            pgb.gemm(1.0, A, A, 0.0, Cm)
+        for _ in range(7):
+            pgb.gemv(0, 1.0, A, x, 0.0, y)
+        path = tmp_path / "profile.txt"
+        pgb.profile_dump(str(path))
+    finally:
+        pgb.profile_enable(False)
+    rows = {l.split()[0]: l.split() for l in path.read_text().splitlines()}
+    assert int(rows["pgb200Dgemm"][2]) == 600 and float(rows["pgb200Dgemm"][4]) > 0.0
+    assert int(rows["pgb200Dgemv"][2]) == 7
+    mean_ms = float(rows["pgb200Dgemm"][6])
+    assert 0.001 < mean_ms < 5.0
+
+
+# --------------------------------------------------------------------------- trmm and non-finite data
+def test_trmm_non_finite_entry_stays_within_its_diagonal_block():
+    """The C nest adds A[k][i]*B[k][j] for k > i only, so a NaN in row k of B
+    reaches rows i <= k of column j.  The tensor-core product also multiplies
+    the zeros of the triangular factor inside the 128-row diagonal block that
+    holds k, so there (rows k+1 .. end of that block) the NaN spreads where the
+    nest would not put it - the documented deviation.  Everything outside that
+    block and every other column must follow the nest exactly."""
+    m, n, k0, j0 = 384, 96, 200, 17
+    A = pbo.fill(m, m, np.float64, SEED, 1, -1.0, 1.0)
+    B0 = pbo.fill(m, n, np.float64, SEED, 2, -1.0, 1.0)
+    B0[k0, j0] = np.nan
+    ref = pbo.trmm(1.5, A, B0.copy())
+    got = B0.copy()
+    polybench.kernel_trmm(m, n, 1.5, A, got)
+    other = np.ones(n, dtype=bool)
+    other[j0] = False
+    assert normwise(got[:, other], ref[:, other]) <= 1e-12
+    assert np.isnan(ref[:k0 + 1, j0]).all() and np.isnan(got[:k0 + 1, j0]).all()
+    assert not np.isnan(ref[k0 + 1:, j0]).any()
+    assert normwise(got[256:, j0], ref[256:, j0]) <= 1e-12      # blocks below the one holding k0

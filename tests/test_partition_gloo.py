@@ -117,6 +117,18 @@ def _worker(rank, world, port, q):
         C_blk = torch.from_numpy(Cs[s0:s1].copy())
         sp.run(1.5, A_loc, 1.2, C_blk)
         ok = ok and np.allclose(C_blk.numpy(), refs[s0:s1], rtol=1e-13, atol=1e-13)
+        # The same plan object with another N but the same number of K-slices:
+        # its packed-slice buffers must be rebuilt, not reused.
+        N2 = 56
+        A2 = rng.uniform(0, 1, (N2, Ks))
+        C2 = rng.uniform(0, 1, (N2, N2))
+        ref2 = np.where(np.tril(np.ones((N2, N2), bool)), 1.5 * A2 @ A2.T + 1.2 * C2, C2)
+        b2 = sp.blocks(N2)
+        t0, t1 = b2[rank], b2[rank + 1]
+        A2_loc = torch.from_numpy(A2.copy()) if rank == 0 else torch.full((N2, Ks), float("nan"), dtype=torch.float64)
+        C2_blk = torch.from_numpy(C2[t0:t1].copy())
+        sp.run(1.5, A2_loc, 1.2, C2_blk)
+        ok = ok and np.allclose(C2_blk.numpy(), ref2[t0:t1], rtol=1e-13, atol=1e-13)
         q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
