@@ -1215,6 +1215,327 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
   }
 }
 
+// ===========================================================================
+// Fused kernel for products with few tiles (configs such as 1024^3): ONE launch,
+// no scratch memory.
+//
+//  * The lo parts are made inside the kernel.  TMA brings the raw fp32 tiles of
+//    A and B into the ring; two "split" warps read each raw tile from shared
+//    memory and write lo = tf32(x - trunc_tf32(x)) at the same offset of a
+//    second buffer, so the (swizzled) layout of the lo tile equals that of the
+//    raw tile by construction and no layout arithmetic is involved.  The tensor
+//    core reads the raw tile as the hi part (it drops the low mantissa bits
+//    itself).  The MMA thread waits on a "ready" barrier the split warps signal
+//    after a generic->async proxy fence.
+//  * Split-K inside a thread-block cluster.  The S CTAs of a cluster (S = 1, 2
+//    or 4) share one 128x256 tile and take consecutive K ranges.  Each writes
+//    its partial tile into its own shared memory (the ring is free by then),
+//    the cluster synchronises, and CTA r adds up column slice r of all S partial
+//    tiles over distributed shared memory, in rank order - so the sum does not
+//    depend on timing - applies alpha/beta and stores its slice of C.  No
+//    partial product ever leaves the SMs, nothing has to be zeroed, and
+//    beta == 0 still never reads C.
+//
+// One (tile, K range) per CTA; grid = tiles * S, cluster = (S, 1, 1).
+// ===========================================================================
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ float lo_part(float x) {
+  const float hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+  uint32_t l;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(x - hi));
+  return __uint_as_float(l);
+}
+
+template <bool B_MN, int S>
+__global__ void __launch_bounds__(THREADS, 1)
+tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
+                         const __grid_constant__ CUtensorMap mapB, int64_t M, int64_t N, int64_t K,
+                         float alpha, float beta, float *__restrict__ C, int64_t ldc, Tiles tiles,
+                         int chunk_kblocks, int b_blocked, int32_t *status) {
+  static_assert(S == 1 || S == 2 || S == 4, "cluster size");
+  constexpr int W = 128 / S;  // columns of the final tile each drain thread reduces and stores
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[3 * STAGES + 4];
+  __shared__ uint32_t tmem_slot;
+  __shared__ float epi_stage[EPI_WARPS][32][33];
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+  const uint32_t ready0 = smem_u32(&bars[2 * STAGES]);
+  const uint32_t accf0 = smem_u32(&bars[3 * STAGES]), acce0 = smem_u32(&bars[3 * STAGES + 2]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = S > 1 ? cluster_ctarank() : 0u;
+
+  if (threadIdx.x == 64) {
+    prefetch_tensor_map(&mapA);
+    prefetch_tensor_map(&mapB);
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+      mbar_init(ready0 + 8 * s, 2);  // one arrival per split warp
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(accf0 + 8 * b, 1);
+      mbar_init(acce0 + 8 * b, EPI_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  // This CTA's work item: tile (cluster index), K-block range (rank).
+  const int64_t t = (int64_t)blockIdx.x / S;
+  const int64_t nkb = (K + BK - 1) / BK;
+  const int64_t kb_lo = (int64_t)rank * tiles.kper < nkb ? (int64_t)rank * tiles.kper : nkb;
+  const int64_t kb_hi = kb_lo + tiles.kper < nkb ? kb_lo + tiles.kper : nkb;
+  const int64_t nch = (kb_hi - kb_lo + chunk_kblocks - 1) / chunk_kblocks;
+  int64_t tm, tn;
+  {
+    TileCursor cur;
+    cur.seek(tiles, t, &tm, &tn);
+  }
+
+  if (warp < FIRST_EPI_WARP) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0) {
+      // ------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        uint32_t stage = 0, phase = 0;
+        for (int64_t kb = kb_lo; kb < kb_hi; kb++) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) {
+            report_status(status, 41, (int32_t)blockIdx.x);
+            break;
+          }
+          const uint32_t dst = ring + stage * STAGE_BYTES;
+          const uint32_t bar = full0 + 8 * stage;
+          mbar_expect_tx(bar, A_BYTES + B_BYTES);
+          const int k0 = (int)(kb * BK);
+          tma_load_2d(dst, &mapA, bar, k0, (int)(tm * BM));
+          if (B_MN) {
+            // Row-major B as it lies: eight [BK x 32] column blocks, by one 3-D
+            // copy when N is a multiple of 32, else by eight 2-D copies
+            // (zero-filled past column N).
+            if (b_blocked) {
+              tma_load_3d(dst + 2 * A_BYTES, &mapB, bar, 0, k0, (int)(tn * (BN / 32)));
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 32; j++)
+                tma_load_2d(dst + 2 * A_BYTES + j * (BK * 128), &mapB, bar, (int)(tn * BN) + 32 * j,
+                            k0);
+            }
+          } else {
+            tma_load_2d(dst + 2 * A_BYTES, &mapB, bar, k0, (int)(tn * BN));
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // -------------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (int64_t ch = 0; ch < nch && ok; ch++) {
+          const uint32_t buf = (uint32_t)(ch & 1);
+          const uint32_t use = (uint32_t)((ch >> 1) & 1);
+          if (!mbar_wait(acce0 + 8 * buf, use ^ 1)) {
+            report_status(status, 42, (int32_t)blockIdx.x);
+            break;
+          }
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + buf * BN;
+          const int64_t kb_first = kb_lo + ch * chunk_kblocks;
+          const int64_t kb_end = kb_first + chunk_kblocks < kb_hi ? kb_first + chunk_kblocks : kb_hi;
+          for (int64_t kb = kb_first; kb < kb_end; kb++) {
+            if (!mbar_wait(ready0 + 8 * stage, phase)) {
+              report_status(status, 43, (int32_t)blockIdx.x);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t sa = ring + stage * STAGE_BYTES;
+            const uint64_t ahi = smem_desc_sw64(sa), alo = smem_desc_sw64(sa + A_BYTES);
+            const uint64_t bhi = B_MN ? smem_desc_mn_sw128(sa + 2 * A_BYTES)
+                                      : smem_desc_sw64(sa + 2 * A_BYTES);
+            const uint64_t blo = B_MN ? smem_desc_mn_sw128(sa + 2 * A_BYTES + B_BYTES)
+                                      : smem_desc_sw64(sa + 2 * A_BYTES + B_BYTES);
+            constexpr uint32_t idesc = B_MN ? IDESC_BMN : IDESC;
+            const bool first = (kb == kb_first);
+#pragma unroll
+            for (int ks = 0; ks < BK / 8; ks++) {
+              const uint64_t ko = (uint64_t)(ks * 2);
+              const uint64_t kob = B_MN ? (uint64_t)(ks * 64) : ko;
+              tc_mma_tf32(tmem_d, alo + ko, bhi + kob, idesc, (first && ks == 0) ? 0u : 1u);
+              tc_mma_tf32(tmem_d, ahi + ko, blo + kob, idesc, 1u);
+              tc_mma_tf32(tmem_d, ahi + ko, bhi + kob, idesc, 1u);
+            }
+            tc_commit(empty0 + 8 * stage);
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+          if (ok) tc_commit(accf0 + 8 * buf);
+        }
+      }
+    } else {
+      // ------------------------------------------------- split warps (2 and 3)
+      const int st = (int)threadIdx.x - 64;  // 0..63
+      uint32_t stage = 0, phase = 0;
+      for (int64_t kb = kb_lo; kb < kb_hi; kb++) {
+        if (!mbar_wait(full0 + 8 * stage, phase)) {
+          if (lane == 0) report_status(status, 45, (int32_t)blockIdx.x);
+          break;
+        }
+        float4 *a_raw = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES);
+        float4 *a_lo = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + A_BYTES);
+        float4 *b_raw = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + 2 * A_BYTES);
+        float4 *b_lo =
+            reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + 2 * A_BYTES + B_BYTES);
+#pragma unroll
+        for (int i = 0; i < A_BYTES / 16 / 64; i++) {
+          const float4 x = a_raw[st + 64 * i];
+          a_lo[st + 64 * i] = make_float4(lo_part(x.x), lo_part(x.y), lo_part(x.z), lo_part(x.w));
+        }
+#pragma unroll 8
+        for (int i = 0; i < B_BYTES / 16 / 64; i++) {
+          const float4 x = b_raw[st + 64 * i];
+          b_lo[st + 64 * i] = make_float4(lo_part(x.x), lo_part(x.y), lo_part(x.z), lo_part(x.w));
+        }
+        // Make the generic-proxy writes visible to the tensor core's reads.
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready0 + 8 * stage);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    if (S > 1) {
+      // The two cluster barriers of the drain warps' reduction, matched here.
+      __syncwarp();
+      cluster_sync_all();
+      cluster_sync_all();
+    }
+  } else {
+    // ------------------------------------------------------------- drain warps
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int quarter = warp & 3;
+    const int half = (warp - FIRST_EPI_WARP) >> 2;
+    bool ok = true;
+    float acc[128];
+#pragma unroll
+    for (int i = 0; i < 128; i++) acc[i] = 0.0f;
+    if (beta != 0.0f) {
+      // This thread's slice of C towards L2 while the tensor cores work.
+      const int64_t pr = tm * BM + quarter * 32 + lane, pc = tn * BN + half * 128 + rank * W;
+      if (pr < M) {
+#pragma unroll
+        for (int q = 0; q < W / 32; q++)
+          if (pc + q * 32 < N)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(C + pr * ldc + pc + q * 32));
+      }
+    }
+    for (int64_t ch = 0; ch < nch; ch++) {
+      const uint32_t buf = (uint32_t)(ch & 1);
+      const uint32_t use = (uint32_t)((ch >> 1) & 1);
+      if (!mbar_wait_backoff(accf0 + 8 * buf, use)) {
+        if (lane == 0) report_status(status, 44, (int32_t)blockIdx.x);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr =
+          tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + (uint32_t)(half * 128);
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        uint32_t v0[32], v1[32];
+        tc_ld32(taddr + j * 32, v0);
+        tc_ld32(taddr + j * 32 + 32, v1);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i++) acc[j * 32 + i] += __uint_as_float(v0[i]);
+#pragma unroll
+        for (int i = 0; i < 32; i++) acc[j * 32 + 32 + i] += __uint_as_float(v1[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acce0 + 8 * buf);
+    }
+
+    const int ew = warp - FIRST_EPI_WARP;
+    const int64_t r_base = tm * BM + quarter * 32;
+    const int64_t cb = tn * BN + half * 128;
+    if (S == 1) {
+      if (ok)
+        epilogue_store<128>(acc, epi_stage[ew], lane, r_base, cb, M, N, ldc, C, alpha, beta,
+                            tiles.lower != 0, tiles.row0);
+    } else {
+      // Partial tile -> own shared memory as [float4 index][drain thread]: every
+      // warp access, local or remote, is 512 contiguous bytes.  All MMAs that
+      // read the ring have retired (the last accumulator was complete before it
+      // was drained), so the ring is free.
+      const int dt = (int)threadIdx.x - 32 * FIRST_EPI_WARP;  // drain thread 0..255
+      float4 *part = reinterpret_cast<float4 *>(ring_ptr);
+#pragma unroll
+      for (int j = 0; j < 32; j++)
+        part[j * 256 + dt] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+      __syncwarp();
+      cluster_sync_all();  // every CTA's partial tile is in place (release/acquire)
+      float red[W];
+      // Column slice `rank` of this thread's row, from every CTA in rank order.
+#pragma unroll
+      for (int q = 0; q < S; q++) {
+#pragma unroll
+        for (int j = 0; j < W / 4; j++) {
+          const uint32_t local = ring + (uint32_t)(((rank * (W / 4) + j) * 256 + dt) * 16);
+          const float4 v = ld_cluster_f4(map_to_cta(local, (uint32_t)q));
+          if (q == 0) {
+            red[4 * j] = v.x; red[4 * j + 1] = v.y; red[4 * j + 2] = v.z; red[4 * j + 3] = v.w;
+          } else {
+            red[4 * j] += v.x; red[4 * j + 1] += v.y; red[4 * j + 2] += v.z; red[4 * j + 3] += v.w;
+          }
+        }
+      }
+      if (ok)
+        epilogue_store<W>(red, epi_stage[ew], lane, r_base, cb + rank * W, M, N, ldc, C, alpha,
+                          beta, tiles.lower != 0, tiles.row0);
+      __syncwarp();
+      cluster_sync_all();  // nobody's shared memory goes away while a peer reads it
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
 }  // namespace
 
 // Self-test of the bounded-wait machinery: one CTA waits on an mbarrier that
@@ -1321,6 +1642,70 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
       else
         splits = 1;
     }
+  }
+  // Few tiles and both operands usable in place: the fused kernel - lo parts
+  // made in shared memory, K split inside a cluster, one launch, no scratch.
+  if (tiles256 * 2 <= rt->num_sms && a_raw && b_raw) {
+    Tiles ft = {};
+    ft.tiles_m = (M + BM - 1) / BM;
+    ft.tiles_n = (N + 255) / 256;
+    ft.bn = 256;
+    ft.bm = BM;
+    ft.row0 = row0;
+    ft.lower = lower ? 1 : 0;
+    ft.total = count_tiles(ft);
+    int S = 1;
+    if (!rt->cfg.no_split_k && ft.total > 0) {
+      int64_t sp = rt->num_sms / ft.total;         // CTAs available per tile
+      const int64_t by_k = nkb_all / (2 * chunk);  // at least two chunks per K range
+      if (sp > by_k) sp = by_k;
+      S = sp >= 4 ? 4 : (sp >= 2 ? 2 : 1);
+    }
+    int64_t fk = ((nkb_all + S - 1) / S + chunk - 1) / chunk * chunk;
+    while (S > 1 && (int64_t)(S - 1) * fk >= nkb_all) {  // a rank would get no K-block
+      S >>= 1;
+      fk = ((nkb_all + S - 1) / S + chunk - 1) / chunk * chunk;
+    }
+    ft.splits = S;
+    ft.kper = fk;
+    CUtensorMap mA, mB;
+    const int fb_blocked = (!transB && (N % 32) == 0) ? 1 : 0;
+    PGB_TRY(make_plane_map(&mA, A, M, K, lda, BM));
+    if (transB)
+      PGB_TRY(make_plane_map(&mB, B, N, K, ldb, 256));
+    else if (fb_blocked)
+      PGB_TRY(make_nmajor_map_blocked(&mB, B, K, N, ldb, 256));
+    else
+      PGB_TRY(make_nmajor_map(&mB, B, K, N, ldb));
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)(ft.total * S), 1, 1);
+    lc.blockDim = dim3(THREADS, 1, 1);
+    lc.dynamicSmemBytes = SMEM_BYTES;
+    lc.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs = attr;
+    lc.numAttrs = S > 1 ? 1 : 0;
+    auto launchf = [&](auto kernel) -> int32_t {
+      PGB_TRY(ensure_dynamic_smem((const void *)kernel, SMEM_BYTES));
+      PGB_CUDA(cudaLaunchKernelEx(&lc, kernel, mA, mB, M, N, K, alpha, beta, C, ldc, ft, chunk,
+                                  fb_blocked, rt->status_dev));
+      return PGB200_OK;
+    };
+    if (transB) {
+      PGB_TRY(S == 4   ? launchf(tf32x3_gemm_fused_kernel<false, 4>)
+              : S == 2 ? launchf(tf32x3_gemm_fused_kernel<false, 2>)
+                       : launchf(tf32x3_gemm_fused_kernel<false, 1>));
+    } else {
+      PGB_TRY(S == 4   ? launchf(tf32x3_gemm_fused_kernel<true, 4>)
+              : S == 2 ? launchf(tf32x3_gemm_fused_kernel<true, 2>)
+                       : launchf(tf32x3_gemm_fused_kernel<true, 1>));
+    }
+    note_launch(PATH_TCGEN05);
+    return PGB200_OK;
   }
   const int64_t ldp = (N + 3) / 4 * 4;
   const size_t part_n = splits > 1 ? (size_t)splits * M * ldp : 0;

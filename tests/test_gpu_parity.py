@@ -394,14 +394,18 @@ def test_sgemm_matches_oracle(M, N, K):
                                          (1000, 1100, 1200, 1.2), (130, 250, 4100, 1.2)])
 def test_sgemm_split_k(M, N, K, beta):
     """Few tiles, long K: the K-blocks of each tile are dealt to several CTAs and
-    the partial products are added in a fixed order (split, product, reduce: 3
-    launches).  Ragged edges in all three extents; beta == 0 must not read C;
-    two runs give the same bits; the result agrees with the unsplit kernel."""
+    the partial products are added in a fixed order.  Operands that can be used
+    in place take the fused kernel (one launch: lo parts made in shared memory,
+    K split inside a cluster, partial tiles added over distributed shared
+    memory); the others take split, product and reduce (3 or 4 launches).
+    Ragged edges in all three extents; beta == 0 must not read C; two runs give
+    the same bits; the result agrees with the unsplit kernel."""
     l0 = pgb.launch_count()
     got, truth, seq = _sgemm_case(M, N, K, beta)
-    # 3 input fills + operand planes (one launch, two when B has to be transposed)
-    # + split-K product + reduce
-    assert pgb.launch_count() - l0 in (6, 7)
+    fused = (K % 4 == 0) and (N % 4 == 0)      # 16-byte aligned rows of A and B
+    # 3 input fills, then: the fused kernel | operand planes (one launch, two when
+    # B has to be transposed) + split-K product + reduce
+    assert pgb.launch_count() - l0 == (4 if fused else 7)
     assert pgb.last_path() == pgb.PATH_TCGEN05
     assert elementwise_rel(got, truth) <= 1e-5
     if K <= 2048:
@@ -442,9 +446,13 @@ def test_sgemm_plain_matmul_nests(M, N, K, beta):
 
 def test_sgemm_config0_1024():
     """configs[0]: fp32 M=N=K=1024, uniform [0,1), alpha=1.5, beta=1.2."""
+    l0 = pgb.launch_count()
     got, truth, seq = _sgemm_case(1024, 1024, 1024)
+    assert pgb.launch_count() - l0 == 4        # 3 input fills + ONE kernel for the product
     assert elementwise_rel(got, truth) <= 1e-5
     assert elementwise_rel(got, seq) <= 1e-5
+    again, _, _ = _sgemm_case(1024, 1024, 1024)
+    assert np.array_equal(got, again)
 
 
 @pytest.mark.parametrize("n,k", [(128, 64), (300, 100), (45, 33), (512, 1024), (1200, 1000)])
