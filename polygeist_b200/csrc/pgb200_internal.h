@@ -40,6 +40,8 @@ int32_t report_cuda(cudaError_t e, const char *expr);
 
 enum Path : int32_t { PATH_NONE = 0, PATH_SIMT = 1, PATH_DMMA = 2, PATH_TCGEN05 = 3, PATH_STREAM = 4 };
 
+struct StageRing;  // page-locked staging ring (pgb200_hostio.cu)
+
 struct Runtime {
   pgb200Config cfg;
   int num_sms;
@@ -51,7 +53,23 @@ struct Runtime {
   // Side streams of the host-array path: uploads and downloads of row blocks
   // run beside the products of the blocks already on the device.
   cudaStream_t copy_in, copy_out;
+  // Page-locked rings through which pageable host arrays travel, one per
+  // direction (4 x 32 MiB each, allocated on first use).
+  StageRing *ring_up, *ring_down;
 };
+
+StageRing *new_stage_ring();
+void delete_stage_ring(StageRing *r);
+// Unregistered (malloc'd) host memory, as opposed to page-locked or device memory.
+bool is_pageable_host(const void *p);
+// Contiguous copies between pageable host memory and the device through the
+// rings, the host side done by several threads.  Upload: returns when the host
+// range has been read (device copies may still be in flight on `stream`).
+// Download: ordered after the work on `stream`, returns when the host range is
+// complete.
+int32_t staged_upload(Runtime *rt, void *dev, const void *host, size_t bytes, cudaStream_t stream);
+int32_t staged_download(Runtime *rt, void *host, const void *dev, size_t bytes,
+                        cudaStream_t stream);
 
 // Lazily initialises the runtime for the current device; fails (no CPU
 // fallback) when there is no sm_100 GPU.
@@ -151,10 +169,12 @@ struct Staged {
 // Scratch memory of one call: hi/lo planes, split-K partial products, mat-vec
 // partial sums.  No two calls that can run at the same time ever share a block:
 //  * small requests (<= 32 MiB) come from a cache private to the calling host
-//    thread, one block per (device, stream): a thread's calls on one stream are
-//    ordered on that stream, so reusing its block is safe, and other threads -
-//    on the same stream or another - have blocks of their own.  No driver call
-//    at all after the first use, which matters for products of a few
+//    thread, one block per (device, stream, nesting depth): a thread's calls on
+//    one stream are ordered on that stream, so reusing its block is safe, and
+//    other threads - on the same stream or another - have blocks of their own.
+//    Holders are stack objects, so the k-th holder alive in a thread always
+//    maps to block k and two holders alive at once never share one.  No driver
+//    call at all after the first use, which matters for products of a few
 //    microseconds;
 //  * larger requests come from the stream-ordered pool and go back to it (in
 //    stream order) when the holder goes out of scope; the pool keeps freed
@@ -165,12 +185,11 @@ struct PoolBuffer {
   void *ptr = nullptr;
   cudaStream_t stream = nullptr;
   bool owned = false;  // from the pool: returned by the destructor
+  bool cached = false; // from the thread's cache: its depth slot is given back
   PoolBuffer() = default;
   PoolBuffer(const PoolBuffer &) = delete;
   PoolBuffer &operator=(const PoolBuffer &) = delete;
-  ~PoolBuffer() {
-    if (ptr && owned) cudaFreeAsync(ptr, stream);
-  }
+  ~PoolBuffer();
   cudaError_t alloc(size_t bytes, cudaStream_t s);
   template <typename T>
   T *as() const { return static_cast<T *>(ptr); }

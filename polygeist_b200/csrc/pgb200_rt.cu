@@ -6,9 +6,12 @@
 #include <string.h>
 
 #include <atomic>
+#include <condition_variable>
 #include <map>
 #include <mutex>
+#include <thread>
 #include <string>
+#include <tuple>
 #include <utility>
 
 #include <algorithm>
@@ -274,6 +277,8 @@ int32_t get_runtime(Runtime **out) {
   rt->status_dev = static_cast<int32_t *>(d);
   PGB_CUDA(cudaStreamCreateWithFlags(&rt->copy_in, cudaStreamNonBlocking));
   PGB_CUDA(cudaStreamCreateWithFlags(&rt->copy_out, cudaStreamNonBlocking));
+  rt->ring_up = new_stage_ring();
+  rt->ring_down = new_stage_ring();
   if (!g_encode) {
     void *fn = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -307,7 +312,8 @@ std::vector<CachedBlock *> g_cache_all;
 std::atomic<uint64_t> g_cache_epoch{1};
 struct ThreadCache {
   uint64_t epoch = 0;
-  std::map<std::pair<int, cudaStream_t>, CachedBlock *> blocks;
+  int live = 0;  // cached holders alive in this thread = depth of the next one
+  std::map<std::tuple<int, cudaStream_t, int>, CachedBlock *> blocks;
 };
 thread_local ThreadCache tls_cache;
 }  // namespace
@@ -328,7 +334,7 @@ cudaError_t PoolBuffer::alloc(size_t bytes, cudaStream_t s) {
     tls_cache.blocks.clear();
     tls_cache.epoch = epoch;
   }
-  CachedBlock *&slot = tls_cache.blocks[std::make_pair(dev, s)];
+  CachedBlock *&slot = tls_cache.blocks[std::make_tuple(dev, s, tls_cache.live)];
   if (!slot) {
     slot = new CachedBlock();
     slot->device = dev;
@@ -347,7 +353,14 @@ cudaError_t PoolBuffer::alloc(size_t bytes, cudaStream_t s) {
     slot->bytes = want;
   }
   ptr = slot->ptr;
+  cached = true;
+  tls_cache.live++;
   return cudaSuccess;
+}
+
+PoolBuffer::~PoolBuffer() {
+  if (ptr && owned) cudaFreeAsync(ptr, stream);
+  if (cached) tls_cache.live--;
 }
 
 static void release_cached_scratch() {
@@ -438,6 +451,9 @@ bool is_host_pointer(const void *p) {
   return a.type == cudaMemoryTypeUnregistered || a.type == cudaMemoryTypeHost;
 }
 
+// Pageable arrays of at least this size travel through the page-locked rings.
+static constexpr size_t STAGED_MIN_BYTES = size_t(64) << 20;
+
 bool needs_staging(const void *p) {
   void *d = nullptr;
   return is_host_pointer(p) && !registry_lookup(p, &d, false);
@@ -474,9 +490,15 @@ int32_t stage(cudaStream_t s, const T *p, int64_t rows, int64_t cols, int64_t ld
   st->dev = static_cast<T *>(d);
   st->host = const_cast<T *>(p);  // from here on the destructor owns the device copy
   if (in) {
+    const size_t bytes = (size_t)rows * ld * sizeof(T);
+    Runtime *rt = nullptr;
+    if (st->ld == ld && bytes >= STAGED_MIN_BYTES && is_pageable_host(p) &&
+        get_runtime(&rt) == PGB200_OK) {
+      PGB_TRY(staged_upload(rt, st->dev, p, bytes, s));
+      return PGB200_OK;  // counted by staged_upload
+    }
     if (st->ld == ld)
-      PGB_CUDA(cudaMemcpyAsync(st->dev, p, (size_t)rows * ld * sizeof(T), cudaMemcpyHostToDevice,
-                               s));
+      PGB_CUDA(cudaMemcpyAsync(st->dev, p, bytes, cudaMemcpyHostToDevice, s));
     else
       PGB_CUDA(cudaMemcpy2DAsync(st->dev, st->ld * sizeof(T), p, ld * sizeof(T), cols * sizeof(T),
                                  rows, cudaMemcpyHostToDevice, s));
@@ -489,9 +511,18 @@ template <typename T>
 int32_t finish(cudaStream_t s, Staged<T> *st) {
   if (!st->host) return PGB200_OK;
   if (st->copy_back) {
+    const size_t bytes = (size_t)st->rows * st->ld * sizeof(T);
+    Runtime *rt = nullptr;
+    if (st->ld == st->host_ld && st->ld == st->cols && bytes >= STAGED_MIN_BYTES &&
+        is_pageable_host(st->host) && get_runtime(&rt) == PGB200_OK) {
+      PGB_TRY(staged_download(rt, st->host, st->dev, bytes, s));
+      T *d = st->dev;
+      st->host = nullptr;
+      PGB_CUDA(cudaFreeAsync(d, s));
+      return PGB200_OK;  // counted by staged_download
+    }
     if (st->ld == st->host_ld && st->ld == st->cols)
-      PGB_CUDA(cudaMemcpyAsync(st->host, st->dev, (size_t)st->rows * st->ld * sizeof(T),
-                               cudaMemcpyDeviceToHost, s));
+      PGB_CUDA(cudaMemcpyAsync(st->host, st->dev, bytes, cudaMemcpyDeviceToHost, s));
     else
       PGB_CUDA(cudaMemcpy2DAsync(st->host, st->host_ld * sizeof(T), st->dev, st->ld * sizeof(T),
                                  st->cols * sizeof(T), st->rows, cudaMemcpyDeviceToHost, s));
@@ -596,6 +627,8 @@ int32_t pgb200Shutdown(void) {
     cudaFreeHost(const_cast<int32_t *>(kv.second->status_host));
     cudaStreamDestroy(kv.second->copy_in);
     cudaStreamDestroy(kv.second->copy_out);
+    delete_stage_ring(kv.second->ring_up);
+    delete_stage_ring(kv.second->ring_down);
     delete kv.second;
   }
   g_rt.clear();
@@ -647,12 +680,21 @@ int32_t pgb200Pin(const void *host, uint64_t bytes) {
   e.bytes = (size_t)bytes;
   e.device = dev;
   PGB_CUDA(cudaMalloc(&e.dev, e.bytes));
-  cudaError_t ce = cudaMemcpy(e.dev, host, e.bytes, cudaMemcpyHostToDevice);
-  if (ce != cudaSuccess) {
-    cudaFree(e.dev);
-    return report_cuda(ce, "cudaMemcpy(Pin upload)");
+  if (e.bytes >= STAGED_MIN_BYTES && is_pageable_host(host)) {
+    int32_t st = staged_upload(rt, e.dev, host, e.bytes, rt->copy_in);
+    if (st == PGB200_OK && cudaStreamSynchronize(rt->copy_in) != cudaSuccess) st = PGB200_ERR_CUDA;
+    if (st != PGB200_OK) {
+      cudaFree(e.dev);
+      return st;
+    }
+  } else {
+    cudaError_t ce = cudaMemcpy(e.dev, host, e.bytes, cudaMemcpyHostToDevice);
+    if (ce != cudaSuccess) {
+      cudaFree(e.dev);
+      return report_cuda(ce, "cudaMemcpy(Pin upload)");
+    }
+    count_h2d(e.bytes);
   }
-  count_h2d(e.bytes);
   {
     std::lock_guard<std::mutex> lk(g_pin_mu);
     g_pins[a] = e;
@@ -688,8 +730,13 @@ static int32_t pin_download(const void *host, bool release) {
     if (st == PGB200_OK) st = take_device_status(rt);
   }
   if (ce == cudaSuccess && st == PGB200_OK && e.written) {
-    ce = cudaMemcpy(const_cast<void *>(host), e.dev, e.bytes, cudaMemcpyDeviceToHost);
-    if (ce == cudaSuccess) count_d2h(e.bytes);
+    Runtime *rt = nullptr;
+    if (e.bytes >= STAGED_MIN_BYTES && is_pageable_host(host) && get_runtime(&rt) == PGB200_OK) {
+      st = staged_download(rt, const_cast<void *>(host), e.dev, e.bytes, rt->copy_out);
+    } else {
+      ce = cudaMemcpy(const_cast<void *>(host), e.dev, e.bytes, cudaMemcpyDeviceToHost);
+      if (ce == cudaSuccess) count_d2h(e.bytes);
+    }
   }
   if (release) cudaFree(e.dev);
   if (cur != e.device) cudaSetDevice(cur);
@@ -794,6 +841,142 @@ static cudaError_t copy_rows(T *dst, int64_t dst_ld, const T *src, int64_t src_l
                            rows, kind, s);
 }
 
+// The same row-block pipeline for pageable arrays (malloc'd, what the C nests
+// hold): an uploader thread stages B and then the blocks of A and C through the
+// page-locked upload ring, the calling thread launches each block's product as
+// soon as its rows are queued, and a downloader thread drains finished blocks
+// through the download ring - three actors, so the host-side memcpy of one
+// direction never holds up the other direction or the launches.  Needs dense
+// arrays (leading dimension = row length, a multiple of 16 bytes).
+template <typename T>
+static int32_t gemm_host_staged(Runtime *rt, cudaStream_t s, int64_t M, int64_t N, int64_t K,
+                                T alpha, const T *A, const T *B, T beta, T *C, bool transB) {
+  const int64_t b_rows = transB ? N : K, b_cols = transB ? K : N;
+  PoolBuffer bufA, bufB, bufC;
+  PGB_CUDA(bufA.alloc((size_t)M * K * sizeof(T), s));
+  PGB_CUDA(bufB.alloc((size_t)b_rows * b_cols * sizeof(T), s));
+  PGB_CUDA(bufC.alloc((size_t)M * N * sizeof(T), s));
+  T *dA = bufA.as<T>(), *dB = bufB.as<T>(), *dC = bufC.as<T>();
+  constexpr int MAXB = 32;
+  int nb = (int)(M / 512);
+  if (nb > MAXB) nb = MAXB;
+  if (nb < 1) nb = 1;
+  const int64_t rows_per = ((M + nb - 1) / nb + 127) / 128 * 128;
+  nb = (int)((M + rows_per - 1) / rows_per);
+  int dev = 0;
+  PGB_CUDA(cudaGetDevice(&dev));
+  std::vector<cudaEvent_t> ev((size_t)2 * nb + 1, nullptr);
+  std::mutex mu;
+  std::condition_variable cv;
+  int uploaded = 0, computed = 0;  // blocks whose copies are queued / whose product is queued
+  int32_t up_st = PGB200_OK, down_st = PGB200_OK, main_st = PGB200_OK;
+  bool stop = false;
+  auto block = [&](int i, int64_t *r0, int64_t *rows) {
+    *r0 = i * rows_per;
+    *rows = (M - *r0 < rows_per) ? (M - *r0) : rows_per;
+  };
+  auto fail = [&](int32_t *slot, int32_t st) {
+    std::lock_guard<std::mutex> lk(mu);
+    *slot = st;
+    stop = true;
+    cv.notify_all();
+  };
+  auto run = [&]() -> int32_t {
+    for (auto &e : ev) PGB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    cudaEvent_t ev_start = ev[0], *ev_in = ev.data() + 1, *ev_c = ev.data() + 1 + nb;
+    PGB_CUDA(cudaEventRecord(ev_start, s));  // buffers exist, earlier work on s is done
+    PGB_CUDA(cudaStreamWaitEvent(rt->copy_in, ev_start, 0));
+    PGB_CUDA(cudaStreamWaitEvent(rt->copy_out, ev_start, 0));
+    std::thread uploader([&] {
+      if (cudaSetDevice(dev) != cudaSuccess) return fail(&up_st, PGB200_ERR_CUDA);
+      int32_t st = staged_upload(rt, dB, B, (size_t)b_rows * b_cols * sizeof(T), rt->copy_in);
+      for (int i = 0; i < nb && st == PGB200_OK; i++) {
+        int64_t r0, rows;
+        block(i, &r0, &rows);
+        st = staged_upload(rt, dA + r0 * K, A + r0 * K, (size_t)rows * K * sizeof(T), rt->copy_in);
+        if (st == PGB200_OK && beta != (T)0)
+          st = staged_upload(rt, dC + r0 * N, C + r0 * N, (size_t)rows * N * sizeof(T), rt->copy_in);
+        if (st == PGB200_OK && cudaEventRecord(ev_in[i], rt->copy_in) != cudaSuccess)
+          st = PGB200_ERR_CUDA;
+        if (st != PGB200_OK) break;
+        std::lock_guard<std::mutex> lk(mu);
+        if (stop) return;
+        uploaded = i + 1;
+        cv.notify_all();
+      }
+      if (st != PGB200_OK) fail(&up_st, st);
+    });
+    std::thread downloader([&] {
+      if (cudaSetDevice(dev) != cudaSuccess) return fail(&down_st, PGB200_ERR_CUDA);
+      for (int i = 0; i < nb; i++) {
+        {
+          std::unique_lock<std::mutex> lk(mu);
+          cv.wait(lk, [&] { return stop || computed > i; });
+          if (computed <= i) return;  // stopped before this block's product was queued
+        }
+        int64_t r0, rows;
+        block(i, &r0, &rows);
+        int32_t st = PGB200_OK;
+        if (cudaStreamWaitEvent(rt->copy_out, ev_c[i], 0) != cudaSuccess) st = PGB200_ERR_CUDA;
+        if (st == PGB200_OK)
+          st = staged_download(rt, C + r0 * N, dC + r0 * N, (size_t)rows * N * sizeof(T),
+                               rt->copy_out);
+        if (st != PGB200_OK) return fail(&down_st, st);
+      }
+    });
+    for (int i = 0; i < nb; i++) {
+      {
+        std::unique_lock<std::mutex> lk(mu);
+        cv.wait(lk, [&] { return stop || uploaded > i; });
+        if (uploaded <= i) break;
+      }
+      int64_t r0, rows;
+      block(i, &r0, &rows);
+      int32_t st = PGB200_OK;
+      if (cudaStreamWaitEvent(s, ev_in[i], 0) != cudaSuccess) st = PGB200_ERR_CUDA;
+      if (st == PGB200_OK)
+        st = gemm_device<T>(s, rows, N, K, alpha, dA + r0 * K, K, dB, b_cols, transB, beta,
+                            dC + r0 * N, N, false, 0);
+      if (st == PGB200_OK && cudaEventRecord(ev_c[i], s) != cudaSuccess) st = PGB200_ERR_CUDA;
+      if (st != PGB200_OK) {
+        fail(&main_st, st);
+        break;
+      }
+      std::lock_guard<std::mutex> lk(mu);
+      computed = i + 1;
+      cv.notify_all();
+    }
+    {
+      // Whatever happened, let the helpers run out and collect them.
+      std::lock_guard<std::mutex> lk(mu);
+      if (main_st != PGB200_OK || up_st != PGB200_OK) stop = true;
+      cv.notify_all();
+    }
+    uploader.join();
+    downloader.join();
+    if (main_st != PGB200_OK) return main_st;
+    if (up_st != PGB200_OK || down_st != PGB200_OK) {
+      set_error("host-array pipeline: the %s thread failed (status %d)",
+                up_st != PGB200_OK ? "upload" : "download", up_st != PGB200_OK ? up_st : down_st);
+      return up_st != PGB200_OK ? up_st : down_st;
+    }
+    return PGB200_OK;
+  };
+  const int32_t st = run();
+  const cudaError_t e1 = cudaStreamSynchronize(rt->copy_in);
+  const cudaError_t e2 = cudaStreamSynchronize(rt->copy_out);
+  const cudaError_t e3 = cudaStreamSynchronize(s);
+  for (auto e : ev)
+    if (e) cudaEventDestroy(e);
+  if (st != PGB200_OK) return st;
+  PGB_CUDA(e1);
+  PGB_CUDA(e2);
+  PGB_CUDA(e3);
+  // Row blocks are downloaded as they finish, so a block whose kernel gave up
+  // may already be in C: the status tells the caller that C is not valid.
+  return take_device_status(rt);
+}
+
 // Host-array GEMM for large problems: the rows of A and C travel in blocks, so
 // that block i+1 is uploaded and block i-1 downloaded (PCIe is full duplex)
 // while block i is being multiplied.  B goes first, whole.  The result is what
@@ -885,8 +1068,13 @@ static int32_t gemm_entry(void *stream, int64_t M, int64_t N, int64_t K, T alpha
               (long long)lda, (long long)K, (long long)ldb, (long long)N);
   cudaStream_t s = (cudaStream_t)stream;
   if (K > 0 && M >= 1024 && (double)M * (double)N * (double)K >= 1e9 && needs_staging(A) &&
-      needs_staging(B) && needs_staging(C))
+      needs_staging(B) && needs_staging(C)) {
+    const int64_t per16 = 16 / (int64_t)sizeof(T), b_cols = transB ? K : N;
+    const bool dense = lda == K && ldb == b_cols && ldc == N && K % per16 == 0 && N % per16 == 0;
+    if (dense && is_pageable_host(A) && is_pageable_host(B) && is_pageable_host(C))
+      return gemm_host_staged<T>(rt, s, M, N, K, alpha, A, B, beta, C, transB);
     return gemm_host_pipelined<T>(rt, s, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, transB);
+  }
   Staged<T> sa, sb, sc;
   PGB_TRY(stage<T>(s, A, M, K, lda, true, false, &sa));
   if (transB)

@@ -1246,11 +1246,13 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
                : "memory");
   return v;
 }
+// lo = tf32(x - trunc_tf32(x)), rounded to nearest with ties away from zero like
+// cvt.rna.tf32.f32 - done on the integer pipe (add half an ulp of TF32 to the
+// magnitude, clear the 13 low bits): the conversion instruction runs at a
+// fraction of the ALU rate, and this sits on the critical path of every K-block.
 __device__ __forceinline__ float lo_part(float x) {
   const float hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
-  uint32_t l;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(x - hi));
-  return __uint_as_float(l);
+  return __uint_as_float((__float_as_uint(x - hi) + 0x1000u) & 0xFFFFE000u);
 }
 
 template <bool B_MN, int S>
@@ -1281,7 +1283,7 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
     for (int s = 0; s < STAGES; s++) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
-      mbar_init(ready0 + 8 * s, 2);  // one arrival per split warp
+      mbar_init(ready0 + 8 * s, EPI_WARPS);  // one arrival per drain warp (they make the lo tiles)
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(accf0 + 8 * b, 1);
@@ -1398,39 +1400,6 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
           if (ok) tc_commit(accf0 + 8 * buf);
         }
       }
-    } else {
-      // ------------------------------------------------- split warps (2 and 3)
-      const int st = (int)threadIdx.x - 64;  // 0..63
-      uint32_t stage = 0, phase = 0;
-      for (int64_t kb = kb_lo; kb < kb_hi; kb++) {
-        if (!mbar_wait(full0 + 8 * stage, phase)) {
-          if (lane == 0) report_status(status, 45, (int32_t)blockIdx.x);
-          break;
-        }
-        float4 *a_raw = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES);
-        float4 *a_lo = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + A_BYTES);
-        float4 *b_raw = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + 2 * A_BYTES);
-        float4 *b_lo =
-            reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + 2 * A_BYTES + B_BYTES);
-#pragma unroll
-        for (int i = 0; i < A_BYTES / 16 / 64; i++) {
-          const float4 x = a_raw[st + 64 * i];
-          a_lo[st + 64 * i] = make_float4(lo_part(x.x), lo_part(x.y), lo_part(x.z), lo_part(x.w));
-        }
-#pragma unroll 8
-        for (int i = 0; i < B_BYTES / 16 / 64; i++) {
-          const float4 x = b_raw[st + 64 * i];
-          b_lo[st + 64 * i] = make_float4(lo_part(x.x), lo_part(x.y), lo_part(x.z), lo_part(x.w));
-        }
-        // Make the generic-proxy writes visible to the tensor core's reads.
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(ready0 + 8 * stage);
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1;
-        }
-      }
     }
     if (S > 1) {
       // The two cluster barriers of the drain warps' reduction, matched here.
@@ -1457,13 +1426,13 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
             asm volatile("prefetch.global.L2 [%0];" ::"l"(C + pr * ldc + pc + q * 32));
       }
     }
-    for (int64_t ch = 0; ch < nch; ch++) {
+    // Adds accumulator chunk `ch` (tensor memory) into the registers.
+    auto drain_chunk = [&](int64_t ch) -> bool {
       const uint32_t buf = (uint32_t)(ch & 1);
       const uint32_t use = (uint32_t)((ch >> 1) & 1);
       if (!mbar_wait_backoff(accf0 + 8 * buf, use)) {
         if (lane == 0) report_status(status, 44, (int32_t)blockIdx.x);
-        ok = false;
-        break;
+        return false;
       }
       tc_fence_after();
       const uint32_t taddr =
@@ -1482,7 +1451,55 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acce0 + 8 * buf);
+      return true;
+    };
+    // The 256 drain threads also make the lo tiles (6 float4 each per K-block:
+    // two spare warps alone took longer per K-block than its MMAs).  A chunk's
+    // accumulator is drained a few K-blocks into the next chunk: by then its
+    // MMAs have retired (the stage being split was freed by a later MMA), and
+    // the MMA thread still has split stages in hand while the drain runs.
+    const int dtid = (int)threadIdx.x - 32 * FIRST_EPI_WARP;  // 0..255
+    const int64_t lag = chunk_kblocks > 3 ? 3 : chunk_kblocks - 1;
+    int64_t drained = 0;
+    {
+      uint32_t stage = 0, phase = 0;
+      for (int64_t kb = kb_lo; kb < kb_hi && ok; kb++) {
+        if (!mbar_wait(full0 + 8 * stage, phase)) {
+          if (lane == 0) report_status(status, 45, (int32_t)blockIdx.x);
+          ok = false;
+          break;
+        }
+        float4 *a_raw = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES);
+        float4 *a_lo = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + A_BYTES);
+        float4 *b_raw = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + 2 * A_BYTES);
+        float4 *b_lo =
+            reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + 2 * A_BYTES + B_BYTES);
+        float4 xa[A_BYTES / 16 / 256], xb[B_BYTES / 16 / 256];
+#pragma unroll
+        for (int i = 0; i < A_BYTES / 16 / 256; i++) xa[i] = a_raw[dtid + 256 * i];
+#pragma unroll
+        for (int i = 0; i < B_BYTES / 16 / 256; i++) xb[i] = b_raw[dtid + 256 * i];
+#pragma unroll
+        for (int i = 0; i < A_BYTES / 16 / 256; i++)
+          a_lo[dtid + 256 * i] =
+              make_float4(lo_part(xa[i].x), lo_part(xa[i].y), lo_part(xa[i].z), lo_part(xa[i].w));
+#pragma unroll
+        for (int i = 0; i < B_BYTES / 16 / 256; i++)
+          b_lo[dtid + 256 * i] =
+              make_float4(lo_part(xb[i].x), lo_part(xb[i].y), lo_part(xb[i].z), lo_part(xb[i].w));
+        // Make the generic-proxy writes visible to the tensor core's reads.
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready0 + 8 * stage);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+        while (ok && drained + 1 < nch && kb - kb_lo >= (drained + 1) * chunk_kblocks + lag)
+          ok = drain_chunk(drained++);
+      }
     }
+    while (ok && drained < nch) ok = drain_chunk(drained++);
 
     const int ew = warp - FIRST_EPI_WARP;
     const int64_t r_base = tm * BM + quarter * 32;

@@ -188,6 +188,33 @@ def test_pin_rejects_overlap_and_unknown_pointers():
     assert lib.pgb200Pin(d.data_ptr(), 64) == pgb.ERR_INVALID
 
 
+def test_large_pageable_arrays_travel_through_the_staging_rings():
+    """Pageable (malloc'd) host arrays of 64 MiB and more are moved by the
+    library's own page-locked rings, several host threads doing the memcpy:
+    upload of a big input (mat-vec pair), download of a big output (a wide
+    GEMM), and the byte counters still add up."""
+    n = 3072                                            # A: 72 MiB
+    Am = pbo.fill(n, n, np.float64, SEED, 1, 0.0, 1.0)
+    v = [pbo.fill_vec(n, np.float64, SEED, 2 + k, 0.0, 1.0) for k in range(4)]
+    r = [x.copy() for x in v]
+    pbo.mvt(r[0], r[1], r[2], r[3], Am)
+    h0, d0 = pgb.transfer_counters()
+    polybench.kernel_mvt(n, v[0], v[1], v[2], v[3], Am)
+    h1, d1 = pgb.transfer_counters()
+    assert elementwise_rel(v[0], r[0]) <= 1e-12 and elementwise_rel(v[1], r[1]) <= 1e-12
+    assert h1 - h0 == Am.nbytes + 4 * n * 8 and d1 - d0 == 2 * n * 8
+    M, N, K = 512, 20000, 64                            # C: 78 MiB, below the row-block pipeline
+    A = pbo.fill(M, K, np.float64, SEED, 6, -1.0, 1.0)
+    B = pbo.fill(K, N, np.float64, SEED, 7, -1.0, 1.0)
+    C0 = pbo.fill(M, N, np.float64, SEED, 8, -1.0, 1.0)
+    got = C0.copy()
+    polybench.kernel_gemm(M, N, K, 1.5, 1.2, got, A, B)
+    assert normwise(got, 1.5 * (A @ B) + 1.2 * C0) <= 1e-12
+    ref = pbo.gemm(1.5, 1.2, C0[7:8].copy(), A[7:8], B)
+    assert normwise(got[7:8], ref) <= 1e-12
+    pgb.poll_device_status()
+
+
 # --------------------------------------------------------------------------- multi-GPU entries
 @pytest.mark.parametrize("ndev", [1, 2])
 def test_multi_gpu_entries_wait_for_the_callers_device_work(ndev):
