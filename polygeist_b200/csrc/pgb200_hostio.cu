@@ -58,7 +58,6 @@ class CopyPool {
     std::unique_lock<std::mutex> lk(job.mu);
     job.cv.wait(lk, [&] { return job.left == 0; });
   }
-  int threads() const { return (int)workers_.size(); }
 
  private:
   struct Job {

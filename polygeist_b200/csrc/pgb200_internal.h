@@ -168,7 +168,7 @@ struct Staged {
 
 // Scratch memory of one call: hi/lo planes, split-K partial products, mat-vec
 // partial sums.  No two calls that can run at the same time ever share a block:
-//  * small requests (<= 32 MiB) come from a cache private to the calling host
+//  * small requests (<= 64 MiB) come from a cache private to the calling host
 //    thread, one block per (device, stream, nesting depth): a thread's calls on
 //    one stream are ordered on that stream, so reusing its block is safe, and
 //    other threads - on the same stream or another - have blocks of their own.

@@ -299,7 +299,7 @@ int32_t get_runtime(Runtime **out) {
 // Per-call scratch (see PoolBuffer in pgb200_internal.h).
 // ---------------------------------------------------------------------------
 namespace {
-constexpr size_t SMALL_SCRATCH = size_t(32) << 20;
+constexpr size_t SMALL_SCRATCH = size_t(64) << 20;
 struct CachedBlock {
   void *ptr = nullptr;
   size_t bytes = 0;

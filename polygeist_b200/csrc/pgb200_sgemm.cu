@@ -1228,32 +1228,52 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
 //    itself).  The MMA thread waits on a "ready" barrier the split warps signal
 //    after a generic->async proxy fence.
 //  * Split-K inside a thread-block cluster.  The S CTAs of a cluster (S = 1, 2
-//    or 4) share one 128x256 tile and take consecutive K ranges.  Each writes
-//    its partial tile into its own shared memory (the ring is free by then),
-//    the cluster synchronises, and CTA r adds up column slice r of all S partial
-//    tiles over distributed shared memory, in rank order - so the sum does not
-//    depend on timing - applies alpha/beta and stores its slice of C.  No
-//    partial product ever leaves the SMs, nothing has to be zeroed, and
-//    beta == 0 still never reads C.
+//    or 4) share one 128x256 tile and take consecutive K ranges.  The partial
+//    tiles are exchanged as a reduce-scatter: CTA q writes column slice r of its
+//    partial tile to a small exchange buffer in global memory (it stays in L2),
+//    ONE cluster barrier (release / acquire) orders the writes before the reads,
+//    and CTA r adds the S slices of its column range in rank order - its own
+//    from registers - so the sum does not depend on timing; then alpha/beta and
+//    the store of its slice of C.  No counters, nothing to zero, no second
+//    launch, and beta == 0 still never reads C.  (Distributed shared memory was
+//    tried for the exchange, pulling and pushing: the SM-to-SM path moved the
+//    96 KiB per CTA at ~20 bytes per cycle, 5-6 thousand cycles; through L2 the
+//    same exchange takes about half of that.)
 //
 // One (tile, K range) per CTA; grid = tiles * S, cluster = (S, 1, 1).
 // ===========================================================================
-__device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(cluster_addr)
-               : "memory");
-  return v;
-}
 // lo = tf32(x - trunc_tf32(x)), rounded to nearest with ties away from zero like
 // cvt.rna.tf32.f32 - done on the integer pipe (add half an ulp of TF32 to the
 // magnitude, clear the 13 low bits): the conversion instruction runs at a
 // fraction of the ALU rate, and this sits on the critical path of every K-block.
+// lo = tf32(x - trunc_tf32(x)), rounded to nearest with ties away from zero like
+// cvt.rna.tf32.f32 - done on the integer pipe (add half an ulp of TF32 to the
+// magnitude, clear the 13 low bits): the conversion instruction runs at a
+// fraction of the ALU rate, and this sits on the critical path of every K-block.
+__device__ __forceinline__ void st_cluster_f4(uint32_t cluster_addr, float a, float b, float c,
+                                              float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(a),
+               "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
 __device__ __forceinline__ float lo_part(float x) {
   const float hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
   return __uint_as_float((__float_as_uint(x - hi) + 0x1000u) & 0xFFFFE000u);
 }
+
+#ifdef PGB200_FUSED_TRACE
+// Development aid (not part of the product build): cycle stamps of a few CTAs.
+__device__ long long g_fused_trace[8][16];
+#define FUSED_STAMP(point)                                                        \
+  do {                                                                            \
+    if ((blockIdx.x & 15) == 0 && (blockIdx.x >> 4) < 8)                          \
+      g_fused_trace[blockIdx.x >> 4][(point)] = clock64();                        \
+  } while (0)
+#else
+#define FUSED_STAMP(point) \
+  do {                     \
+  } while (0)
+#endif
 
 template <bool B_MN, int S>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -1263,33 +1283,108 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
                          int chunk_kblocks, int b_blocked, int32_t *status) {
   static_assert(S == 1 || S == 2 || S == 4, "cluster size");
   constexpr int W = 128 / S;  // columns of the final tile each drain thread reduces and stores
+  // Two rings share the 192 KiB: raw tiles (A 8 KiB + B 16 KiB per K-block), six
+  // deep so that TMA runs ~4600 tensor-core cycles ahead (the first touch of
+  // every panel comes from DRAM), and lo tiles, two deep: they are made just in
+  // time and consumed at once.
+  constexpr int RAW_BYTES = A_BYTES + B_BYTES;  // 24 KiB
+  constexpr int RSTAGES = 6, LSTAGES = 2;
+  static_assert((RSTAGES + LSTAGES) * RAW_BYTES + 1024 <= SMEM_BYTES, "ring does not fit");
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[3 * STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[2 * RSTAGES + 2 * LSTAGES + 4];
   __shared__ uint32_t tmem_slot;
   __shared__ float epi_stage[EPI_WARPS][32][33];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
-  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
-  const uint32_t ready0 = smem_u32(&bars[2 * STAGES]);
-  const uint32_t accf0 = smem_u32(&bars[3 * STAGES]), acce0 = smem_u32(&bars[3 * STAGES + 2]);
+  const uint32_t lo_ring = ring + RSTAGES * RAW_BYTES;
+  uint8_t *lo_ptr = ring_ptr + RSTAGES * RAW_BYTES;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[RSTAGES]);
+  const uint32_t ready0 = smem_u32(&bars[2 * RSTAGES]);           // lo slot filled
+  const uint32_t lfree0 = smem_u32(&bars[2 * RSTAGES + LSTAGES]);  // lo slot consumed
+  const uint32_t accf0 = smem_u32(&bars[2 * RSTAGES + 2 * LSTAGES]);
+  const uint32_t acce0 = smem_u32(&bars[2 * RSTAGES + 2 * LSTAGES + 2]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = S > 1 ? cluster_ctarank() : 0u;
+  if (threadIdx.x == 0) FUSED_STAMP(0);
 
   if (threadIdx.x == 64) {
     prefetch_tensor_map(&mapA);
     prefetch_tensor_map(&mapB);
   }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) {
+    for (int s = 0; s < RSTAGES; s++) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int s = 0; s < LSTAGES; s++) {
       mbar_init(ready0 + 8 * s, EPI_WARPS);  // one arrival per drain warp (they make the lo tiles)
+      mbar_init(lfree0 + 8 * s, 1);
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(accf0 + 8 * b, 1);
       mbar_init(acce0 + 8 * b, EPI_WARPS);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // This CTA's work item: tile (cluster index), K-block range (rank).  32-bit
+  // arithmetic where the values allow it: 64-bit divisions cost hundreds of
+  // cycles each and sit in front of the first load.
+  const int64_t t = (int64_t)(blockIdx.x / (unsigned)S);
+  const int64_t nkb = (K + BK - 1) / BK;
+  const int64_t kb_lo = (int64_t)rank * tiles.kper < nkb ? (int64_t)rank * tiles.kper : nkb;
+  const int64_t kb_hi = kb_lo + tiles.kper < nkb ? kb_lo + tiles.kper : nkb;
+  const int64_t nch =
+      (int64_t)(((unsigned)(kb_hi - kb_lo) + (unsigned)chunk_kblocks - 1u) / (unsigned)chunk_kblocks);
+  int64_t tm, tn;
+  if (!tiles.lower) {
+    // TileCursor::seek for a full product, on unsigned ints.
+    const unsigned idx = (unsigned)t, tmn = (unsigned)tiles.tiles_m, tnn = (unsigned)tiles.tiles_n;
+    const unsigned per_group = (unsigned)TileCursor::G * tnn, grp = idx / per_group;
+    const unsigned first = grp * (unsigned)TileCursor::G;
+    const unsigned rows = tmn - first < (unsigned)TileCursor::G ? tmn - first : (unsigned)TileCursor::G;
+    const unsigned in = idx - grp * per_group;
+    tm = first + in % rows;
+    tn = in / rows;
+  } else {
+    TileCursor cur;
+    cur.seek(tiles, t, &tm, &tn);
+  }
+  // The producer's state lives across the CTA-wide sync below: its first loads
+  // (cold: DRAM and page-table latency) leave before tensor memory is allocated.
+  uint32_t p_stage = 0, p_phase = 0;
+  int64_t p_kb = kb_lo;
+  auto produce = [&](int64_t kb) {
+    const uint32_t dst = ring + p_stage * RAW_BYTES;
+    const uint32_t bar = full0 + 8 * p_stage;
+    mbar_expect_tx(bar, RAW_BYTES);
+    const int k0 = (int)(kb * BK);
+    tma_load_2d(dst, &mapA, bar, k0, (int)(tm * BM));
+    if (B_MN) {
+      // Row-major B as it lies: eight [BK x 32] column blocks, by one 3-D copy
+      // when N is a multiple of 32, else by eight 2-D copies (zero-filled past
+      // column N).
+      if (b_blocked) {
+        tma_load_3d(dst + A_BYTES, &mapB, bar, 0, k0, (int)(tn * (BN / 32)));
+      } else {
+#pragma unroll
+        for (int j = 0; j < BN / 32; j++)
+          tma_load_2d(dst + A_BYTES + j * (BK * 128), &mapB, bar, (int)(tn * BN) + 32 * j, k0);
+      }
+    } else {
+      tma_load_2d(dst + A_BYTES, &mapB, bar, k0, (int)(tn * BN));
+    }
+    if (++p_stage == RSTAGES) {
+      p_stage = 0;
+      p_phase ^= 1;
+    }
+  };
+  if (threadIdx.x == 0) {
+    // Every stage is free at the start: fill the ring (thread 0 initialised the
+    // barriers itself, so it may use them before the sync).
+    for (; p_kb < kb_hi && p_kb < kb_lo + RSTAGES; p_kb++) {
+      if (p_kb == kb_lo) FUSED_STAMP(2);
+      produce(p_kb);
+    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -1302,60 +1397,25 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-
-  // This CTA's work item: tile (cluster index), K-block range (rank).
-  const int64_t t = (int64_t)blockIdx.x / S;
-  const int64_t nkb = (K + BK - 1) / BK;
-  const int64_t kb_lo = (int64_t)rank * tiles.kper < nkb ? (int64_t)rank * tiles.kper : nkb;
-  const int64_t kb_hi = kb_lo + tiles.kper < nkb ? kb_lo + tiles.kper : nkb;
-  const int64_t nch = (kb_hi - kb_lo + chunk_kblocks - 1) / chunk_kblocks;
-  int64_t tm, tn;
-  {
-    TileCursor cur;
-    cur.seek(tiles, t, &tm, &tn);
-  }
+  if (threadIdx.x == 0) FUSED_STAMP(1);
 
   if (warp < FIRST_EPI_WARP) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
       // ------------------------------------------------------------ TMA producer
       if (lane == 0) {
-        uint32_t stage = 0, phase = 0;
-        for (int64_t kb = kb_lo; kb < kb_hi; kb++) {
-          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) {
+        for (; p_kb < kb_hi; p_kb++) {
+          if (!mbar_wait(empty0 + 8 * p_stage, p_phase ^ 1)) {
             report_status(status, 41, (int32_t)blockIdx.x);
             break;
           }
-          const uint32_t dst = ring + stage * STAGE_BYTES;
-          const uint32_t bar = full0 + 8 * stage;
-          mbar_expect_tx(bar, A_BYTES + B_BYTES);
-          const int k0 = (int)(kb * BK);
-          tma_load_2d(dst, &mapA, bar, k0, (int)(tm * BM));
-          if (B_MN) {
-            // Row-major B as it lies: eight [BK x 32] column blocks, by one 3-D
-            // copy when N is a multiple of 32, else by eight 2-D copies
-            // (zero-filled past column N).
-            if (b_blocked) {
-              tma_load_3d(dst + 2 * A_BYTES, &mapB, bar, 0, k0, (int)(tn * (BN / 32)));
-            } else {
-#pragma unroll
-              for (int j = 0; j < BN / 32; j++)
-                tma_load_2d(dst + 2 * A_BYTES + j * (BK * 128), &mapB, bar, (int)(tn * BN) + 32 * j,
-                            k0);
-            }
-          } else {
-            tma_load_2d(dst + 2 * A_BYTES, &mapB, bar, k0, (int)(tn * BN));
-          }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
+          produce(p_kb);
         }
       }
     } else if (warp == 1) {
       // -------------------------------------------------------------- MMA issuer
       if (lane == 0) {
-        uint32_t stage = 0, phase = 0;
+        uint32_t stage = 0, lslot = 0, lphase = 0;
         bool ok = true;
         for (int64_t ch = 0; ch < nch && ok; ch++) {
           const uint32_t buf = (uint32_t)(ch & 1);
@@ -1369,18 +1429,18 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
           const int64_t kb_first = kb_lo + ch * chunk_kblocks;
           const int64_t kb_end = kb_first + chunk_kblocks < kb_hi ? kb_first + chunk_kblocks : kb_hi;
           for (int64_t kb = kb_first; kb < kb_end; kb++) {
-            if (!mbar_wait(ready0 + 8 * stage, phase)) {
+            // The lo tile is made from the raw tile, so "lo ready" implies "raw full".
+            if (!mbar_wait(ready0 + 8 * lslot, lphase)) {
               report_status(status, 43, (int32_t)blockIdx.x);
               ok = false;
               break;
             }
             tc_fence_after();
-            const uint32_t sa = ring + stage * STAGE_BYTES;
-            const uint64_t ahi = smem_desc_sw64(sa), alo = smem_desc_sw64(sa + A_BYTES);
-            const uint64_t bhi = B_MN ? smem_desc_mn_sw128(sa + 2 * A_BYTES)
-                                      : smem_desc_sw64(sa + 2 * A_BYTES);
-            const uint64_t blo = B_MN ? smem_desc_mn_sw128(sa + 2 * A_BYTES + B_BYTES)
-                                      : smem_desc_sw64(sa + 2 * A_BYTES + B_BYTES);
+            if (kb == kb_lo) FUSED_STAMP(4);
+            const uint32_t sr = ring + stage * RAW_BYTES, sl = lo_ring + lslot * RAW_BYTES;
+            const uint64_t ahi = smem_desc_sw64(sr), alo = smem_desc_sw64(sl);
+            const uint64_t bhi = B_MN ? smem_desc_mn_sw128(sr + A_BYTES) : smem_desc_sw64(sr + A_BYTES);
+            const uint64_t blo = B_MN ? smem_desc_mn_sw128(sl + A_BYTES) : smem_desc_sw64(sl + A_BYTES);
             constexpr uint32_t idesc = B_MN ? IDESC_BMN : IDESC;
             const bool first = (kb == kb_first);
 #pragma unroll
@@ -1391,20 +1451,22 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
               tc_mma_tf32(tmem_d, ahi + ko, blo + kob, idesc, 1u);
               tc_mma_tf32(tmem_d, ahi + ko, bhi + kob, idesc, 1u);
             }
-            tc_commit(empty0 + 8 * stage);
-            if (++stage == STAGES) {
-              stage = 0;
-              phase ^= 1;
+            tc_commit(empty0 + 8 * stage);   // raw stage back to the producer
+            tc_commit(lfree0 + 8 * lslot);   // lo slot back to the drain warps
+            if (++stage == RSTAGES) stage = 0;
+            if (++lslot == LSTAGES) {
+              lslot = 0;
+              lphase ^= 1;
             }
           }
           if (ok) tc_commit(accf0 + 8 * buf);
         }
+        FUSED_STAMP(5);
       }
     }
     if (S > 1) {
-      // The two cluster barriers of the drain warps' reduction, matched here.
+      // The cluster barrier of the drain warps' reduction, matched here.
       __syncwarp();
-      cluster_sync_all();
       cluster_sync_all();
     }
   } else {
@@ -1455,51 +1517,48 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
     };
     // The 256 drain threads also make the lo tiles (6 float4 each per K-block:
     // two spare warps alone took longer per K-block than its MMAs).  A chunk's
-    // accumulator is drained a few K-blocks into the next chunk: by then its
-    // MMAs have retired (the stage being split was freed by a later MMA), and
-    // the MMA thread still has split stages in hand while the drain runs.
+    // accumulator is drained once a later lo slot has come back, which shows that
+    // the chunk's last MMA has retired; the MMA thread then still has up to two
+    // K-blocks in hand while the drain runs.
     const int dtid = (int)threadIdx.x - 32 * FIRST_EPI_WARP;  // 0..255
-    const int64_t lag = chunk_kblocks > 3 ? 3 : chunk_kblocks - 1;
+    const int64_t lag = chunk_kblocks > 1 ? 1 : 0;
     int64_t drained = 0;
     {
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, lslot = 0, lphase = 0;
       for (int64_t kb = kb_lo; kb < kb_hi && ok; kb++) {
-        if (!mbar_wait(full0 + 8 * stage, phase)) {
+        if (!mbar_wait(full0 + 8 * stage, phase) || !mbar_wait(lfree0 + 8 * lslot, lphase ^ 1)) {
           if (lane == 0) report_status(status, 45, (int32_t)blockIdx.x);
           ok = false;
           break;
         }
-        float4 *a_raw = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES);
-        float4 *a_lo = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + A_BYTES);
-        float4 *b_raw = reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + 2 * A_BYTES);
-        float4 *b_lo =
-            reinterpret_cast<float4 *>(ring_ptr + stage * STAGE_BYTES + 2 * A_BYTES + B_BYTES);
-        float4 xa[A_BYTES / 16 / 256], xb[B_BYTES / 16 / 256];
+        if (kb == kb_lo && dtid == 0) FUSED_STAMP(3);
+        const float4 *raw = reinterpret_cast<const float4 *>(ring_ptr + stage * RAW_BYTES);
+        float4 *lo = reinterpret_cast<float4 *>(lo_ptr + lslot * RAW_BYTES);
+        float4 x[RAW_BYTES / 16 / 256];
 #pragma unroll
-        for (int i = 0; i < A_BYTES / 16 / 256; i++) xa[i] = a_raw[dtid + 256 * i];
+        for (int i = 0; i < RAW_BYTES / 16 / 256; i++) x[i] = raw[dtid + 256 * i];
 #pragma unroll
-        for (int i = 0; i < B_BYTES / 16 / 256; i++) xb[i] = b_raw[dtid + 256 * i];
-#pragma unroll
-        for (int i = 0; i < A_BYTES / 16 / 256; i++)
-          a_lo[dtid + 256 * i] =
-              make_float4(lo_part(xa[i].x), lo_part(xa[i].y), lo_part(xa[i].z), lo_part(xa[i].w));
-#pragma unroll
-        for (int i = 0; i < B_BYTES / 16 / 256; i++)
-          b_lo[dtid + 256 * i] =
-              make_float4(lo_part(xb[i].x), lo_part(xb[i].y), lo_part(xb[i].z), lo_part(xb[i].w));
+        for (int i = 0; i < RAW_BYTES / 16 / 256; i++)
+          lo[dtid + 256 * i] =
+              make_float4(lo_part(x[i].x), lo_part(x[i].y), lo_part(x[i].z), lo_part(x[i].w));
         // Make the generic-proxy writes visible to the tensor core's reads.
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(ready0 + 8 * stage);
-        if (++stage == STAGES) {
+        if (lane == 0) mbar_arrive(ready0 + 8 * lslot);
+        if (++stage == RSTAGES) {
           stage = 0;
           phase ^= 1;
+        }
+        if (++lslot == LSTAGES) {
+          lslot = 0;
+          lphase ^= 1;
         }
         while (ok && drained + 1 < nch && kb - kb_lo >= (drained + 1) * chunk_kblocks + lag)
           ok = drain_chunk(drained++);
       }
     }
     while (ok && drained < nch) ok = drain_chunk(drained++);
+    if (dtid == 0) FUSED_STAMP(6);
 
     const int ew = warp - FIRST_EPI_WARP;
     const int64_t r_base = tm * BM + quarter * 32;
@@ -1509,25 +1568,59 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
         epilogue_store<128>(acc, epi_stage[ew], lane, r_base, cb, M, N, ldc, C, alpha, beta,
                             tiles.lower != 0, tiles.row0);
     } else {
-      // Partial tile -> own shared memory as [float4 index][drain thread]: every
-      // warp access, local or remote, is 512 contiguous bytes.  All MMAs that
-      // read the ring have retired (the last accumulator was complete before it
-      // was drained), so the ring is free.
+      // Reduce-scatter through the exchange buffer: slice r of this CTA's
+      // partial tile goes to block (cluster, receiver r, source rank) as
+      // [float4 index in the slice][drain thread], so every warp access is 512
+      // contiguous bytes; the own slice stays in registers.
       const int dt = (int)threadIdx.x - 32 * FIRST_EPI_WARP;  // drain thread 0..255
-      float4 *part = reinterpret_cast<float4 *>(ring_ptr);
+      constexpr int SLICE4 = W / 4;                            // float4 per thread and slice
+      float4 *xbuf = reinterpret_cast<float4 *>(tiles.partial) +
+                     (size_t)t * S * S * SLICE4 * 256;
+      if (dt == 0) FUSED_STAMP(7);
 #pragma unroll
-      for (int j = 0; j < 32; j++)
-        part[j * 256 + dt] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+      for (int j = 0; j < 32; j++) {
+        const uint32_t r = (uint32_t)(j / SLICE4), jl = (uint32_t)(j % SLICE4);
+        if (r != rank)
+          __stcg(xbuf + ((size_t)(r * S + rank) * SLICE4 + jl) * 256 + dt,
+                 make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
+      }
+      // Own slice: `acc` is indexed with a run-time rank, so it is selected with
+      // constant indices (the array stays in registers and is dead afterwards).
+      float mine[W];
+#pragma unroll
+      for (int rr = 0; rr < S; rr++)
+        if ((uint32_t)rr == rank) {
+#pragma unroll
+          for (int i = 0; i < W; i++) mine[i] = acc[rr * W + i];
+        }
+      // The old values of this CTA's slice of C, asked for before the barrier so
+      // that their latency hides behind it (interior tiles only; edge and
+      // diagonal tiles take the general epilogue below).
+      const int64_t cs = cb + rank * W;  // first column of this thread block's slice
+      const bool interior = (r_base + 31 < M) && (cs + W - 1 < N) &&
+                            (!tiles.lower || cs + W - 1 <= r_base + tiles.row0);
+      float cold[W];
+      if (interior && beta != 0.0f) {
+#pragma unroll
+        for (int b = 0; b < W / 32; b++)
+#pragma unroll
+          for (int q = 0; q < 32; q++)
+            cold[b * 32 + q] = __ldcs(C + (r_base + q) * ldc + cs + b * 32 + lane);
+      }
       __syncwarp();
-      cluster_sync_all();  // every CTA's partial tile is in place (release/acquire)
+      if (dt == 0) FUSED_STAMP(8);
+      cluster_sync_all();  // every peer's slices are written (release) and visible (acquire)
+      if (dt == 0) FUSED_STAMP(9);
       float red[W];
-      // Column slice `rank` of this thread's row, from every CTA in rank order.
 #pragma unroll
       for (int q = 0; q < S; q++) {
 #pragma unroll
-        for (int j = 0; j < W / 4; j++) {
-          const uint32_t local = ring + (uint32_t)(((rank * (W / 4) + j) * 256 + dt) * 16);
-          const float4 v = ld_cluster_f4(map_to_cta(local, (uint32_t)q));
+        for (int j = 0; j < SLICE4; j++) {
+          float4 v;
+          if ((uint32_t)q == rank)
+            v = make_float4(mine[4 * j], mine[4 * j + 1], mine[4 * j + 2], mine[4 * j + 3]);
+          else
+            v = __ldcg(xbuf + ((size_t)(rank * S + q) * SLICE4 + j) * 256 + dt);
           if (q == 0) {
             red[4 * j] = v.x; red[4 * j + 1] = v.y; red[4 * j + 2] = v.z; red[4 * j + 3] = v.w;
           } else {
@@ -1535,11 +1628,29 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
           }
         }
       }
-      if (ok)
-        epilogue_store<W>(red, epi_stage[ew], lane, r_base, cb + rank * W, M, N, ldc, C, alpha,
-                          beta, tiles.lower != 0, tiles.row0);
-      __syncwarp();
-      cluster_sync_all();  // nobody's shared memory goes away while a peer reads it
+      if (dt == 0) FUSED_STAMP(10);
+      if (ok && interior) {
+        // Turn each 32x32 block through the padded shared tile so that C is
+        // written as full 128-byte row segments (lane = column).
+        float(*stg)[33] = epi_stage[ew];
+#pragma unroll
+        for (int b = 0; b < W / 32; b++) {
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 32; i++) stg[lane][i] = alpha * red[b * 32 + i];
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 32; q++) {
+            const float o = stg[q][lane];
+            C[(r_base + q) * ldc + cs + b * 32 + lane] =
+                (beta != 0.0f) ? fmaf(beta, cold[b * 32 + q], o) : o;
+          }
+        }
+      } else if (ok) {
+        epilogue_store<W>(red, epi_stage[ew], lane, r_base, cs, M, N, ldc, C, alpha, beta,
+                          tiles.lower != 0, tiles.row0);
+      }
+      if (dt == 0) FUSED_STAMP(11);
     }
   }
 
@@ -1551,9 +1662,16 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
                  "r"(TMEM_COLS)
                  : "memory");
   }
+  if (threadIdx.x == 32) FUSED_STAMP(12);
 }
 
 }  // namespace
+
+#ifdef PGB200_FUSED_TRACE
+extern "C" int32_t pgb200DebugFusedTrace(long long *out) {
+  return cudaMemcpyFromSymbol(out, g_fused_trace, sizeof(g_fused_trace)) == cudaSuccess ? 0 : 2;
+}
+#endif
 
 // Self-test of the bounded-wait machinery: one CTA waits on an mbarrier that
 // nothing ever arrives at, with a caller-chosen cycle limit, and must come back
@@ -1685,6 +1803,13 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     }
     ft.splits = S;
     ft.kper = fk;
+    // Exchange buffer of the in-cluster reduce-scatter: S x S slices per tile,
+    // S * 128 KiB in all per tile; written and read once, it lives in L2.
+    PoolBuffer xchg;
+    if (S > 1) {
+      PGB_CUDA(xchg.alloc((size_t)ft.total * S * BM * 256 * sizeof(float), s));
+      ft.partial = xchg.as<float>();
+    }
     CUtensorMap mA, mB;
     const int fb_blocked = (!transB && (N % 32) == 0) ? 1 : 0;
     PGB_TRY(make_plane_map(&mA, A, M, K, lda, BM));
