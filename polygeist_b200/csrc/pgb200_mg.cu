@@ -50,6 +50,8 @@ ncclResult_t failing_async_error(ncclComm_t, ncclResult_t *out) {
 
 struct MgState {
   int ndev = 0;
+  bool links_checked = false;  // this call's link streams have been drained (or found failed)
+  bool comm_failed = false;    // a collective failed or is overdue: communicators to be aborted
   std::vector<ncclComm_t> comm;
   std::vector<cudaStream_t> compute, link;
 };
@@ -241,6 +243,20 @@ bool drain_link(MgState *st, int d) {
   }
 }
 
+// Drains the link streams of all devices (once per call), polling for
+// collective failures; false when a collective failed or is overdue.
+bool mg_links_ok(MgState *st) {
+  if (st->links_checked) return !st->comm_failed;
+  st->links_checked = true;
+  st->comm_failed = false;
+  if (st->ndev > 1)
+    for (int d = 0; d < st->ndev && !st->comm_failed; d++) {
+      cudaSetDevice(d);
+      if (!drain_link(st, d)) st->comm_failed = true;
+    }
+  return !st->comm_failed;
+}
+
 // Common exit of the multi-GPU entries, also taken after a failure: drain both
 // streams of every device, release the scratch, destroy the events and make
 // the caller's device current again.  Returns `status`, or the first error of
@@ -255,12 +271,9 @@ int32_t mg_release(MgState *st, int entry_dev, int32_t status,
   // Link streams first: when a collective failed or is overdue the
   // communicators are aborted, which also ends kernels still waiting on a peer,
   // so the synchronisations below cannot hang.
-  bool comm_ok = true;
-  if (st->ndev > 1)
-    for (int d = 0; d < st->ndev && comm_ok; d++) {
-      note(cudaSetDevice(d));
-      comm_ok = drain_link(st, d);
-    }
+  const bool comm_ok = mg_links_ok(st);
+  st->links_checked = false;  // per call
+  st->comm_failed = false;
   if (!comm_ok && status == PGB200_OK) status = PGB200_ERR_NCCL;
   if (!comm_ok && g_nccl.CommAbort) {
     for (int d = 0; d < st->ndev; d++) {
@@ -293,6 +306,8 @@ int32_t mg_release(MgState *st, int entry_dev, int32_t status,
 // Before the results travel back: wait for every device's products and read
 // its status word, so a kernel that gave up is reported instead of copied.
 int32_t mg_products_done(MgState *st) {
+  // A failed or overdue broadcast means the products ran on incomplete data.
+  if (!mg_links_ok(st)) return PGB200_ERR_NCCL;
   int32_t status = PGB200_OK;
   for (int d = 0; d < st->ndev; d++) {
     PGB_CUDA(cudaSetDevice(d));
