@@ -591,6 +591,7 @@ class Bench:
                 derate = 1.4 / 1.59  # fallback ratio of the profiling recipe
         peak = burst * derate
         ach = 3 * (units / world if strong else units) / (ms_per_step * 1e-3) / 1e12
+        lib = self.library_tf32() if (capped and world == 1) else None
         return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                 "frac": ach / peak, "frac_of_burst": ach / burst, "traffic": TRAFFIC.get(name),
                 "peak_burst": burst, "peak_after_run": peak_hot,
@@ -599,7 +600,48 @@ class Bench:
                                + (f"burst x {derate:.3f} (sustained/burst ratio of the measured "
                                   "bf16 GEMM) because the timed region ran at the power cap" if capped
                                   else "burst (max of before/after the timed region)")
-                               + "; achieved counts the 3 tensor products per useful product", **extra}
+                               + "; achieved counts the 3 tensor products per useful product",
+                "library_tf32": lib, **extra}
+
+    def library_tf32(self):
+        """Context for the power-capped fp32 figures: the vendor library's dense
+        TF32 GEMM (torch.matmul with TF32 allowed, 8192^3) on this GPU, best of 10
+        and back to back for 3 s - the same protocol MEASURED_PEAKS.json used for
+        bf16.  Not a kernel of this library and not on its path; it only shows
+        what a dense TF32 GEMM sustains under the same 1 kW cap."""
+        torch = self.torch
+        try:
+            old = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = True
+            n = 8192
+            a = torch.rand((n, n), dtype=torch.float32, device=self.dev)
+            b = torch.rand((n, n), dtype=torch.float32, device=self.dev)
+            c = torch.empty((n, n), dtype=torch.float32, device=self.dev)
+            torch.cuda.synchronize()
+            time.sleep(2.0)                      # from an idle GPU, like a burst probe
+            best = 1e9
+            for _ in range(10):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                torch.matmul(a, b, out=c)
+                e1.record()
+                torch.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(10, int(3000.0 / best))
+            e0.record()
+            for _ in range(reps):
+                torch.matmul(a, b, out=c)
+            e1.record()
+            torch.cuda.synchronize()
+            sus = e0.elapsed_time(e1) / reps
+            torch.backends.cuda.matmul.allow_tf32 = old
+            flop = 2.0 * n ** 3
+            return {"burst_tflops": flop / (best * 1e-3) / 1e12,
+                    "sustained_tflops": flop / (sus * 1e-3) / 1e12,
+                    "how": "torch.matmul, TF32 allowed, 8192^3: best of 10 / back to back for 3 s"}
+        except Exception as ex:               # context only: never fails the bench
+            return {"error": repr(ex)}
 
     def cold_peak(self, name, w):
         if self.rank != 0 or name.startswith("mvt"):
@@ -748,11 +790,17 @@ def run_pgb200(args, w, name):
             k = min(args.steps, 20 if wn != "sgemm32768" else 5)
             ms, ln, ck, rf, o = bench.measure(wn, ww, k, max(3, min(args.warmup, 5)))
             m2, u2, s2 = metric_of(wn)
+            # end to end through the host-array drop-in where one call is short
+            pe = None
+            if wn.startswith(("dgemm", "sgemm")) and wn != "sgemm32768":
+                pe, _ = bench.e2e_gemm(wn, ww, o, algorithmic_work(wn, ww), s2, u2, 5)
+            elif wn.startswith("mvt"):
+                pe = bench.e2e_mvt(ww, o, s2, u2)
             per_config.append({"config": label, "workload": ww["desc"], "metric": m2,
                                "value": algorithmic_work(wn, ww) / (ms * 1e-3) / s2, "unit": u2,
                                "dtype": ww["dtype"], "steps": k, "ms_per_step": ms,
                                "gpu_launches": ln, "l2": l2_note(wn, ww), "roofline": rf,
-                               "clocks": ck})
+                               "clocks": ck, "e2e": pe})
             del o
             torch.cuda.empty_cache()
 

@@ -40,6 +40,8 @@
 // Every wait is time-bounded: on expiry the kernel records a code in the
 // host-visible status word, leaves its loops, frees its tensor memory and
 // returns.
+#include <stdlib.h>
+
 #include <vector>
 
 #include "pgb200_internal.h"
@@ -298,6 +300,11 @@ struct Tiles {
   int64_t kper;
   float *partial;
   int64_t ldp;
+  // Height of the bands the tile walk uses (tile rows; see TileCursor), and
+  // which operand's loads ask L2 to keep their lines longest (0 none, 1 B, 2 A):
+  // the panel that more of the tiles in flight share.
+  int band;
+  int keep;
   __device__ __forceinline__ int64_t first_kblock(int64_t tm) const {
     return a_upper ? (tm * bm) / BK : 0;
   }
@@ -324,10 +331,11 @@ __host__ __device__ __forceinline__ int64_t row_tiles(const Tiles &t, int64_t tm
 // tile indices only grow within a CTA, so the band position advances
 // monotonically.
 struct TileCursor {
-  static constexpr int64_t G = 16;
+  static constexpr int64_t G_DEFAULT = 16;
   int64_t band = 0, before = 0;  // tiles in bands < band (lower only)
   __host__ __device__ __forceinline__ void seek(const Tiles &t, int64_t idx, int64_t *otm,
                                                 int64_t *otn) {
+    const int64_t G = t.band > 0 ? t.band : G_DEFAULT;
     if (!t.lower) {
       const int64_t per_group = G * t.tiles_n;
       const int64_t grp = idx / per_group;
@@ -918,6 +926,31 @@ __device__ __forceinline__ void tma2_load_3d(uint32_t dst, const CUtensorMap *ma
       "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// The same loads with an L2 cache policy (createpolicy): lines of the panel that
+// most tiles in flight share are asked to be evicted last.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma2_load_2d_hint(uint32_t dst, const CUtensorMap *map,
+                                                  uint32_t leader_bar, int c0, int c1,
+                                                  uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(dst),
+      "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d_hint(uint32_t dst, const CUtensorMap *map,
+                                                  uint32_t leader_bar, int c0, int c1, int c2,
+                                                  uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(dst),
+      "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tc2_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                              uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -1042,6 +1075,7 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         const uint32_t leader_full0 = map_to_cta(full0, 0);
+        const uint64_t keep_policy = l2_policy_evict_last();
         TileCursor cur;
         for (int64_t it = A_UPPER ? 0 : pair; p2_more<A_UPPER>(sp, it, pair, npairs, total) && ok;
              it += A_UPPER ? 1 : npairs) {
@@ -1062,11 +1096,25 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
             // The same barrier in the leader CTA, as a cluster address.
             const uint32_t lbar = leader_full0 + 8 * stage;
             const int k0 = (int)(kb * BK);
-            tma2_load_2d(dst, &mapAhi, lbar, k0, row_a);
-            tma2_load_2d(dst + A_BYTES, &mapAlo, lbar, k0, row_a);
+            if (tiles.keep == 2) {
+              tma2_load_2d_hint(dst, &mapAhi, lbar, k0, row_a, keep_policy);
+              tma2_load_2d_hint(dst + A_BYTES, &mapAlo, lbar, k0, row_a, keep_policy);
+            } else {
+              tma2_load_2d(dst, &mapAhi, lbar, k0, row_a);
+              tma2_load_2d(dst + A_BYTES, &mapAlo, lbar, k0, row_a);
+            }
             if (B_MN) {
-              tma2_load_3d(dst + 2 * A_BYTES, &mapBhi, lbar, 0, k0, col_b / 32);
-              tma2_load_3d(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, 0, k0, col_b / 32);
+              if (tiles.keep == 1) {
+                tma2_load_3d_hint(dst + 2 * A_BYTES, &mapBhi, lbar, 0, k0, col_b / 32, keep_policy);
+                tma2_load_3d_hint(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, 0, k0, col_b / 32,
+                                  keep_policy);
+              } else {
+                tma2_load_3d(dst + 2 * A_BYTES, &mapBhi, lbar, 0, k0, col_b / 32);
+                tma2_load_3d(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, 0, k0, col_b / 32);
+              }
+            } else if (tiles.keep == 1) {
+              tma2_load_2d_hint(dst + 2 * A_BYTES, &mapBhi, lbar, k0, col_b, keep_policy);
+              tma2_load_2d_hint(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, k0, col_b, keep_policy);
             } else {
               tma2_load_2d(dst + 2 * A_BYTES, &mapBhi, lbar, k0, col_b);
               tma2_load_2d(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, k0, col_b);
@@ -1339,9 +1387,10 @@ tf32x3_gemm_fused_kernel(const __grid_constant__ CUtensorMap mapA,
   if (!tiles.lower) {
     // TileCursor::seek for a full product, on unsigned ints.
     const unsigned idx = (unsigned)t, tmn = (unsigned)tiles.tiles_m, tnn = (unsigned)tiles.tiles_n;
-    const unsigned per_group = (unsigned)TileCursor::G * tnn, grp = idx / per_group;
-    const unsigned first = grp * (unsigned)TileCursor::G;
-    const unsigned rows = tmn - first < (unsigned)TileCursor::G ? tmn - first : (unsigned)TileCursor::G;
+    const unsigned G = tiles.band > 0 ? (unsigned)tiles.band : (unsigned)TileCursor::G_DEFAULT;
+    const unsigned per_group = G * tnn, grp = idx / per_group;
+    const unsigned first = grp * G;
+    const unsigned rows = tmn - first < G ? tmn - first : G;
     const unsigned in = idx - grp * per_group;
     tm = first + in % rows;
     tn = in / rows;
@@ -1941,6 +1990,10 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   }
 
   Tiles tiles;
+  static const int exp_band = [] { const char *e = getenv("PGB200_EXP_BAND"); return e ? atoi(e) : 0; }();
+  static const int exp_keep = [] { const char *e = getenv("PGB200_EXP_KEEP"); return e ? atoi(e) : 0; }();
+  tiles.band = exp_band;
+  tiles.keep = exp_keep;
   tiles.tiles_m = (M + BM - 1) / BM;
   tiles.tiles_n = (N + bn - 1) / bn;
   tiles.bn = bn;
@@ -2009,11 +2062,12 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
       if (t2.total > pairs) {
         const int64_t nkb = (K + BK - 1) / BK;
         std::vector<int64_t> cost((size_t)t2.total);
-        const int64_t per_group = TileCursor::G * t2.tiles_n;
+        const int64_t G = t2.band > 0 ? t2.band : TileCursor::G_DEFAULT;
+        const int64_t per_group = G * t2.tiles_n;
         for (int64_t t = 0; t < t2.total; t++) {
-          const int64_t grp = t / per_group, first = grp * TileCursor::G;
+          const int64_t grp = t / per_group, first = grp * G;
           const int64_t rows =
-              (t2.tiles_m - first < TileCursor::G) ? (t2.tiles_m - first) : TileCursor::G;
+              (t2.tiles_m - first < G) ? (t2.tiles_m - first) : G;
           const int64_t tm = first + (t - grp * per_group) % rows;
           const int64_t len = nkb - (tm * 256) / BK;
           cost[(size_t)t] = (len > 0 ? len : 0) + 1;
