@@ -40,8 +40,6 @@
 // Every wait is time-bounded: on expiry the kernel records a code in the
 // host-visible status word, leaves its loops, frees its tensor memory and
 // returns.
-#include <stdlib.h>
-
 #include <vector>
 
 #include "pgb200_internal.h"
@@ -300,11 +298,12 @@ struct Tiles {
   int64_t kper;
   float *partial;
   int64_t ldp;
-  // Height of the bands the tile walk uses (tile rows; see TileCursor), and
-  // which operand's loads ask L2 to keep their lines longest (0 none, 1 B, 2 A):
-  // the panel that more of the tiles in flight share.
+  // Height of the bands the tile walk uses, in tile rows (0: the default of 16;
+  // see TileCursor).  Measured at 16384^3 and 32768^3: bands of 8, 16 and 32 rows,
+  // with and without an evict-last L2 policy on the loads of either operand,
+  // all gave the same time within run-to-run noise and DRAM traffic within
+  // +-10 %, so the walk is not what limits the large products.
   int band;
-  int keep;
   __device__ __forceinline__ int64_t first_kblock(int64_t tm) const {
     return a_upper ? (tm * bm) / BK : 0;
   }
@@ -926,31 +925,6 @@ __device__ __forceinline__ void tma2_load_3d(uint32_t dst, const CUtensorMap *ma
       "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
-// The same loads with an L2 cache policy (createpolicy): lines of the panel that
-// most tiles in flight share are asked to be evicted last.
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-__device__ __forceinline__ void tma2_load_2d_hint(uint32_t dst, const CUtensorMap *map,
-                                                  uint32_t leader_bar, int c0, int c1,
-                                                  uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(dst),
-      "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "l"(policy)
-      : "memory");
-}
-__device__ __forceinline__ void tma2_load_3d_hint(uint32_t dst, const CUtensorMap *map,
-                                                  uint32_t leader_bar, int c0, int c1, int c2,
-                                                  uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      ".L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(dst),
-      "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
-      : "memory");
-}
 __device__ __forceinline__ void tc2_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                              uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -1075,7 +1049,6 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         const uint32_t leader_full0 = map_to_cta(full0, 0);
-        const uint64_t keep_policy = l2_policy_evict_last();
         TileCursor cur;
         for (int64_t it = A_UPPER ? 0 : pair; p2_more<A_UPPER>(sp, it, pair, npairs, total) && ok;
              it += A_UPPER ? 1 : npairs) {
@@ -1096,25 +1069,11 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
             // The same barrier in the leader CTA, as a cluster address.
             const uint32_t lbar = leader_full0 + 8 * stage;
             const int k0 = (int)(kb * BK);
-            if (tiles.keep == 2) {
-              tma2_load_2d_hint(dst, &mapAhi, lbar, k0, row_a, keep_policy);
-              tma2_load_2d_hint(dst + A_BYTES, &mapAlo, lbar, k0, row_a, keep_policy);
-            } else {
-              tma2_load_2d(dst, &mapAhi, lbar, k0, row_a);
-              tma2_load_2d(dst + A_BYTES, &mapAlo, lbar, k0, row_a);
-            }
+            tma2_load_2d(dst, &mapAhi, lbar, k0, row_a);
+            tma2_load_2d(dst + A_BYTES, &mapAlo, lbar, k0, row_a);
             if (B_MN) {
-              if (tiles.keep == 1) {
-                tma2_load_3d_hint(dst + 2 * A_BYTES, &mapBhi, lbar, 0, k0, col_b / 32, keep_policy);
-                tma2_load_3d_hint(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, 0, k0, col_b / 32,
-                                  keep_policy);
-              } else {
-                tma2_load_3d(dst + 2 * A_BYTES, &mapBhi, lbar, 0, k0, col_b / 32);
-                tma2_load_3d(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, 0, k0, col_b / 32);
-              }
-            } else if (tiles.keep == 1) {
-              tma2_load_2d_hint(dst + 2 * A_BYTES, &mapBhi, lbar, k0, col_b, keep_policy);
-              tma2_load_2d_hint(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, k0, col_b, keep_policy);
+              tma2_load_3d(dst + 2 * A_BYTES, &mapBhi, lbar, 0, k0, col_b / 32);
+              tma2_load_3d(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, 0, k0, col_b / 32);
             } else {
               tma2_load_2d(dst + 2 * A_BYTES, &mapBhi, lbar, k0, col_b);
               tma2_load_2d(dst + 2 * A_BYTES + P2_B_BYTES, &mapBlo, lbar, k0, col_b);
@@ -1990,10 +1949,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   }
 
   Tiles tiles;
-  static const int exp_band = [] { const char *e = getenv("PGB200_EXP_BAND"); return e ? atoi(e) : 0; }();
-  static const int exp_keep = [] { const char *e = getenv("PGB200_EXP_KEEP"); return e ? atoi(e) : 0; }();
-  tiles.band = exp_band;
-  tiles.keep = exp_keep;
+  tiles.band = 0;
   tiles.tiles_m = (M + BM - 1) / BM;
   tiles.tiles_n = (N + bn - 1) / bn;
   tiles.bn = bn;
