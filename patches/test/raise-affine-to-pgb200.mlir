@@ -171,3 +171,125 @@ module {
 // CHECK:         affine.for
 // CHECK:           affine.for
 // CHECK-NOT:     call @pgb200
+
+// -----
+
+// The two nests of kernel_mvt
+// (tools/cgeist/Test/polybench/linear-algebra/kernels/mvt/mvt.c:102-109): both
+// accumulate into their result (no zero store -> beta = 1); the second walks A
+// by columns (A[j][i] -> transA = 1).
+module {
+  func.func @kernel_mvt(%arg0: i32, %arg1: memref<?xf64>, %arg2: memref<?xf64>, %arg3: memref<?xf64>, %arg4: memref<?xf64>, %arg5: memref<?x2000xf64>) {
+    %0 = arith.index_cast %arg0 : i32 to index
+    affine.for %arg6 = 0 to %0 {
+      affine.for %arg7 = 0 to %0 {
+        %1 = affine.load %arg1[%arg6] : memref<?xf64>
+        %2 = affine.load %arg5[%arg6, %arg7] : memref<?x2000xf64>
+        %3 = affine.load %arg3[%arg7] : memref<?xf64>
+        %4 = arith.mulf %2, %3 : f64
+        %5 = arith.addf %1, %4 : f64
+        affine.store %5, %arg1[%arg6] : memref<?xf64>
+      }
+    }
+    affine.for %arg6 = 0 to %0 {
+      affine.for %arg7 = 0 to %0 {
+        %1 = affine.load %arg2[%arg6] : memref<?xf64>
+        %2 = affine.load %arg5[%arg7, %arg6] : memref<?x2000xf64>
+        %3 = affine.load %arg4[%arg7] : memref<?xf64>
+        %4 = arith.mulf %2, %3 : f64
+        %5 = arith.addf %1, %4 : f64
+        affine.store %5, %arg2[%arg6] : memref<?xf64>
+      }
+    }
+    return
+  }
+}
+
+// CHECK-LABEL: func.func @kernel_mvt(
+// CHECK-SAME:    %{{.*}}: i32, %[[X1:.+]]: memref<?xf64>, %[[X2:.+]]: memref<?xf64>, %[[Y1:.+]]: memref<?xf64>, %[[Y2:.+]]: memref<?xf64>, %[[A:.+]]: memref<?x2000xf64>)
+// CHECK-NOT:     affine.for
+// CHECK:         %[[NOTRANS:.+]] = arith.constant 0 : i32
+// CHECK-DAG:     %[[PY1:.+]] = "polygeist.memref2pointer"(%[[Y1]])
+// CHECK-DAG:     %[[PX1:.+]] = "polygeist.memref2pointer"(%[[X1]])
+// CHECK:         call @pgb200Dgemv(%{{.*}}, %[[NOTRANS]], %{{.*}}, %{{.*}}, %{{.*}}, %{{.*}}, %{{.*}}, %[[PY1]], %{{.*}}, %[[PX1]])
+// CHECK-NOT:     affine.for
+// CHECK:         %[[TRANS:.+]] = arith.constant 1 : i32
+// CHECK-DAG:     %[[PY2:.+]] = "polygeist.memref2pointer"(%[[Y2]])
+// CHECK-DAG:     %[[PX2:.+]] = "polygeist.memref2pointer"(%[[X2]])
+// CHECK:         call @pgb200Dgemv(%{{.*}}, %[[TRANS]], %{{.*}}, %{{.*}}, %{{.*}}, %{{.*}}, %{{.*}}, %[[PY2]], %{{.*}}, %[[PX2]])
+// CHECK-NOT:     affine.for
+// CHECK:         return
+
+// -----
+
+// kernel_syrk (tools/cgeist/Test/polybench/linear-algebra/blas/syrk/syrk.c:97-106):
+// both inner loops run to j <= i, i.e. to #map(%i) with #map = (d0) -> (d0 + 1).
+// A nest with the same triangular bound that multiplies two different arrays
+// (the update of trmm / a triangular gemm) is not a rank-k update and stays.
+#map = affine_map<(d0) -> (d0 + 1)>
+module {
+  func.func @kernel_syrk(%arg0: i32, %arg1: i32, %arg2: f64, %arg3: f64, %arg4: memref<?x1200xf64>, %arg5: memref<?x1000xf64>) {
+    %0 = arith.index_cast %arg0 : i32 to index
+    %1 = arith.index_cast %arg1 : i32 to index
+    affine.for %arg6 = 0 to %0 {
+      affine.for %arg7 = 0 to #map(%arg6) {
+        %2 = affine.load %arg4[%arg6, %arg7] : memref<?x1200xf64>
+        %3 = arith.mulf %2, %arg3 : f64
+        affine.store %3, %arg4[%arg6, %arg7] : memref<?x1200xf64>
+      }
+      affine.for %arg7 = 0 to %1 {
+        affine.for %arg8 = 0 to #map(%arg6) {
+          %2 = affine.load %arg5[%arg6, %arg7] : memref<?x1000xf64>
+          %3 = arith.mulf %arg2, %2 : f64
+          %4 = affine.load %arg5[%arg8, %arg7] : memref<?x1000xf64>
+          %5 = arith.mulf %3, %4 : f64
+          %6 = affine.load %arg4[%arg6, %arg8] : memref<?x1200xf64>
+          %7 = arith.addf %6, %5 : f64
+          affine.store %7, %arg4[%arg6, %arg8] : memref<?x1200xf64>
+        }
+      }
+    }
+    return
+  }
+  func.func @triangular_product(%n: index, %beta: f64, %C: memref<?x64xf64>, %A: memref<?x64xf64>, %B: memref<?x64xf64>) {
+    affine.for %i = 0 to %n {
+      affine.for %j = 0 to #map(%i) {
+        %2 = affine.load %C[%i, %j] : memref<?x64xf64>
+        %3 = arith.mulf %2, %beta : f64
+        affine.store %3, %C[%i, %j] : memref<?x64xf64>
+      }
+      affine.for %k = 0 to %n {
+        affine.for %j = 0 to #map(%i) {
+          %2 = affine.load %A[%i, %k] : memref<?x64xf64>
+          %4 = affine.load %B[%k, %j] : memref<?x64xf64>
+          %5 = arith.mulf %2, %4 : f64
+          %6 = affine.load %C[%i, %j] : memref<?x64xf64>
+          %7 = arith.addf %6, %5 : f64
+          affine.store %7, %C[%i, %j] : memref<?x64xf64>
+        }
+      }
+    }
+    return
+  }
+}
+
+// CHECK:       func.func private @pgb200Dsyrk(!llvm.ptr, i64, i64, f64, !llvm.ptr, i64, f64, !llvm.ptr, i64) -> i32
+// CHECK-LABEL: func.func @kernel_syrk(
+// CHECK-SAME:    %[[NN:.+]]: i32, %[[NM:.+]]: i32, %[[ALPHA:.+]]: f64, %[[BETA:.+]]: f64, %[[C:.+]]: memref<?x1200xf64>, %[[A:.+]]: memref<?x1000xf64>)
+// CHECK-DAG:     %[[N:.+]] = arith.index_cast %[[NN]] : i32 to index
+// CHECK-DAG:     %[[K:.+]] = arith.index_cast %[[NM]] : i32 to index
+// CHECK-NOT:     affine.for
+// CHECK:         %[[STREAM:.+]] = llvm.mlir.zero : !llvm.ptr
+// CHECK-DAG:     %[[N64:.+]] = arith.index_cast %[[N]] : index to i64
+// CHECK-DAG:     %[[K64:.+]] = arith.index_cast %[[K]] : index to i64
+// CHECK-DAG:     %[[PA:.+]] = "polygeist.memref2pointer"(%[[A]]) : (memref<?x1000xf64>) -> !llvm.ptr
+// CHECK-DAG:     %[[PC:.+]] = "polygeist.memref2pointer"(%[[C]]) : (memref<?x1200xf64>) -> !llvm.ptr
+// CHECK-DAG:     %[[LDA:.+]] = arith.constant 1000 : i64
+// CHECK-DAG:     %[[LDC:.+]] = arith.constant 1200 : i64
+// CHECK:         call @pgb200Dsyrk(%[[STREAM]], %[[N64]], %[[K64]], %[[ALPHA]], %[[PA]], %[[LDA]], %[[BETA]], %[[PC]], %[[LDC]]) : (!llvm.ptr, i64, i64, f64, !llvm.ptr, i64, f64, !llvm.ptr, i64) -> i32
+// CHECK-NOT:     affine.for
+// CHECK:         return
+// CHECK-LABEL: func.func @triangular_product(
+// CHECK:         affine.for
+// CHECK:           affine.for
+// CHECK-NOT:     call @pgb200

@@ -32,7 +32,8 @@ def _prototype(name):
     return out
 
 
-@pytest.mark.parametrize("name", ["pgb200Dgemm", "pgb200Sgemm", "pgb200Dgemv"])
+@pytest.mark.parametrize("name", ["pgb200Dgemm", "pgb200Sgemm", "pgb200Dgemv", "pgb200Dsyrk",
+                                  "pgb200Ssyrk"])
 def test_emitted_calls_match_the_header_prototypes(name):
     """The type lists the pass declares (in the new .cpp inside the patch) and
     the lit test expects are those of the C prototypes."""
@@ -46,6 +47,13 @@ def test_emitted_calls_match_the_header_prototypes(name):
     if name in ("pgb200Dgemm", "pgb200Sgemm"):
         m = re.search(r"\{ptr, i64, i64, i64, fty, ptr, i64, ptr, i64, fty, ptr, i64\}", patch)
         assert m and [sym.get(t, t) for t in want] == "ptr i64 i64 i64 fty ptr i64 ptr i64 fty ptr i64".split()
+    elif name in ("pgb200Dsyrk", "pgb200Ssyrk"):
+        m = re.search(r"\{ptr, i64, i64, elt, ptr, i64, elt, ptr, i64\}", patch)
+        assert m and [{"f64": "elt", "f32": "elt", "!llvm.ptr": "ptr"}.get(t, t) for t in want] == \
+            "ptr i64 i64 elt ptr i64 elt ptr i64".split()
+        if name == "pgb200Dsyrk":
+            m = re.search(r"func\.func private @pgb200Dsyrk\(([^)]*)\) -> i32", lit)
+            assert [t.strip() for t in m.group(1).split(",")] == want
     else:
         m = re.search(r"\{ptr, i32, i64, i64, elt, ptr, i64, ptr, elt, ptr\}", patch)
         assert m and [{"f64": "elt", "!llvm.ptr": "ptr"}.get(t, t) for t in want] == \
