@@ -71,6 +71,11 @@ typedef struct pgb200Config {
   int32_t sgemm_b_in_place;   /* 1: fp32 row-major B always used in place,
                                  whatever M (default: transposed once into
                                  K-major planes for tall products)             */
+  int32_t no_step_sync;       /* 1: the CTAs of the two-CTA fp32 kernel do not
+                                 meet between rounds of tiles (default: they
+                                 do, which keeps the CTAs that share an operand
+                                 panel close together in K so that one DRAM
+                                 read serves all of them)                      */
 } pgb200Config;
 
 /* Runtime life cycle.  Replaces nothing in the reference one-to-one; plays the

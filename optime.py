@@ -43,11 +43,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--back-to-back", action="store_true",
                     help="time all iterations with one event pair, no L2 flush (launch-bound sizes)")
+    ap.add_argument("--no-step-sync", action="store_true",
+                    help="pgb200Config.no_step_sync = 1 (two-CTA fp32 kernel without the meeting between rounds)")
     a = ap.parse_args()
 
     import torch
 
     import polygeist_b200 as pgb
+
+    if a.no_step_sync:
+        pgb.init(no_step_sync=1)
 
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)

@@ -35,7 +35,8 @@ class Config(C.Structure):
     _fields_ = [("log_level", C.c_int32), ("sgemm_chunk_kblocks", C.c_int32),
                 ("force_generic", C.c_int32), ("sgemm_planes_only", C.c_int32),
                 ("reserve_sms", C.c_int32), ("no_two_cta", C.c_int32),
-                ("no_split_k", C.c_int32), ("sgemm_b_in_place", C.c_int32)]
+                ("no_split_k", C.c_int32), ("sgemm_b_in_place", C.c_int32),
+                ("no_step_sync", C.c_int32)]
 
 
 _i32, _i64, _vp, _f64, _f32 = C.c_int32, C.c_int64, C.c_void_p, C.c_double, C.c_float
@@ -131,9 +132,9 @@ def check(status):
 
 
 def init(log_level=0, sgemm_chunk_kblocks=0, force_generic=0, sgemm_planes_only=0, reserve_sms=0,
-         no_two_cta=0, no_split_k=0, sgemm_b_in_place=0):
+         no_two_cta=0, no_split_k=0, sgemm_b_in_place=0, no_step_sync=0):
     cfg = Config(log_level, sgemm_chunk_kblocks, force_generic, sgemm_planes_only, reserve_sms,
-                 no_two_cta, no_split_k, sgemm_b_in_place)
+                 no_two_cta, no_split_k, sgemm_b_in_place, no_step_sync)
     check(load().pgb200Init(C.byref(cfg)))
 
 

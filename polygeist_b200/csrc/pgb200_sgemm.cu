@@ -59,6 +59,7 @@ constexpr int FIRST_EPI_WARP = 4;                         // warps 0-3: producer
 constexpr int THREADS = 32 * (FIRST_EPI_WARP + EPI_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_CYCLES = 4000000000ll;           // ~2 s
+constexpr long long STEP_WAIT_MIN = 200000ll;             // ~0.1 ms: least patience of the meeting between rounds
 constexpr int DEFAULT_CHUNK_KBLOCKS = 8;                  // 128 K-elements
 
 // ------------------------------------------------------------------ PTX helpers
@@ -118,6 +119,54 @@ __device__ __forceinline__ void report_status(int32_t *status, int32_t code, int
   s[0] = code;
   __threadfence_system();
 }
+// The TMA producers of a persistent grid meet between rounds of tiles (round r
+// = tiles [r * CTAs, (r + 1) * CTAs) of the walk).  The tiles of a round share
+// their A and B panels, and a panel (rows x K x hi+lo) is far larger than L2,
+// so a CTA only finds a panel's lines in L2 while it walks K close behind the
+// CTA that fetched them.  Left alone the CTAs drift apart over the rounds and
+// most panel reads go to DRAM again (fp32 16384^3: 79-86 GB read against 44 GB
+// with the meeting, which is what 74 tiles in step need); at the power cap the
+// saved DRAM energy is SM clock (fp32 32768^3: 1155 -> 1455 MHz, 319 -> 268 ms).
+// Each producer adds one to a zeroed counter when the loads of its tile are
+// issued and waits for CTAs * r before round r.  The meeting is only a hint: a
+// producer that has waited as long as a whole tile took (the CTAs of the grid
+// are not all running, e.g. another kernel holds some SMs) stops meeting and
+// goes on alone; the product is the same either way.
+struct RoundMeeting {
+  int32_t *ctr;
+  bool waits;
+  int32_t round;
+  long long t_begin, tile_cycles;
+  __device__ __forceinline__ void init(int32_t *counter) {
+    ctr = counter;
+    waits = counter != nullptr;
+    round = 0;
+    t_begin = 0;
+    tile_cycles = 0;
+  }
+  __device__ __forceinline__ void before_tile() {
+    if (ctr == nullptr) return;
+    t_begin = clock64();
+    if (waits && round > 0) {
+      const int32_t want = (int32_t)gridDim.x * round;
+      const volatile int32_t *c = ctr;
+      const long long limit = tile_cycles > STEP_WAIT_MIN ? tile_cycles : STEP_WAIT_MIN;
+      while (*c < want) {
+        if (clock64() - t_begin > limit) {
+          waits = false;
+          break;
+        }
+        __nanosleep(100);
+      }
+    }
+  }
+  __device__ __forceinline__ void after_tile() {
+    if (ctr == nullptr) return;
+    atomicAdd(ctr, 1);
+    tile_cycles = clock64() - t_begin;
+    round++;
+  }
+};
 // Pulls a tensor map into the descriptor cache ahead of its first use.
 __device__ __forceinline__ void prefetch_tensor_map(const CUtensorMap *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -304,6 +353,9 @@ struct Tiles {
   // all gave the same time within run-to-run noise and DRAM traffic within
   // +-10 %, so the walk is not what limits the large products.
   int band;
+  // Products with more tiles than CTAs and a long K: the zeroed counter of the
+  // meeting between rounds of tiles (see RoundMeeting); null: no meeting.
+  int32_t *step_ctr;
   __device__ __forceinline__ int64_t first_kblock(int64_t tm) const {
     return a_upper ? (tm * bm) / BK : 0;
   }
@@ -455,12 +507,15 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
       TileCursor cur;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      RoundMeeting meeting;
+      meeting.init(SPLITK ? nullptr : tiles.step_ctr);
       for (int64_t w = blockIdx.x; w < work && ok; w += gridDim.x) {
         const int64_t t = SPLITK ? w / tiles.splits : w;
         const int64_t kb_lo = SPLITK ? (w % tiles.splits) * tiles.kper : 0;
         const int64_t kb_hi = SPLITK ? (kb_lo + tiles.kper < nkb ? kb_lo + tiles.kper : nkb) : nkb;
         int64_t tm, tn;
         cur.seek(tiles, t, &tm, &tn);
+        meeting.before_tile();
         for (int64_t kb = kb_lo; kb < kb_hi; kb++) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) {
             report_status(status, 11, (int32_t)blockIdx.x);
@@ -495,6 +550,7 @@ tf32x3_gemm_kernel(const __grid_constant__ CUtensorMap mapAhi,
             phase ^= 1;
           }
         }
+        meeting.after_tile();
       }
     }
   } else if (warp == 1) {
@@ -1050,10 +1106,13 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
         bool ok = true;
         const uint32_t leader_full0 = map_to_cta(full0, 0);
         TileCursor cur;
+        RoundMeeting meeting;
+        meeting.init(A_UPPER ? nullptr : tiles.step_ctr);
         for (int64_t it = A_UPPER ? 0 : pair; p2_more<A_UPPER>(sp, it, pair, npairs, total) && ok;
              it += A_UPPER ? 1 : npairs) {
           const int64_t t = p2_tile<A_UPPER>(sp, tiles, it, pair, npairs, total);
           if (A_UPPER && t < 0) continue;
+          meeting.before_tile();
           int64_t tm2, tn;
           cur.seek(tiles, t, &tm2, &tn);
           const int row_a = (int)(tm2 * 256 + rank * 128);
@@ -1083,6 +1142,7 @@ tf32x3_gemm_2cta_kernel(const __grid_constant__ CUtensorMap mapAhi,
               phase ^= 1;
             }
           }
+          meeting.after_tile();
         }
       }
     } else if (warp == 1 && rank == 0) {
@@ -1867,13 +1927,15 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   const size_t a_lo_n = shared_planes ? 0 : (size_t)M * Kp;
   const size_t a_hi_n = (shared_planes || a_raw) ? 0 : (size_t)M * Kp;
   PoolBuffer scratch;  // this call's own planes and partial products, released in stream order
-  PGB_CUDA(scratch.alloc((b_lo_n + b_hi_n + a_lo_n + a_hi_n + part_n) * sizeof(float), s));
+  const size_t ctr_n = 64;  // the two-CTA kernel's round counter, on a line of its own
+  PGB_CUDA(scratch.alloc((b_lo_n + b_hi_n + a_lo_n + a_hi_n + part_n + ctr_n) * sizeof(float), s));
   void *ws = scratch.ptr;
   float *Blo = static_cast<float *>(ws);
   float *Bhi_pl = Blo + b_lo_n;
   float *Alo_pl = Bhi_pl + b_hi_n;
   float *Ahi_pl = Alo_pl + a_lo_n;
   float *partial = Ahi_pl + a_hi_n;
+  int32_t *step_ctr = reinterpret_cast<int32_t *>(partial + part_n);
 
   const int64_t cap = (int64_t)rt->num_sms * 8;
   auto grid_for = [&](int64_t total) {
@@ -1950,6 +2012,7 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
 
   Tiles tiles;
   tiles.band = 0;
+  tiles.step_ctr = nullptr;
   tiles.tiles_m = (M + BM - 1) / BM;
   tiles.tiles_n = (N + bn - 1) / bn;
   tiles.bn = bn;
@@ -1966,6 +2029,10 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
   if (ctas < 1) ctas = 1;
   const int64_t work = tiles.total * splits;
   const unsigned grid = (unsigned)(work < ctas ? work : ctas);
+  // Meeting between rounds of tiles: measured (8192 x 8192 and 16384 x 16384
+  // by K) it costs 3-5 % at K = 512, nothing at 1024-2048 and gains from there
+  // on (16384 x 32768 x 2048: 7.74 vs 7.97 ms; 32768^3: 268 vs 319 ms).
+  const bool meet_k = K >= 2048 && !rt->cfg.no_step_sync;
   // Large full products: the two-CTA kernel (256x256 tiles on SM pairs).
   // Measured against the one-CTA kernel: 8192^3 4.01-4.18 vs 4.45 ms, 16384^3
   // 36.7-38.1 vs 40.5-40.8 ms, 32768^3 354-356 vs 423-443 ms (same GPU, back to
@@ -1992,6 +2059,10 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     int64_t pairs = t2.total;
     const int64_t max_pairs = ctas / 2 > 0 ? ctas / 2 : 1;
     if (pairs > max_pairs) pairs = max_pairs;
+    if (!t2.a_upper && t2.total > pairs && meet_k) {
+      PGB_CUDA(cudaMemsetAsync(step_ctr, 0, sizeof(int32_t), s));
+      t2.step_ctr = step_ctr;
+    }
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
     lc.blockDim = dim3(THREADS, 1, 1);
@@ -2040,6 +2111,10 @@ int32_t tf32x3_gemm(cudaStream_t s, int64_t M, int64_t N, int64_t K, float alpha
     note_launch(PATH_TCGEN05);
     PGB_CUDA(cudaGetLastError());
     return PGB200_OK;
+  }
+  if (splits == 1 && tiles.total > (int64_t)grid && meet_k) {
+    PGB_CUDA(cudaMemsetAsync(step_ctr, 0, sizeof(int32_t), s));
+    tiles.step_ctr = step_ctr;
   }
   auto launch = [&](auto kernel, int bhi_blk) -> int32_t {
     PGB_TRY(ensure_dynamic_smem((const void *)kernel, SMEM_BYTES));

@@ -427,6 +427,48 @@ def test_sgemm_split_k(M, N, K, beta):
     assert elementwise_rel(got, unsplit) <= 1e-5
 
 
+@pytest.mark.parametrize("M,N,K", [(2560, 2304, 2048), (2048, 2832, 2048)])
+def test_sgemm_round_meeting_changes_no_bit(M, N, K):
+    """More tiles than CTAs and K >= 2048: the TMA producers of the persistent
+    fp32 kernels meet between rounds of tiles so that CTAs sharing an operand
+    panel stay close in K (two-CTA kernel: 10 x 9 pair tiles on 74 pairs;
+    one-CTA kernel, N % 32 != 0: 16 x 12 tiles on 148 CTAs).  The meeting only
+    changes when loads are issued: the bits are those of a run with
+    pgb200Config.no_step_sync, also when two such products run at once on two
+    streams (the CTAs of the second grid cannot all be running, so its
+    producers give the meeting up), and they match the fp64-accumulated product."""
+    A = dev_fill(M, K, torch.float32, 1, 0.0, 1.0)
+    B = dev_fill(K, N, torch.float32, 2, 0.0, 1.0)
+    C0 = dev_fill(M, N, torch.float32, 3, 0.0, 1.0)
+
+    def run():
+        Cm = C0.clone()
+        pgb.gemm(1.5, A, B, 1.2, Cm)
+        sync_ok()
+        return Cm
+
+    met = run()
+    assert pgb.last_path() == pgb.PATH_TCGEN05
+    pgb.init(no_step_sync=1)
+    try:
+        alone = run()
+    finally:
+        pgb.init()
+    assert torch.equal(met, alone)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    C1, C2 = C0.clone(), C0.clone()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s1):
+        pgb.gemm(1.5, A, B, 1.2, C1)
+    with torch.cuda.stream(s2):
+        pgb.gemm(1.5, A, B, 1.2, C2)
+    sync_ok()
+    assert torch.equal(C1, met) and torch.equal(C2, met)
+    hA, hB, hC = (t.cpu().numpy().astype(np.float64) for t in (A, B, C0))
+    truth = 1.5 * (hA @ hB) + 1.2 * hC
+    assert elementwise_rel(met.cpu().numpy(), truth) <= 1e-5
+
+
 @pytest.mark.parametrize("M,N,K,beta", [(200, 300, 400, 1.0), (100, 300, 200, 0.0)])
 def test_sgemm_plain_matmul_nests(M, N, K, beta):
     """The two fp32 matmul nests of the reference's raise-to-affine test
