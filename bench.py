@@ -50,8 +50,12 @@ PER_CONFIG = [("configs[0]", "sgemm1024"), ("configs[1]", "dgemm4096"), ("config
 
 # DRAM bytes (read + write) per launch of the dominant kernel from the ncu
 # captures summarised under profiles/ (mvt32768: the N=16384 capture x 4;
-# sgemm32768: the 4096^3 capture does not scale linearly, so none is given).
-TRAFFIC = {"dgemm4096": 1.1345e9, "mvt16384": 2.156e9, "mvt32768": 8.624e9, "sgemm4096": 8.31e8}
+# sgemm32768: the 16384^3 capture, 45.07 GB, x 8 - with the producers meeting
+# between rounds of tiles the traffic is rounds x panels x panel bytes, i.e.
+# proportional to tiles x K: 8192^3 5.94 GB, 16384^3 45.07 GB.  One-GPU launch
+# only; the row-block launches of a multi-GPU run were not captured).
+TRAFFIC = {"dgemm4096": 1.1345e9, "mvt16384": 2.156e9, "mvt32768": 8.624e9, "sgemm4096": 8.31e8,
+           "sgemm8192": 5.94e9, "sgemm32768": 3.606e11}
 
 WORKLOADS = {
     "dgemm4096": dict(dtype="f64", M=4096, N=4096, K=4096, lo=-1.0, hi=1.0,
@@ -598,7 +602,8 @@ class Bench:
         if lib and "burst_tflops" in lib:
             lib_peak = lib["sustained_tflops"] if capped else lib["burst_tflops"]
         return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                "frac": ach / peak, "frac_of_burst": ach / burst, "traffic": TRAFFIC.get(name),
+                "frac": ach / peak, "frac_of_burst": ach / burst,
+                "traffic": TRAFFIC.get(name) if world == 1 else None,
                 "peak_burst": burst, "peak_after_run": peak_hot,
                 "peak_source": "dense TF32 tcgen05.mma issue-rate probe of this library "
                                "(MEASURED_PEAKS.json has no TF32 figure): "
