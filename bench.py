@@ -9,7 +9,9 @@ fits one GPU - fp32 GEMM C = alpha*A*B + beta*C, M=N=K=32768, inputs uniform
 [0,1) from a seed, alpha=1.5, beta=1.2, on the 3xTF32 tensor path.  With N>1
 ranks (torchrun) the rows of A and C are partitioned across the ranks (strong
 scaling: total work fixed) and the shared operand B is broadcast from rank 0
-by NCCL inside every step, K-chunked so that the transfer overlaps the product.
+inside every step, in K-slices, so that the transfer overlaps the product: by
+the copy engines over peer-mapped memory (no SMs; `broadcast` in the line says
+which route ran), else by NCCL.
 
 `value`   device-resident throughput, CUDA events on the launching stream.
 `e2e`     same metric through the reference-facing drop-in (pgb200_kernel_gemm
@@ -68,10 +70,10 @@ WORKLOADS = {
                       desc="fp32 GEMM 8192^3 (3xTF32), uniform [0,1)"),
     "sgemm32768": dict(dtype="f32", M=32768, N=32768, K=32768, lo=0.0, hi=1.0, strong=True,
                        desc="configs[4]b: fp32 GEMM 32768^3 (3xTF32), uniform [0,1), alpha=1.5 beta=1.2; "
-                            "rows partitioned across the GPUs, B broadcast by NCCL"),
+                            "rows partitioned across the GPUs, B broadcast from rank 0 in every step"),
     "ssyrk16384": dict(dtype="f32", N=16384, K=8192, lo=0.0, hi=1.0, strong=True,
                        desc="configs[4]a: fp32 SYRK N=16384 K=8192 lower (3xTF32), uniform [0,1), rows "
-                            "partitioned by equal triangular area, A broadcast by NCCL"),
+                            "partitioned by equal triangular area, A broadcast from rank 0 in every step"),
     "mvt16384": dict(dtype="f64", N=16384, lo=0.0, hi=1.0,
                      desc="fp64 mat-vec pair, N=16384 (2.1 GB; the profiling-size case of configs[2])"),
     "mvt32768": dict(dtype="f64", N=32768, lo=0.0, hi=1.0,
@@ -244,7 +246,7 @@ def config_of(name, w, world):
     """The `config` object of the JSON line; both arms print the same one."""
     return {"workload": w["desc"], "l2": l2_note(name, w),
             "parallelism": ("single GPU" if world == 1 else
-                            f"{world} row blocks, shared operand broadcast by NCCL each step")}
+                            f"{world} row blocks, shared operand broadcast from rank 0 each step")}
 
 
 def measured_peaks():
@@ -422,6 +424,8 @@ class Bench:
         if self.world > 1:
             dist.init_process_group("nccl", device_id=self.dev)
         self.flush = None
+        self.broadcast = None        # route of the shared operand in a multi-GPU strong run
+        self.broadcast_note = None   # why the copy-engine route was not taken, if so
         self.peaks = measured_peaks()
 
     def barrier(self):
@@ -431,6 +435,63 @@ class Bench:
 
     def tdt(self, w):
         return self.torch.float64 if w["dtype"] == "f64" else self.torch.float32
+
+    def peer_broadcast(self, w, K, N):
+        """The shared operand in symmetric memory (every rank's copy mapped into
+        every process) and a PeerPullBroadcast over it, or None when that cannot
+        be set up here (the step then uses the NCCL broadcast).  All ranks take
+        the same branch: the outcome is agreed on with an all-reduce."""
+        torch, dist, partition = self.torch, self.dist, self.partition
+        self.broadcast_note = None
+        if os.environ.get("PGB_BENCH_BCAST", "peer") == "nccl":
+            return None
+        peer, err = None, None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            dt = self.tdt(w)
+            buf = symm_mem.empty((K, N), dtype=dt, device=self.dev)
+            hb = symm_mem.rendezvous(buf, dist.group.WORLD)
+            views = [hb.get_buffer(r, (K, N), dt) for r in range(self.world)]
+            flags, memops, fl, hf = None, None, None, None
+            if self.world > 2:
+                slots = 64
+                fl = symm_mem.empty((self.world, slots), dtype=torch.int32, device=self.dev)
+                fl.zero_()
+                hf = symm_mem.rendezvous(fl, dist.group.WORLD)
+                flags = [hf.get_buffer(r, (self.world, slots), torch.int32) for r in range(self.world)]
+                memops = partition.stream_memops()
+            peer = partition.PeerPullBroadcast(torch, dist, views, src=0, flags=flags, memops=memops)
+            self._symm = (buf, hb, fl, hf)   # the allocations must outlive the mapped views
+        except Exception as e:          # noqa: BLE001 - any failure means "use NCCL"
+            err = repr(e)
+        ok = torch.tensor([0 if peer is None else 1], dtype=torch.int32, device=self.dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        torch.cuda.synchronize()
+        if int(ok.item()) == 0:
+            self.broadcast_note = err or "a peer could not map the operand"
+            return None
+        return peer
+
+    def check_broadcast(self, plan, A, B, Cm):
+        """One untimed step on poisoned receive buffers: afterwards every rank's
+        copy of the shared operand must equal the source's bit for bit (sum of
+        the words as integers, compared across ranks), and C is restored."""
+        torch, dist = self.torch, self.dist
+        keep = Cm.clone()
+        if self.rank != 0:
+            B.fill_(float("nan"))
+        self.barrier()
+        plan.run(ALPHA, A, B, BETA, Cm)
+        torch.cuda.synchronize()
+        words = B.view(torch.int32)
+        sums = torch.stack([words[i::8].sum(dtype=torch.int64) for i in range(8)])
+        lo, hi = sums.clone(), sums.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if not bool(torch.equal(lo, hi)):
+            raise RuntimeError(f"rank {self.rank}: the broadcast operand differs between the ranks")
+        Cm.copy_(keep)
+        self.barrier()
 
     def filled(self, w, rows, cols, aid, row0=0):
         t = self.torch.empty((rows, cols), dtype=self.tdt(w), device=self.dev)
@@ -488,8 +549,14 @@ class Bench:
                 r0, r1 = rank * M, (rank + 1) * M
             A = self.filled(w, r1 - r0, K, 1, row0=r0)
             Cm = self.filled(w, r1 - r0, N, 3, row0=r0)
-            B = self.filled(w, K, N, 2) if rank == 0 else torch.empty((K, N), dtype=self.tdt(w),
-                                                                      device=self.dev)
+            peer = self.peer_broadcast(w, K, N) if (world > 1 and strong) else None
+            if peer is not None:
+                B = peer.views[rank]
+                if rank == 0:
+                    pgb.fill_uniform(B, SEED, 2, w["lo"], w["hi"])
+            else:
+                B = self.filled(w, K, N, 2) if rank == 0 else torch.empty(
+                    (K, N), dtype=self.tdt(w), device=self.dev)
             ops.update(A=A, B=B, C=Cm)
             if world > 1:
                 # Large shared operand: K-chunks that overlap the chunk products.
@@ -499,7 +566,12 @@ class Bench:
                 dflt = K // 16 if strong else K
                 plan = partition.PartitionedGemm(
                     dist, pgb.gemm, src=0, chunk=int(os.environ.get("PGB_BENCH_KCHUNK", dflt)),
-                    first_chunk=int(os.environ.get("PGB_BENCH_KFIRST", 0)))
+                    first_chunk=int(os.environ.get("PGB_BENCH_KFIRST", 0)),
+                    grow=os.environ.get("PGB_BENCH_KGROW", "1") != "0", peer_broadcast=peer)
+                self.broadcast = ("copy engines over peer-mapped memory, stream-ordered signals"
+                                  if peer is not None else "nccl")
+                if strong:
+                    self.check_broadcast(plan, A, B, Cm)
 
                 def step():
                     plan.run(ALPHA, A, B, BETA, Cm)
@@ -832,6 +904,10 @@ def run_pgb200(args, w, name):
         }
         if per_config is not None:
             line["per_config"] = per_config
+        if bench.broadcast is not None:
+            line["broadcast"] = bench.broadcast
+            if bench.broadcast_note:
+                line["broadcast_note"] = bench.broadcast_note
         print(json.dumps(line))
     if world > 1:
         bench.dist.destroy_process_group()

@@ -51,6 +51,27 @@ def k_chunks(K, chunk, first=0):
     return head + [(k0, min(K, k0 + chunk)) for k0 in range(start, K, chunk)] or [(0, 0)]
 
 
+def slice_groups(nslices, grow=True):
+    """Groups of consecutive K-slices that are multiplied by one product each:
+    [first, last) index pairs of sizes 1, 1, 2, 4, 8, ... (the last one takes
+    what is left).  The slices travel one by one, so the first product starts
+    as soon as one slice has landed; a product of few long-K calls is faster
+    than one of many short ones (fp32 32768^3 on one GPU: 16 slices of 2048
+    cost 9 % over the unsliced product, 4 of 8192 cost 3 %), and the transfer
+    is several times faster than the product, so the later, longer groups
+    have landed long before they are needed.  grow=False: one slice per group."""
+    if not grow:
+        return [(i, i + 1) for i in range(nslices)]
+    groups, start, size = [], 0, 1
+    while start < nslices:
+        end = min(nslices, start + size)
+        groups.append((start, end))
+        if len(groups) >= 2:
+            size *= 2
+        start = end
+    return groups
+
+
 def pull_plan(rank, world, src, k0, k1):
     """Copy-engine broadcast of rows [k0,k1) from `src`, as pulls by `rank`.
 
@@ -73,41 +94,141 @@ def pull_plan(rank, world, src, k0, k1):
     return p1, p2
 
 
+def pull_schedule(rank, world, src, chunks):
+    """The copy-engine broadcast of all K-slices as one ordered list of
+    operations for `rank`'s copy stream:
+
+      ("pull", peer, r0, r1)  copy rows [r0,r1) from `peer`'s buffer into mine
+      ("signal", c)           tell the other non-source ranks that my piece of
+                              slice c has landed (after the phase-1 pull; the
+                              source has no piece and skips it)
+      ("wait", peer, c)       wait until `peer` has signalled slice c (before
+                              pulling its piece)
+      ("ready", c)            slice c is complete here: record its event
+
+    No rank ever waits for something that comes later in the signaller's own
+    list than an operation that waits for this rank, so the lists cannot
+    deadlock (checked by simulation in the tests)."""
+    ops = []
+    for c, (k0, k1) in enumerate(chunks):
+        p1, p2 = pull_plan(rank, world, src, k0, k1)
+        for peer, r0, r1 in p1:
+            ops.append(("pull", peer, r0, r1))
+        if world > 2:
+            ops.append(("signal", c))     # the source has nothing to signal: phase boundary only
+        for peer, r0, r1 in p2:
+            ops.append(("wait", peer, c))
+            ops.append(("pull", peer, r0, r1))
+        ops.append(("ready", c))
+    return ops
+
+
+def stream_memops():
+    """(write_value, wait_value): 32-bit stream memory operations of the CUDA
+    driver through cuda-python.  write_value(stream, ptr, v) stores v at ptr in
+    stream order; wait_value(stream, ptr, v) holds the stream until the word at
+    ptr is >= v.  Neither launches a kernel, so they make progress while
+    persistent kernels hold every SM."""
+    from cuda.bindings import driver
+
+    def check(ret, what):
+        err = ret[0] if isinstance(ret, tuple) else ret
+        if err != driver.CUresult.CUDA_SUCCESS:
+            raise RuntimeError(f"{what} failed with {err}")
+
+    geq = int(driver.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_GEQ)
+
+    def write_value(stream, ptr, value):
+        check(driver.cuStreamWriteValue32(driver.CUstream(stream), driver.CUdeviceptr(ptr),
+                                          int(value), 0), "cuStreamWriteValue32")
+
+    def wait_value(stream, ptr, value):
+        check(driver.cuStreamWaitValue32(driver.CUstream(stream), driver.CUdeviceptr(ptr),
+                                         int(value), geq), "cuStreamWaitValue32")
+
+    return write_value, wait_value
+
+
 class PeerPullBroadcast:
     """Broadcast of the shared operand by peer-to-peer copies (DMA engines, no
     SMs), so the transfer does not compete with the persistent GEMM kernels the
-    way a collective kernel does.  `views[r]` is rank r's buffer mapped into
-    this process (torch symmetric memory); copies run on a private stream and
-    one event per K-chunk tells the compute stream when its rows have landed.
-    A one-element all-reduce on the same stream is the device-side barrier
-    between the two phases of pull_plan()."""
+    way a collective kernel does: those kernels fill the register file of every
+    SM, a collective's CTAs only run between two of them, and the broadcast ends
+    up in series with the products (measured at 2 GPUs, fp32 32768^3: 160 ms per
+    step with the NCCL broadcast against 139 ms for the products alone).
 
-    def __init__(self, torch, dist, views, src=0, group=None):
+    `views[r]` is rank r's buffer mapped into this process (torch symmetric
+    memory); copies run on a private stream and one event per K-slice tells the
+    compute stream when its rows have landed.  One small all-reduce per call on
+    that stream (it runs before the first product, when the GPU is idle) keeps
+    any rank from overwriting rows a peer may still be reading.
+
+    Between the two phases of pull_plan() a rank must know that the owner of a
+    piece has received it.  With `flags` (flags[r] = rank r's int32 [world,
+    slots] array, mapped like `views`) and `memops` (see stream_memops) this is
+    a word per (owner, slice) that the owner sets to the call number in every
+    peer's array after its phase-1 copy - a 4-byte copy in stream order (the
+    driver refuses a stream memory operation that writes a peer-mapped word:
+    CUDA_ERROR_INVALID_VALUE) - and that the peer's copy stream waits for with
+    a stream memory operation on its own memory: no kernel at all.  Without them an all-reduce per slice is the barrier (its
+    kernel waits for the running product)."""
+
+    def __init__(self, torch, dist, views, src=0, group=None, flags=None, memops=None):
         self.torch, self.dist, self.views, self.src, self.group = torch, dist, views, src, group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.stream = torch.cuda.Stream()
         self.flag = torch.zeros(1, device=views[self.rank].device)
+        self.flags = flags
+        self.memops = memops if flags is not None else None
+        self.call = 0
+        self._numbers = None          # device words 1, 2, 3, ...: sources of the signal copies
+        self._numbers_base = 0
+
+    def _number(self, value):
+        """A one-element device tensor holding `value` (a call number)."""
+        torch = self.torch
+        if self._numbers is None or not (self._numbers_base <= value < self._numbers_base + 4096):
+            self._numbers_base = value
+            self._numbers = torch.arange(value, value + 4096, dtype=torch.int32,
+                                         device=self.views[self.rank].device)
+        i = value - self._numbers_base
+        return self._numbers[i:i + 1]
 
     def start(self, chunks):
         torch, dist = self.torch, self.dist
         mine = self.views[self.rank]
+        signalled = self.flags is not None and self.world > 2
+        if signalled and len(chunks) > self.flags[self.rank].shape[1]:
+            raise ValueError("more K-slices than signal slots")
+        self.call += 1
+        number = self._number(self.call) if signalled else None
         self.stream.wait_stream(torch.cuda.current_stream())
         events = []
         with torch.cuda.stream(self.stream):
             # Nobody overwrites its buffer while a peer may still be reading it.
             dist.all_reduce(self.flag, group=self.group)
-            for k0, k1 in chunks:
-                p1, p2 = pull_plan(self.rank, self.world, self.src, k0, k1)
-                for peer, r0, r1 in p1:
+            handle = self.stream.cuda_stream
+            for op in pull_schedule(self.rank, self.world, self.src, chunks):
+                if op[0] == "pull":
+                    _, peer, r0, r1 = op
                     mine[r0:r1].copy_(self.views[peer][r0:r1], non_blocking=True)
-                if self.world > 2:
-                    dist.all_reduce(self.flag, group=self.group)
-                for peer, r0, r1 in p2:
-                    mine[r0:r1].copy_(self.views[peer][r0:r1], non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record(self.stream)
-                events.append(ev)
+                elif op[0] == "signal":
+                    if not signalled:
+                        dist.all_reduce(self.flag, group=self.group)
+                    elif self.rank != self.src:
+                        for q in range(self.world):
+                            if q == self.rank or q == self.src:
+                                continue
+                            self.flags[q][self.rank, op[1]:op[1] + 1].copy_(number, non_blocking=True)
+                elif op[0] == "wait":
+                    if signalled:
+                        word = self.flags[self.rank][op[1], op[2]:op[2] + 1]
+                        self.memops[1](handle, word.data_ptr(), self.call)
+                else:
+                    ev = torch.cuda.Event()
+                    ev.record(self.stream)
+                    events.append(ev)
         return events
 
 
@@ -120,12 +241,13 @@ class PartitionedGemm:
     """
 
     def __init__(self, dist, compute, src=0, chunk=1024, group=None, peer_broadcast=None,
-                 first_chunk=0):
+                 first_chunk=0, grow=True):
         self.dist = dist
         self.compute = compute
         self.src = src
         self.chunk = chunk
         self.first_chunk = first_chunk
+        self.grow = grow                      # slice_groups(): longer products as the run goes on
         self.group = group
         self.peer_broadcast = peer_broadcast  # PeerPullBroadcast, or None for NCCL
 
@@ -141,8 +263,9 @@ class PartitionedGemm:
             pb = self.peer_broadcast
             events = pb.start(chunks)
             first = True
-            for (k0, k1), ev in zip(chunks, events):
-                pb.torch.cuda.current_stream().wait_event(ev)
+            for g0, g1 in slice_groups(len(chunks), self.grow):
+                pb.torch.cuda.current_stream().wait_event(events[g1 - 1])  # slices land in order
+                k0, k1 = chunks[g0][0], chunks[g1 - 1][1]
                 self.compute(alpha, A_p[:, k0:k1], B_local[k0:k1], beta if first else 1.0, C_p)
                 first = False
             return C_p
@@ -154,9 +277,12 @@ class PartitionedGemm:
                 else:
                     works.append(None)
         first = True
-        for idx, (k0, k1) in enumerate(chunks):
-            if world > 1 and works[idx] is not None:
-                works[idx].wait()  # CUDA: orders the current stream after the transfer
+        for g0, g1 in slice_groups(len(chunks), self.grow and world > 1):
+            if world > 1:
+                for idx in range(g0, g1):
+                    if works[idx] is not None:
+                        works[idx].wait()  # CUDA: orders the current stream after the transfer
+            k0, k1 = chunks[g0][0], chunks[g1 - 1][1]
             self.compute(alpha, A_p[:, k0:k1], B_local[k0:k1], beta if first else 1.0, C_p)
             first = False
         return C_p

@@ -32,6 +32,51 @@ def test_syrk_blocks_balance_area():
     assert max(area_eq) / min(area_eq) > 10
 
 
+def test_slice_groups():
+    assert partition.slice_groups(16) == [(0, 1), (1, 2), (2, 4), (4, 8), (8, 16)]
+    assert partition.slice_groups(5) == [(0, 1), (1, 2), (2, 4), (4, 5)]
+    assert partition.slice_groups(1) == [(0, 1)]
+    assert partition.slice_groups(0) == []
+    assert partition.slice_groups(3, grow=False) == [(0, 1), (1, 2), (2, 3)]
+    for n in range(1, 40):       # a partition of range(n), in order
+        g = partition.slice_groups(n)
+        assert g[0][0] == 0 and g[-1][1] == n and all(a[1] == b[0] for a, b in zip(g, g[1:]))
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+def test_pull_schedule_delivers_every_slice_without_deadlock(world):
+    """All ranks' copy-stream lists run against each other: a wait blocks until
+    the owner has signalled, a pull may only read rows its source already
+    holds, and when a slice is declared ready all its rows are there."""
+    chunks = [(0, 5), (5, 16), (16, 17), (17, 64)]
+    for src in (0, world - 1):
+        ops = {r: partition.pull_schedule(r, world, src, chunks) for r in range(world)}
+        pc = {r: 0 for r in range(world)}
+        signalled, have = set(), {r: set() for r in range(world)}
+        have[src] = set(range(chunks[-1][1]))
+        progress = True
+        while progress:
+            progress = False
+            for r in range(world):
+                while pc[r] < len(ops[r]):
+                    op = ops[r][pc[r]]
+                    if op[0] == "wait" and (op[1], op[2]) not in signalled:
+                        break
+                    if op[0] == "pull":
+                        rows = set(range(op[2], op[3]))
+                        assert rows <= have[op[1]], (r, op)
+                        have[r] |= rows
+                    elif op[0] == "signal":
+                        signalled.add((r, op[1]))
+                    elif op[0] == "ready":
+                        k0, k1 = chunks[op[1]]
+                        assert set(range(k0, k1)) <= have[r]
+                    pc[r] += 1
+                    progress = True
+        assert all(pc[r] == len(ops[r]) for r in range(world)), "deadlock"
+        assert [op[1] for op in ops[src] if op[0] == "ready"] == list(range(len(chunks)))
+
+
 def test_k_chunks():
     assert partition.k_chunks(10, 4) == [(0, 4), (4, 8), (8, 10)]
     assert partition.k_chunks(0, 4) == [(0, 0)]
