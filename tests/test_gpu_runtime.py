@@ -216,6 +216,26 @@ def test_large_pageable_arrays_travel_through_the_staging_rings():
 
 
 # --------------------------------------------------------------------------- multi-GPU entries
+def test_peer_pull_broadcast_matches_nccl():
+    """The strong-scaled GEMM plan with the shared operand sent by the copy
+    engines (PeerPullBroadcast) against the same plan with the NCCL broadcast:
+    same bits in B on every rank and in C, twice in a row (flag words reused).
+    One process per GPU through torchrun, up to four ranks (three or more use
+    the stream-ordered signals between the two pull phases)."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    world = min(n, 4)
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "peer_broadcast_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                        f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                        "--master-port", "29533", worker],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert f"PEER_BROADCAST_OK {world}" in r.stdout
+
+
 @pytest.mark.parametrize("ndev", [1, 2])
 def test_multi_gpu_entries_wait_for_the_callers_device_work(ndev):
     """Arrays of device 0 that are still being produced on the caller's stream
