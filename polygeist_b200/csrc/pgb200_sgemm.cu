@@ -129,17 +129,21 @@ __device__ __forceinline__ void report_status(int32_t *status, int32_t code, int
 // saved DRAM energy is SM clock (fp32 32768^3: 1155 -> 1455 MHz, 319 -> 268 ms).
 // Each producer adds one to a zeroed counter when the loads of its tile are
 // issued and waits for CTAs * r before round r.  The meeting is only a hint: a
-// producer that has waited as long as a whole tile took (the CTAs of the grid
-// are not all running, e.g. another kernel holds some SMs) stops meeting and
-// goes on alone; the product is the same either way.
+// producer that has waited as long as a whole tile took goes on without the
+// others (CTAs that started late, e.g. behind a short kernel of another
+// stream, have caught up by the next round), and after the third such wait
+// (the CTAs of the grid are not all running: another kernel holds some SMs)
+// it stops meeting for good; the product is the same either way.
 struct RoundMeeting {
   int32_t *ctr;
   bool waits;
+  int32_t given_up;
   int32_t round;
   long long t_begin, tile_cycles;
   __device__ __forceinline__ void init(int32_t *counter) {
     ctr = counter;
     waits = counter != nullptr;
+    given_up = 0;
     round = 0;
     t_begin = 0;
     tile_cycles = 0;
@@ -153,7 +157,7 @@ struct RoundMeeting {
       const long long limit = tile_cycles > STEP_WAIT_MIN ? tile_cycles : STEP_WAIT_MIN;
       while (*c < want) {
         if (clock64() - t_begin > limit) {
-          waits = false;
+          if (++given_up >= 3) waits = false;
           break;
         }
         __nanosleep(100);
