@@ -460,10 +460,7 @@ class Bench:
                 hf = symm_mem.rendezvous(fl, dist.group.WORLD)
                 flags = [hf.get_buffer(r, (self.world, slots), torch.int32) for r in range(self.world)]
                 memops = partition.stream_memops()
-            drop = os.environ.get("PGB_BENCH_DROP_SIGNAL")     # "owner,slice": a lost signal (tests)
-            peer = partition.PeerPullBroadcast(
-                torch, dist, views, src=0, flags=flags, memops=memops,
-                drop_signal=tuple(int(x) for x in drop.split(",")) if drop else None)
+            peer = partition.PeerPullBroadcast(torch, dist, views, src=0, flags=flags, memops=memops)
             self._symm = (buf, hb, fl, hf)   # the allocations must outlive the mapped views
         except Exception as e:          # noqa: BLE001 - any failure means "use NCCL"
             err = repr(e)
@@ -479,37 +476,23 @@ class Bench:
         """One untimed step on poisoned receive buffers: afterwards every rank's
         copy of the shared operand must equal the source's bit for bit (sum of
         the words as integers, compared across ranks); C is restored.  Returns
-        whether that held on every rank.  A step that does not finish within
-        a minute (a signal of the copy-engine route that never arrived) is let
-        through with PeerPullBroadcast.release() and counts as a failure."""
+        whether that held on every rank."""
         torch, dist = self.torch, self.dist
         keep = Cm.clone()
         if self.rank != 0:
             B.fill_(float("nan"))
         self.barrier()
         plan.run(ALPHA, A, B, BETA, Cm)
-        done = torch.cuda.Event()
-        done.record()
-        deadline, stuck = time.time() + 60.0, False
-        while not done.query():
-            if time.time() > deadline:
-                stuck = True
-                break
-            time.sleep(0.005)
-        if stuck and plan.peer_broadcast is not None:
-            plan.peer_broadcast.release()
         torch.cuda.synchronize()
         words = B.view(torch.int32)
         sums = torch.stack([words[i::8].sum(dtype=torch.int64) for i in range(8)])
         lo, hi = sums.clone(), sums.clone()
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-        ok = torch.tensor([0 if (stuck or not bool(torch.equal(lo, hi))) else 1],
-                          dtype=torch.int32, device=self.dev)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        same = bool(torch.equal(lo, hi))
         Cm.copy_(keep)
         self.barrier()
-        return int(ok.item()) == 1
+        return same
 
     def filled(self, w, rows, cols, aid, row0=0):
         t = self.torch.empty((rows, cols), dtype=self.tdt(w), device=self.dev)

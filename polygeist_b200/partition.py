@@ -173,8 +173,7 @@ class PeerPullBroadcast:
     a stream memory operation on its own memory: no kernel at all.  Without them an all-reduce per slice is the barrier (its
     kernel waits for the running product)."""
 
-    def __init__(self, torch, dist, views, src=0, group=None, flags=None, memops=None,
-                 drop_signal=None):
+    def __init__(self, torch, dist, views, src=0, group=None, flags=None, memops=None):
         self.torch, self.dist, self.views, self.src, self.group = torch, dist, views, src, group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -182,7 +181,6 @@ class PeerPullBroadcast:
         self.flag = torch.zeros(1, device=views[self.rank].device)
         self.flags = flags
         self.memops = memops if flags is not None else None
-        self.drop_signal = drop_signal   # (owner rank, slice): that signal is never sent (tests)
         self.call = 0
         self._numbers = None          # device words 1, 2, 3, ...: sources of the signal copies
         self._numbers_base = 0
@@ -196,20 +194,6 @@ class PeerPullBroadcast:
                                          device=self.views[self.rank].device)
         i = value - self._numbers_base
         return self._numbers[i:i + 1]
-
-    def release(self):
-        """Lets every wait of this rank's copy stream pass, now and from now on
-        (all flag words of this rank set to the largest value, from a stream of
-        its own): the way out when a signal did not arrive.  The slices it
-        lets through may be incomplete, so the caller must send the operand
-        again by another route; this object is not to be used afterwards."""
-        if self.flags is None:
-            return
-        torch = self.torch
-        side = torch.cuda.Stream()
-        with torch.cuda.stream(side):
-            self.flags[self.rank].fill_(2**31 - 1)
-        side.synchronize()
 
     def start(self, chunks):
         torch, dist = self.torch, self.dist
@@ -235,8 +219,6 @@ class PeerPullBroadcast:
                     elif self.rank != self.src:
                         for q in range(self.world):
                             if q == self.rank or q == self.src:
-                                continue
-                            if self.drop_signal == (self.rank, op[1]):
                                 continue
                             self.flags[q][self.rank, op[1]:op[1] + 1].copy_(number, non_blocking=True)
                 elif op[0] == "wait":
