@@ -293,3 +293,84 @@ module {
 // CHECK:         affine.for
 // CHECK:           affine.for
 // CHECK-NOT:     call @pgb200
+
+// -----
+
+// kernel_syr2k as tools/cgeist/Test/polybench/linear-algebra/blas/syr2k/syr2k.c:162-190
+// pins it: two products in one statement, the factors that do not depend on j
+// (B[i][k], A[i][k]) already hoisted into the k loop's body.  kernel_syrk in the
+// same hoisted form (syrk.c:147-170: alpha * A[i][k] computed in the k body).
+#map = affine_map<(d0) -> (d0 + 1)>
+module {
+  func.func @kernel_syr2k(%arg0: i32, %arg1: i32, %arg2: f64, %arg3: f64, %arg4: memref<?x1200xf64>, %arg5: memref<?x1000xf64>, %arg6: memref<?x1000xf64>) {
+    %0 = arith.index_cast %arg0 : i32 to index
+    %1 = arith.index_cast %arg1 : i32 to index
+    affine.for %arg7 = 0 to %0 {
+      affine.for %arg8 = 0 to #map(%arg7) {
+        %2 = affine.load %arg4[%arg7, %arg8] : memref<?x1200xf64>
+        %3 = arith.mulf %2, %arg3 : f64
+        affine.store %3, %arg4[%arg7, %arg8] : memref<?x1200xf64>
+      }
+      affine.for %arg8 = 0 to %1 {
+        %2 = affine.load %arg6[%arg7, %arg8] : memref<?x1000xf64>
+        %3 = affine.load %arg5[%arg7, %arg8] : memref<?x1000xf64>
+        affine.for %arg9 = 0 to #map(%arg7) {
+          %4 = affine.load %arg5[%arg9, %arg8] : memref<?x1000xf64>
+          %5 = arith.mulf %4, %arg2 : f64
+          %6 = arith.mulf %5, %2 : f64
+          %7 = affine.load %arg6[%arg9, %arg8] : memref<?x1000xf64>
+          %8 = arith.mulf %7, %arg2 : f64
+          %9 = arith.mulf %8, %3 : f64
+          %10 = arith.addf %6, %9 : f64
+          %11 = affine.load %arg4[%arg7, %arg9] : memref<?x1200xf64>
+          %12 = arith.addf %11, %10 : f64
+          affine.store %12, %arg4[%arg7, %arg9] : memref<?x1200xf64>
+        }
+      }
+    }
+    return
+  }
+  func.func @kernel_syrk_hoisted(%arg0: i32, %arg1: i32, %arg2: f64, %arg3: f64, %arg4: memref<?x1200xf64>, %arg5: memref<?x1000xf64>) {
+    %0 = arith.index_cast %arg0 : i32 to index
+    %1 = arith.index_cast %arg1 : i32 to index
+    affine.for %arg6 = 0 to %0 {
+      affine.for %arg7 = 0 to #map(%arg6) {
+        %2 = affine.load %arg4[%arg6, %arg7] : memref<?x1200xf64>
+        %3 = arith.mulf %2, %arg3 : f64
+        affine.store %3, %arg4[%arg6, %arg7] : memref<?x1200xf64>
+      }
+      affine.for %arg7 = 0 to %1 {
+        %2 = affine.load %arg5[%arg6, %arg7] : memref<?x1000xf64>
+        %3 = arith.mulf %arg2, %2 : f64
+        affine.for %arg8 = 0 to #map(%arg6) {
+          %4 = affine.load %arg5[%arg8, %arg7] : memref<?x1000xf64>
+          %5 = arith.mulf %3, %4 : f64
+          %6 = affine.load %arg4[%arg6, %arg8] : memref<?x1200xf64>
+          %7 = arith.addf %6, %5 : f64
+          affine.store %7, %arg4[%arg6, %arg8] : memref<?x1200xf64>
+        }
+      }
+    }
+    return
+  }
+}
+
+// CHECK:       func.func private @pgb200Dsyr2k(!llvm.ptr, i64, i64, f64, !llvm.ptr, i64, !llvm.ptr, i64, f64, !llvm.ptr, i64) -> i32
+// CHECK-LABEL: func.func @kernel_syr2k(
+// CHECK-SAME:    %[[NN:.+]]: i32, %[[NM:.+]]: i32, %[[ALPHA:.+]]: f64, %[[BETA:.+]]: f64, %[[C:.+]]: memref<?x1200xf64>, %[[A:.+]]: memref<?x1000xf64>, %[[B:.+]]: memref<?x1000xf64>)
+// CHECK-NOT:     affine.for
+// CHECK:         %[[STREAM:.+]] = llvm.mlir.zero : !llvm.ptr
+// CHECK-DAG:     %[[PA:.+]] = "polygeist.memref2pointer"(%[[A]]) : (memref<?x1000xf64>) -> !llvm.ptr
+// CHECK-DAG:     %[[PB:.+]] = "polygeist.memref2pointer"(%[[B]]) : (memref<?x1000xf64>) -> !llvm.ptr
+// CHECK-DAG:     %[[PC:.+]] = "polygeist.memref2pointer"(%[[C]]) : (memref<?x1200xf64>) -> !llvm.ptr
+// CHECK:         call @pgb200Dsyr2k(%[[STREAM]], %{{.*}}, %{{.*}}, %[[ALPHA]], %[[PA]], %{{.*}}, %[[PB]], %{{.*}}, %[[BETA]], %[[PC]], %{{.*}}) : (!llvm.ptr, i64, i64, f64, !llvm.ptr, i64, !llvm.ptr, i64, f64, !llvm.ptr, i64) -> i32
+// CHECK-NOT:     affine.for
+// CHECK:         return
+// CHECK-LABEL: func.func @kernel_syrk_hoisted(
+// CHECK-SAME:    %{{.*}}: i32, %{{.*}}: i32, %[[ALPHA:.+]]: f64, %[[BETA:.+]]: f64, %[[C:.+]]: memref<?x1200xf64>, %[[A:.+]]: memref<?x1000xf64>)
+// CHECK-NOT:     affine.for
+// CHECK-DAG:     %[[PA:.+]] = "polygeist.memref2pointer"(%[[A]])
+// CHECK-DAG:     %[[PC:.+]] = "polygeist.memref2pointer"(%[[C]])
+// CHECK:         call @pgb200Dsyrk(%{{.*}}, %{{.*}}, %{{.*}}, %[[ALPHA]], %[[PA]], %{{.*}}, %[[BETA]], %[[PC]], %{{.*}})
+// CHECK-NOT:     affine.for
+// CHECK:         return

@@ -33,7 +33,7 @@ def _prototype(name):
 
 
 @pytest.mark.parametrize("name", ["pgb200Dgemm", "pgb200Sgemm", "pgb200Dgemv", "pgb200Dsyrk",
-                                  "pgb200Ssyrk"])
+                                  "pgb200Ssyrk", "pgb200Dsyr2k", "pgb200Ssyr2k"])
 def test_emitted_calls_match_the_header_prototypes(name):
     """The type lists the pass declares (in the new .cpp inside the patch) and
     the lit test expects are those of the C prototypes."""
@@ -47,6 +47,13 @@ def test_emitted_calls_match_the_header_prototypes(name):
     if name in ("pgb200Dgemm", "pgb200Sgemm"):
         m = re.search(r"\{ptr, i64, i64, i64, fty, ptr, i64, ptr, i64, fty, ptr, i64\}", patch)
         assert m and [sym.get(t, t) for t in want] == "ptr i64 i64 i64 fty ptr i64 ptr i64 fty ptr i64".split()
+    elif name in ("pgb200Dsyr2k", "pgb200Ssyr2k"):
+        m = re.search(r"\{ptr, i64, i64, elt, ptr, i64, ptr, i64, elt, ptr, i64\}", patch)
+        assert m and [{"f64": "elt", "f32": "elt", "!llvm.ptr": "ptr"}.get(t, t) for t in want] == \
+            "ptr i64 i64 elt ptr i64 ptr i64 elt ptr i64".split()
+        if name == "pgb200Dsyr2k":
+            m = re.search(r"func\.func private @pgb200Dsyr2k\(([^)]*)\) -> i32", lit)
+            assert [t.strip() for t in m.group(1).split(",")] == want
     elif name in ("pgb200Dsyrk", "pgb200Ssyrk"):
         m = re.search(r"\{ptr, i64, i64, elt, ptr, i64, elt, ptr, i64\}", patch)
         assert m and [{"f64": "elt", "f32": "elt", "!llvm.ptr": "ptr"}.get(t, t) for t in want] == \
